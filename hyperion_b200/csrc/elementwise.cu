@@ -1,0 +1,183 @@
+// Row-wise kernels of the decoder: embedding lookup, residual add fused with RMSNorm, SwiGLU,
+// rotate-half position encoding, and the write of new keys and values into cache pages.
+// Each is instantiated for float (the 32-bit path) and for bfloat16 storage; arithmetic is float in
+// both. What they compute corresponds to the reference's embedding_gather_bf16, add_rmsnorm_bf16,
+// swiglu_rows_bf16, rope_bf16 and kv_append_rows_paged_bf16
+// (helios/crates/helios-hal/kernels/elementwise.cu:13,29,42,844; kernels/rmsnorm.cu:66), except
+// that the residual stream stays in float and a value is rounded once, when it is stored.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embedding_kernel(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                                 int hidden, int vocab, int* status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicOr(status, HB_STATUS_BAD_TOKEN);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)t * hidden + i] = 0.f;
+        return;
+    }
+    const TW* row = table + (size_t)id * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)t * hidden + i] = to_float(row[i]);
+}
+
+HB_EXPORT int hb_embedding(const void* table, int table_is_bf16, const int* ids, float* out, int tokens, int hidden,
+                           int vocab, int* status, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (table_is_bf16)
+        embedding_kernel<<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+    else
+        embedding_kernel<<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab, status);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- residual add + RMSNorm
+// Output row r normalises source row s = rows ? rows[r] : r of h (+ delta). With `write_h` the sum
+// is stored back into h[s] (the residual stream); it is skipped when rows are gathered for the
+// final norm, whose sum nobody reads again. The sum of squares is taken in a fixed order.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ weight,
+                                   TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps, int write_h) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* hrow = h + (size_t)s * hidden;
+    const TD* drow = delta ? delta + (size_t)s * hidden : nullptr;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = hrow[i];
+        if (drow) {
+            v += to_float(drow[i]);
+            if (write_h) hrow[i] = v;
+        }
+        sum = fmaf(v, v, sum);
+    }
+    const float total = block_sum(sum, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    TO* orow = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = hrow[i];
+        if (drow && !write_h) v += to_float(drow[i]);
+        orow[i] = from_float<TO>(v * inv * weight[i]);
+    }
+}
+
+HB_EXPORT int hb_add_rmsnorm(float* h, const void* delta, int delta_is_bf16, const float* weight, void* out,
+                             int out_is_bf16, const int* rows, int n_rows, int hidden, float eps, int write_h,
+                             cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = hidden >= 4096 ? 1024 : (hidden >= 1024 ? 512 : 256);
+#define HB_NORM(TD, TO) \
+    add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, write_h)
+    if (delta_is_bf16) {
+        if (out_is_bf16) HB_NORM(__nv_bfloat16, __nv_bfloat16); else HB_NORM(__nv_bfloat16, float);
+    } else {
+        if (out_is_bf16) HB_NORM(float, __nv_bfloat16); else HB_NORM(float, float);
+    }
+#undef HB_NORM
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// in: [tokens, 2*inter] with the gate in the first `inter` columns and the up projection in the
+// rest; out[t, i] = silu(gate) * up, silu(g) = g / (1 + exp(-g)) in float.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+    const int t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= inter) return;
+    const float g = to_float(gate_up[(size_t)t * 2 * inter + i]);
+    const float u = to_float(gate_up[(size_t)t * 2 * inter + inter + i]);
+    out[(size_t)t * inter + i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+}
+
+HB_EXPORT int hb_swiglu(const void* gate_up, void* out, int is_bf16, int tokens, int inter, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (tokens > 65535) return HB_UNSUPPORTED_SIZE;
+    dim3 grid((inter + 255) / 256, tokens);
+    if (is_bf16)
+        swiglu_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
+    else
+        swiglu_kernel<<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- rotate-half position encoding
+// Rotates `heads` consecutive heads of `head_dim` columns at the start of every row of `x` (row
+// stride `stride` elements), in place: y[i] = x[i] c - x[i+d/2] s, y[i+d/2] = x[i+d/2] c + x[i] s
+// with (c, s) = table[position][i]. The table holds cos and sin of position * base^(-2i/d).
+template <typename T>
+__global__ void rope_kernel(T* __restrict__ x, const int* __restrict__ positions, const float2* __restrict__ table,
+                            int stride, int heads, int head_dim, int max_positions, int* status) {
+    const int t = blockIdx.x;
+    const int half = head_dim >> 1;
+    const int pos = positions[t];
+    if (pos < 0 || pos >= max_positions) {
+        if (threadIdx.x == 0) atomicOr(status, HB_STATUS_BAD_POSITION);
+        return;
+    }
+    T* row = x + (size_t)t * stride;
+    const float2* cs = table + (size_t)pos * half;
+    for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
+        const int head = e / half, i = e - head * half;
+        const float2 c = cs[i];
+        T* p = row + head * head_dim + i;
+        const float x1 = to_float(p[0]), x2 = to_float(p[half]);
+        p[0] = from_float<T>(x1 * c.x - x2 * c.y);
+        p[half] = from_float<T>(x2 * c.x + x1 * c.y);
+    }
+}
+
+HB_EXPORT int hb_rope(void* x, int is_bf16, const int* positions, const float* table, int tokens, int stride, int heads,
+                      int head_dim, int max_positions, int* status, cudaStream_t stream) {
+    if (tokens <= 0 || heads <= 0) return 0;
+    if (head_dim & 1) return HB_UNSUPPORTED_SIZE;
+    if (is_bf16)
+        rope_kernel<<<tokens, 256, 0, stream>>>((__nv_bfloat16*)x, positions, (const float2*)table, stride, heads, head_dim, max_positions, status);
+    else
+        rope_kernel<<<tokens, 256, 0, stream>>>((float*)x, positions, (const float2*)table, stride, heads, head_dim, max_positions, status);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- key/value write into pages
+// One cache layer is [pages, 2, kv_heads, page_size, head_dim]. Token t of row r = token_row[t] at
+// position p goes to page block_table[r][p / page_size], slot p % page_size. A missing page sets
+// the status word and the token is skipped.
+template <typename T>
+__global__ void kv_store_kernel(const T* __restrict__ src, int stride, int k_offset, int v_offset, T* __restrict__ cache,
+                                const int* __restrict__ block_table, int table_width, const int* __restrict__ token_row,
+                                const int* __restrict__ positions, int kv_heads, int head_dim, int page_size, int pages,
+                                int* status) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int block = pos / page_size;
+    const int page = (block < table_width && pos >= 0) ? block_table[(size_t)token_row[t] * table_width + block] : -1;
+    if (page < 0 || page >= pages) {
+        if (threadIdx.x == 0) atomicOr(status, HB_STATUS_BAD_PAGE);
+        return;
+    }
+    const int slot = pos - block * page_size;
+    const int width = kv_heads * head_dim;
+    const T* row = src + (size_t)t * stride;
+    const size_t page_base = (size_t)page * 2 * kv_heads * page_size * head_dim;
+    for (int e = threadIdx.x; e < 2 * width; e += blockDim.x) {
+        const int which = e / width, c = e - which * width;
+        const int head = c / head_dim, d = c - head * head_dim;
+        const T v = row[(which ? v_offset : k_offset) + c];
+        cache[page_base + (((size_t)which * kv_heads + head) * page_size + slot) * head_dim + d] = v;
+    }
+}
+
+HB_EXPORT int hb_kv_store(const void* src, int is_bf16, int tokens, int stride, int k_offset, int v_offset, void* cache,
+                          const int* block_table, int table_width, const int* token_row, const int* positions,
+                          int kv_heads, int head_dim, int page_size, int pages, int* status, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (is_bf16)
+        kv_store_kernel<<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)src, stride, k_offset, v_offset, (__nv_bfloat16*)cache,
+                                                    block_table, table_width, token_row, positions, kv_heads, head_dim, page_size, pages, status);
+    else
+        kv_store_kernel<<<tokens, 256, 0, stream>>>((const float*)src, stride, k_offset, v_offset, (float*)cache, block_table,
+                                                    table_width, token_row, positions, kv_heads, head_dim, page_size, pages, status);
+    return launch_status();
+}

@@ -1,0 +1,129 @@
+"""The step function: run a batch of (request, its next tokens) from the cache and return the
+logits at the wanted places.
+
+A step runs only the tokens it is given, as one flat batch, whatever mixture of prompt portions
+and single decoded tokens it holds.  It is refused as a whole, with nothing applied, when an entry
+is malformed or the pages it needs are not there, as the reference refuses a bad plan whole
+(helios/crates/helios-hal/src/backends/hopper_sm90/plan_exec.rs:17-41,
+helios/crates/helios-hal/src/pool_plan.rs:86-102).
+"""
+from __future__ import annotations
+
+from typing import Hashable, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..cache.manager import NO_PAGE, CacheManager, OutOfPages
+from ..csrc import build
+from ..models.model import DecoderModel
+from .batch import BadStep, MetadataPacker, Row, StepContext, StepEntry
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager):
+        if model.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device only (no CPU path exists)")
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.packer = MetadataPacker(self.device)
+        self.planners = model.step_planners()
+        build.build_many(model.kernel_modules())
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ validation
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise BadStep("a step needs at least one entry")
+        seen: set[Hashable] = set()
+        vocab, limit = self.model.spec.vocab_size, self.model.spec.max_positions
+        for entry in entries:
+            if entry.request in seen:
+                raise BadStep(f"request {entry.request!r} appears twice in one step")
+            seen.add(entry.request)
+            count = len(entry.tokens)
+            if count == 0:
+                raise BadStep(f"request {entry.request!r} brings no tokens")
+            for token in entry.tokens:
+                if isinstance(token, bool) or not isinstance(token, int) or not 0 <= token < vocab:
+                    raise BadStep(f"request {entry.request!r}: token {token!r} is outside the vocabulary of {vocab}")
+            for index in entry.want:
+                if isinstance(index, bool) or not isinstance(index, int) or not 0 <= index < count:
+                    raise BadStep(f"request {entry.request!r}: wanted index {index!r} is outside its {count} tokens")
+            length = self.cache.length(entry.request) if self.cache.has(entry.request) else 0
+            if length + count > limit:
+                raise BadStep(f"request {entry.request!r} would reach position {length + count}, the model's limit is {limit}")
+
+    # ------------------------------------------------------------------ the batch on the device
+    def _context(self, entries: Sequence[StepEntry]) -> StepContext:
+        rows: list[Row] = []
+        token_ids: list[int] = []
+        positions: list[int] = []
+        token_row: list[int] = []
+        want: list[int] = []
+        for index, entry in enumerate(entries):
+            start, position = len(token_ids), self.cache.length(entry.request)
+            rows.append(Row(entry.request, start, len(entry.tokens), position, self.cache.slot(entry.request)))
+            token_ids.extend(entry.tokens)
+            positions.extend(range(position, position + len(entry.tokens)))
+            token_row.extend([index] * len(entry.tokens))
+            want.extend(start + i for i in entry.want)
+        packer = self.packer
+        packer.begin()
+        packer.add("token_ids", token_ids)
+        packer.add("positions", positions)
+        packer.add("token_row", token_row)
+        packer.add("row_start", [row.start for row in rows] + [len(token_ids)])
+        packer.add("slots", [row.slot for row in rows])
+        if want:
+            packer.add("want", want)
+        for group in range(len(self.cache.paged)):
+            tables = [self.cache.table(group, row.request) for row in rows]
+            width = max(1, max(len(t) for t in tables))
+            flat: list[int] = []
+            for table in tables:
+                flat.extend(table)
+                flat.extend([NO_PAGE] * (width - len(table)))
+            packer.add(f"table{group}", flat, (len(rows), width))
+        host = {"positions": positions, "token_row": token_row, "want": want}
+        for key, plan in self.planners.items():
+            plan(rows, packer, host)
+        arrays = packer.finish()
+        extra = {k: v for k, v in arrays.items() if k not in ("token_ids", "positions", "token_row", "row_start", "slots", "want")
+                 and not k.startswith("table")}
+        return StepContext(rows=rows, n_tokens=len(token_ids), token_ids=arrays["token_ids"], positions=arrays["positions"],
+                           token_row=arrays["token_row"], row_start=arrays["row_start"], want_rows=arrays.get("want"),
+                           n_want=len(want), paged_tables=[arrays[f"table{g}"] for g in range(len(self.cache.paged))],
+                           slots=arrays["slots"], extra=extra, host=host)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the entries as one batch.  Returns float logits [wanted, vocab] on the device, in the
+        order of the entries and of each entry's ``want``, or None when nothing was wanted."""
+        entries = list(entries)
+        self._validate(entries)
+        added = []
+        try:
+            for entry in entries:
+                if not self.cache.has(entry.request):
+                    self.cache.add_request(entry.request)
+                    added.append(entry.request)
+            self.cache.extend_all([(entry.request, len(entry.tokens)) for entry in entries])
+        except OutOfPages:
+            for request in added:
+                self.cache.free(request)
+            raise
+        context = self._context(entries)
+        logits = self.model.forward(context, self.cache)
+        for entry in entries:
+            self.cache.advance(entry.request, len(entry.tokens))
+        self.steps_run += 1
+        return logits
+
+    def finish(self, request: Hashable) -> None:
+        """The request is over: its pages and its state slot go back to the pools."""
+        self.cache.free(request)
+
+    def check_device_status(self) -> None:
+        ops.raise_on_status(self.device)

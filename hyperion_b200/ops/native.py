@@ -1,0 +1,65 @@
+"""Glue between torch tensors and the exported C launchers of ``csrc``.
+
+Every launcher takes raw device pointers, sizes and the CUDA stream and returns an int: 0 on
+success, a positive ``cudaError_t`` if the launch failed, a negative code if it refused its
+arguments.  Nothing here falls back to another implementation: a tensor that is not on a CUDA
+device, a failed build or a refused size raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any
+
+import torch
+
+from ..csrc import build
+
+_REFUSALS = {-1: "bad argument", -2: "unsupported size", -3: "scratch too small", -4: "set-up failed"}
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or the launch failed."""
+
+
+def ptr(tensor: torch.Tensor | None) -> ctypes.c_void_p:
+    if tensor is None:
+        return ctypes.c_void_p(0)
+    return ctypes.c_void_p(tensor.data_ptr())
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def require_cuda(*tensors: torch.Tensor | None) -> None:
+    for tensor in tensors:
+        if tensor is not None and not tensor.is_cuda:
+            raise KernelError("the kernels run on a CUDA device only; got a tensor on " + str(tensor.device))
+
+
+def check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: launcher refused its arguments ({_REFUSALS.get(code, code)})")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def is_bf16(tensor: torch.Tensor) -> int:
+    if tensor.dtype == torch.bfloat16:
+        return 1
+    if tensor.dtype == torch.float32:
+        return 0
+    raise KernelError(f"unsupported element type {tensor.dtype} (float32 and bfloat16 only)")
+
+
+def library(module: str, **defines: Any) -> ctypes.CDLL:
+    return build.load(module, defines)
+
+
+def i32(value: int) -> ctypes.c_int:
+    return ctypes.c_int(int(value))
+
+
+def f32(value: float) -> ctypes.c_float:
+    return ctypes.c_float(float(value))

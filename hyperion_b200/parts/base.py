@@ -1,0 +1,160 @@
+"""Interfaces and registries of the parts a layer is put together from.
+
+Five kinds of part exist: mixer (attention here), feed-forward, norm, position encoding and the
+arrangement of a block; embedding and output head are parts too.  A part is built from its
+:class:`PartSpec` (sizes and constants only), declares the tensors it wants by name and shape,
+receives them once, and then runs on the tokens of a step.  A part never learns which model it is
+in.  New kinds are added with the ``register_*`` functions; nothing else has to change.
+
+What a part must offer:
+
+``weights() -> dict[name, WeightSpec]``   tensor names relative to its prefix, with shapes
+``load(tensors)``                         the tensors, on the device, in their stored element type
+``forward(...)``                          see each base class
+
+A mixer additionally states what it keeps between steps (``cache_request``): pages of keys and
+values (:class:`PagedKV`), a record of fixed size per request (:class:`RequestState`), or nothing.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Mapping, Optional
+
+import torch
+
+from .spec import PartSpec
+
+
+@dataclass(frozen=True)
+class WeightSpec:
+    shape: tuple[int, ...]
+    integer: bool = False  # integer tables are kept as int32, everything else as a float type
+    init: str = "normal"  # how random weights fill it: "normal" = N(0, std), "one_plus_normal" = 1 + N(0, std)
+
+
+@dataclass(frozen=True)
+class PagedKV:
+    """Keys and values per token, kept in pages. ``window`` > 0: only the last ``window`` positions
+    are ever read again, so older pages may be given back while the request lives."""
+
+    kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class RequestState:
+    """A record of fixed shape per live request, zeroed when a request takes the slot."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class BuildContext:
+    """What a part may know when it is built: the element type of activations and the device."""
+
+    dtype: torch.dtype
+    device: torch.device
+    max_positions: int
+    shared: dict  # parts may keep tables here that other parts with the same parameters reuse
+
+
+class Part:
+    def __init__(self, spec: PartSpec, build: BuildContext):
+        self.spec = spec
+        self.dtype = build.dtype
+        self.device = build.device
+
+    def weights(self) -> dict[str, WeightSpec]:
+        return {}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        pass
+
+    def kernel_modules(self) -> list[tuple[str, dict]]:
+        """The native modules (name, definitions) this part launches; built before the first step."""
+        return []
+
+
+class Norm(Part):
+    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Add ``delta`` into the float residual stream ``h`` (in place, unless ``rows`` selects rows
+        to gather) and return the normalised rows in the activation type."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def apply_(self, x: torch.Tensor, heads: int, head_dim: int, positions: torch.Tensor) -> None:
+        """Encode the positions into the first ``heads`` heads of every row of ``x``, in place."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_request(self) -> PagedKV | RequestState | None:
+        return None
+
+    def forward(self, x: torch.Tensor, step: Any, cache: Any, own_cache: bool) -> torch.Tensor:
+        """``x`` [tokens, hidden] in the activation type; ``step`` the step's batch description
+        (:class:`hyperion_b200.engine.batch.StepContext`); ``cache`` the view of this run's cache
+        (``None`` if it asked for none); ``own_cache`` false when the cache belongs to another
+        schedule entry and must only be read.  Returns [tokens, hidden]."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, step: Any) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """int32 ids -> float residual stream [tokens, hidden]."""
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Normalised rows -> float logits [rows, vocab]."""
+        raise NotImplementedError
+
+
+class Arrangement:
+    """How one layer wires its parts.  ``forward`` gets the residual stream ``h`` and a pending
+    ``delta`` not yet added to it (so the add fuses with the next norm) and returns the new pair."""
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Mapping[str, Norm]):
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, dict(norms)
+
+    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], step: Any, cache: Any, own_cache: bool):
+        raise NotImplementedError
+
+
+MIXERS: dict[str, Callable[[PartSpec, BuildContext], Mixer]] = {}
+FEED_FORWARDS: dict[str, Callable[[PartSpec, BuildContext], FeedForward]] = {}
+NORMS: dict[str, Callable[[PartSpec, BuildContext], Norm]] = {}
+POSITIONS: dict[str, Callable[[PartSpec, BuildContext], PositionEncoding]] = {}
+EMBEDDINGS: dict[str, Callable[[PartSpec, BuildContext], Embedding]] = {}
+HEADS: dict[str, Callable[[PartSpec, BuildContext], Head]] = {}
+ARRANGEMENTS: dict[str, Callable[..., Arrangement]] = {}
+
+
+def _register(table: dict, kind: str, factory: Callable) -> None:
+    if kind in table and table[kind] is not factory:
+        raise ValueError(f"part kind {kind!r} is already registered")
+    table[kind] = factory
+
+
+def register_mixer(kind: str, factory) -> None: _register(MIXERS, kind, factory)
+def register_feed_forward(kind: str, factory) -> None: _register(FEED_FORWARDS, kind, factory)
+def register_norm(kind: str, factory) -> None: _register(NORMS, kind, factory)
+def register_position(kind: str, factory) -> None: _register(POSITIONS, kind, factory)
+def register_embedding(kind: str, factory) -> None: _register(EMBEDDINGS, kind, factory)
+def register_head(kind: str, factory) -> None: _register(HEADS, kind, factory)
+def register_arrangement(kind: str, factory) -> None: _register(ARRANGEMENTS, kind, factory)
+
+
+def make(table: dict, spec: PartSpec, build: BuildContext):
+    if spec.kind not in table:
+        raise KeyError(f"no part of kind {spec.kind!r} is registered (known: {sorted(table)})")
+    return table[spec.kind](spec, build)
