@@ -1,0 +1,124 @@
+"""Trace replay on the GPU: the same requests whole, with the last 32 tokens one by one, in portions
+of changing size, and mixed with other requests over a pool so small that pages are reused; in
+float32 and in bfloat16, every position compared with the plain implementation."""
+from __future__ import annotations
+
+import pytest
+
+from helpers import TINY, TOLERANCE, compare_steps, make_folder, plain_logits, random_ids, run_trace
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [70, 45, 100, 33, 90, 61], "B": [130, 40, 77, 200, 35, 96]}
+
+
+def requests_for(name: str) -> dict[str, list[int]]:
+    config, seed = TINY[name]
+    return {f"r{i}": random_ids(100 * seed + i, n, config.vocab_size) for i, n in enumerate(LENGTHS[name])}
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def model(request, tmp_path_factory):
+    name = request.param
+    folder = make_folder(tmp_path_factory.mktemp(f"model_{name}"), name)
+    requests = requests_for(name)
+    reference = {rid: plain_logits(folder, ids) for rid, ids in requests.items()}
+    return name, folder, requests, reference
+
+
+def round64(n: int) -> int:
+    return -(-n // 64) * 64
+
+
+def whole_steps(requests):
+    steps = []
+    for i, (rid, ids) in enumerate(requests.items()):
+        steps.append({"step": i, "entries": [{"id": rid, "tokens": ids, "want": list(range(len(ids)))}], "end": [rid]})
+    return steps
+
+
+def tail_steps(requests, tail=32):
+    steps = []
+    for rid, ids in requests.items():
+        head = len(ids) - tail
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": ids[:head], "want": [head - 1]}], "end": []})
+        for k in range(head, len(ids)):
+            steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": [ids[k]], "want": [0]}],
+                          "end": [rid] if k == len(ids) - 1 else []})
+    return steps
+
+
+def portion_steps(requests, sizes=(7, 2, 16, 3, 2, 33, 5, 2, 64, 9)):
+    steps = []
+    k = 0
+    for rid, ids in requests.items():
+        at = 0
+        while at < len(ids):
+            n = min(sizes[k % len(sizes)], len(ids) - at)
+            if len(ids) - at - n == 1:  # never leave a single token over: portions go down to two
+                n += 1
+            k += 1
+            steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": ids[at:at + n], "want": list(range(n))}],
+                          "end": [rid] if at + n == len(ids) else []})
+            at += n
+    return steps
+
+
+def mixed_steps(requests, live_max=4, decode_tail=12, sizes=(5, 2, 19, 3, 8, 2, 30, 4)):
+    """Up to four live requests; portions of some beside single tokens of others; a request sits out
+    every fifth step; new requests start as others end, so freed pages go to later requests."""
+    waiting = list(requests.items())
+    live: dict[str, int] = {}
+    steps = []
+    peak = 0
+    k = 0
+    while waiting or live:
+        while waiting and len(live) < live_max:
+            rid, _ = waiting.pop(0)
+            live[rid] = 0
+        entries, ended = [], []
+        for j, rid in enumerate(list(live)):
+            ids, at = requests[rid], live[rid]
+            if (len(steps) + j) % 5 == 4 and len(live) > 1:
+                continue
+            n = 1 if at >= len(ids) - decode_tail else min(sizes[k % len(sizes)], len(ids) - decode_tail - at)
+            k += 1
+            entries.append({"id": rid, "tokens": ids[at:at + n], "want": list(range(n))})
+            live[rid] = at + n
+            if live[rid] == len(ids):
+                ended.append(rid)
+        peak = max(peak, sum(round64(at) for at in live.values()))
+        steps.append({"step": len(steps), "entries": entries, "end": ended})
+        for rid in ended:
+            del live[rid]
+    return steps, peak
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+class TestReplay:
+    def test_whole(self, model, dtype, tmp_path):
+        name, folder, requests, reference = model
+        steps = whole_steps(requests)
+        results = run_trace(folder, dtype, steps, tmp_path, max_tokens=round64(max(map(len, requests.values()))))
+        compare_steps(steps, results, reference, TOLERANCE[dtype])
+
+    def test_last_32_one_by_one(self, model, dtype, tmp_path):
+        name, folder, requests, reference = model
+        steps = tail_steps(requests)
+        results = run_trace(folder, dtype, steps, tmp_path, max_tokens=round64(max(map(len, requests.values()))))
+        compare_steps(steps, results, reference, TOLERANCE[dtype])
+
+    def test_portions_of_changing_size(self, model, dtype, tmp_path):
+        name, folder, requests, reference = model
+        steps = portion_steps(requests)
+        assert min(len(e["tokens"]) for s in steps for e in s["entries"]) == 2
+        results = run_trace(folder, dtype, steps, tmp_path, max_tokens=round64(max(map(len, requests.values()))))
+        compare_steps(steps, results, reference, TOLERANCE[dtype])
+
+    def test_mixed_with_page_reuse(self, model, dtype, tmp_path):
+        name, folder, requests, reference = model
+        steps, peak = mixed_steps(requests)
+        assert max(len(s["entries"]) for s in steps) == 4
+        assert peak < sum(round64(len(ids)) for ids in requests.values())  # the pool cannot hold all: pages are reused
+        results = run_trace(folder, dtype, steps, tmp_path, max_tokens=peak)
+        compare_steps(steps, results, reference, TOLERANCE[dtype])
