@@ -1,0 +1,276 @@
+"""Decode and prefill throughput of the engine on one B200, Qwen2.5-7B shape, random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch (default 8): W
+untimed and K timed decode steps of ``batch`` requests that were each prefilled with 2,048 random
+token ids, timed with CUDA events on the device.  ``e2e`` is the same through ``Engine.generate``
+(token ids in from the host every step, sampled ids back to the host every step).  ``prefill`` is
+one whole 2,048-token prompt in one step.  ``roofline`` relates the decode step to the bytes it has
+to read (every weight it uses once, plus the cache of the live requests).  ``points`` holds decode
+at batch 1 and 64.  Weights (15 GB) are larger than L2, so every step streams them from HBM.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PROMPT = 2048
+CONTEXT = 4096
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# H100 decode at batch 8 (context 512) published by the reference: docs/performance-log.md:239-242
+BASELINE_TOK_S = {1: 146.0, 8: 1087.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        return json.loads(path.read_text()), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.path = Path(tempfile.mkstemp(suffix=".csv")[1])
+        self.process = None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                            stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.process = None
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.path.read_text().splitlines():
+            fields = [f.strip() for f in line.split(",")]
+            if len(fields) < 6:
+                continue
+            try:
+                clocks.append(float(fields[0]))
+                maxima.append(float(fields[1]))
+            except ValueError:
+                continue
+            for name, value in zip(names, fields[2:6]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        self.path.unlink(missing_ok=True)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max(maxima) if maxima else None,
+                "reasons": sorted(reasons)}
+
+
+def reference_arm() -> int:
+    # The reference's runtime is Rust (helios) with CUDA kernels built for sm_80/sm_90; this image has
+    # no cargo or rustc, and `pip install /root/reference` finds no Python project at its root.
+    print(json.dumps({"impl": "reference", "unavailable": "the reference runtime is Rust + sm_90 CUDA; no Rust toolchain in this image and pip finds no installable project (see DESIGN.md)"}))
+    return 0
+
+
+def model_config(layers: int):
+    from hyperion_b200.config import Qwen2Config
+
+    return Qwen2Config(num_hidden_layers=layers, hidden_size=3584, intermediate_size=18944, num_attention_heads=28,
+                       num_key_value_heads=4, head_dim=128, vocab_size=152064, max_position_embeddings=32768, rope_theta=1e6,
+                       rms_norm_eps=1e-6, tie_word_embeddings=False)
+
+
+def weight_bytes(c) -> int:
+    q, kv = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
+    per_layer = (q + 2 * kv) * c.hidden_size + (q + 2 * kv) + q * c.hidden_size + 3 * c.hidden_size * c.intermediate_size
+    return 2 * (c.num_hidden_layers * per_layer + c.vocab_size * c.hidden_size) + 4 * (2 * c.num_hidden_layers + 1) * c.hidden_size
+
+
+def prefill_flops(c, tokens: int) -> float:
+    q, kv = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
+    linear = 2.0 * tokens * ((q + 2 * kv) * c.hidden_size + q * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
+    attention = 4.0 * c.num_attention_heads * c.head_dim * tokens * (tokens + 1) / 2
+    return c.num_hidden_layers * (linear + attention) + 2.0 * c.hidden_size * c.vocab_size
+
+
+def random_prompt(seed: int, count: int, vocab: int) -> list[int]:
+    import torch
+
+    return torch.randint(0, vocab, (count,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def time_decode(engine, batch: int, steps: int, warmup: int) -> dict:
+    """``batch`` requests prefilled to 2,048 tokens, then W untimed + K timed decode steps (one new
+    token per request per step, LM head and token choice included), CUDA events around the K steps."""
+    import torch
+
+    from hyperion_b200.engine.batch import StepEntry
+    from hyperion_b200.ops import native
+    from hyperion_b200.sampling import GREEDY, pack_options
+
+    vocab = engine.model.spec.vocab_size
+    names = [f"bench{batch}_{i}" for i in range(batch)]
+    for i, name in enumerate(names):
+        engine.step([StepEntry(name, random_prompt(i, PROMPT, vocab), [])])
+    feed = [random_prompt(1000 + s, batch, vocab) for s in range(steps + warmup)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    options = {"sampling_options": ([w for name in names for w in pack_options(GREEDY, 0, engine.cache.slot(name))], (batch, 8))}
+
+    def one(s):
+        logits = engine.runner.step([StepEntry(name, [feed[s][i]], [0]) for i, name in enumerate(names)], options)
+        engine.sampler.sample(logits, engine.runner.last_context.extra["sampling_options"])
+
+    for s in range(warmup):
+        one(s)
+    torch.cuda.synchronize()
+    launches_before = native.LAUNCHES[0]
+    host_start = time.perf_counter()
+    start.record()
+    for s in range(warmup, warmup + steps):
+        one(s)
+    stop.record()
+    torch.cuda.synchronize()
+    host_ms = (time.perf_counter() - host_start) * 1e3
+    ms = start.elapsed_time(stop)
+    launches = native.LAUNCHES[0] - launches_before + getattr(engine.runner, "graph_launches", 0)
+    mean_context = PROMPT + warmup + (steps + 1) / 2
+    h2d = engine.runner.packer._cursor * 4
+    for name in names:
+        engine.finish(name)
+    engine.check()
+    return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "host_ms_per_step": host_ms / steps,
+            "launches": launches, "mean_context": mean_context, "h2d_bytes": h2d}
+
+
+def time_prefill(engine, reps: int = 5, warmup: int = 3) -> dict:
+    import torch
+
+    from hyperion_b200.engine.batch import StepEntry
+
+    vocab = engine.model.spec.vocab_size
+    times = []
+    for r in range(warmup + reps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        prompt = random_prompt(50 + r, PROMPT, vocab)
+        torch.cuda.synchronize()
+        start.record()
+        engine.step([StepEntry("prefill", prompt, [PROMPT - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        engine.finish("prefill")
+        if r >= warmup:
+            times.append(start.elapsed_time(stop))
+    engine.check()
+    return {"ms": statistics.median(times)}
+
+
+def time_e2e(engine, batch: int, steps: int, warmup: int) -> dict:
+    """Decode throughput through ``Engine.generate``: prompts go in from the host, every step's
+    sampled ids come back to the host before the next step is planned."""
+    from hyperion_b200.sampling import SamplingParams
+
+    vocab = engine.model.spec.vocab_size
+    prompts = [random_prompt(i, PROMPT, vocab) for i in range(batch)]
+    stamps: list[float] = []
+
+    def on_token(index, token):
+        if index == batch - 1:
+            stamps.append(time.perf_counter())
+
+    engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=warmup + steps + 1, ignore_eos=True), max_batch=batch,
+                    max_batch_tokens=batch * PROMPT, prefill_chunk_busy=PROMPT, on_token=on_token)
+    seconds = stamps[-1] - stamps[warmup]
+    return {"tok_s": batch * steps / seconds, "ms_per_step": seconds / steps * 1e3, "h2d_bytes": engine.runner.packer._cursor * 4,
+            "d2h_bytes": batch * 4}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=28, help="fewer than the configuration's 28 only to save memory or time")
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points, prefill and e2e")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print("bench.py: this engine runs on one GPU; --gpus > 1 is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from hyperion_b200.api import Engine
+    from hyperion_b200.ops import native
+
+    measured, source = peaks()
+    config = model_config(args.layers)
+    largest = args.batch if args.skip_points else max(args.batch, 64)
+    tokens_needed = largest * (PROMPT + 64 + max(args.steps + args.warmup, 64 + 8)) + PROMPT
+    engine = Engine.from_random("Qwen2ForCausalLM", config, seed=0, dtype="bfloat16", page_size=16,
+                                max_tokens=tokens_needed, max_requests=max(largest, 8))
+    clocks = ClockSampler()
+    clocks.start()
+    main_run = time_decode(engine, args.batch, args.steps, args.warmup)
+    clock_record = clocks.stop()
+
+    record = {
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen2.5-7B)",
+        "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(main_run["tok_s"] / BASELINE_TOK_S[args.batch], 3) if args.batch in BASELINE_TOK_S else None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights (N(0, 0.02)) and uniform random token ids",
+        "impl": "ours",
+        "config": {"model": "Qwen2.5-7B shape", "layers": args.layers, "layers_of_config": 28, "hidden": config.hidden_size,
+                   "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
+                   "intermediate": config.intermediate_size, "vocab": config.vocab_size, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "prompt_len": PROMPT, "decode_from_context": PROMPT, "page_size": 16, "parallelism": "single GPU",
+                   "l2": "weights (15 GB) exceed L2; every step streams them", "peaks": source},
+        "clocks": clock_record,
+        "gpu_launches": main_run["launches"],
+        "host_ms_per_step": round(main_run["host_ms_per_step"], 4),
+    }
+    bytes_per_step = weight_bytes(config) + args.batch * main_run["mean_context"] * engine.cache.bytes_per_token()
+    achieved = bytes_per_step / (main_run["ms_per_step"] / 1e3) / 1e9
+    record["roofline"] = {"bound": "hbm", "achieved": round(achieved, 1), "peak": measured["hbm_gbs"], "unit": "GB/s",
+                          "frac": round(achieved / measured["hbm_gbs"], 4), "of": source}
+    if not args.skip_points:
+        prefill = time_prefill(engine)
+        flops = prefill_flops(config, PROMPT)
+        record["prefill"] = {"value": round(PROMPT / (prefill["ms"] / 1e3), 1), "tokens": PROMPT, "ms": round(prefill["ms"], 3),
+                             "frac": round(flops / (prefill["ms"] / 1e3) / (measured["bf16_tflops"] * 1e12), 4), "of": source}
+        short = min(args.steps, 64)
+        record["points"] = {"decode_b1": round(time_decode(engine, 1, short, args.warmup)["tok_s"], 1),
+                            "decode_b64": round(time_decode(engine, 64, short, args.warmup)["tok_s"], 1)}
+        e2e = time_e2e(engine, args.batch, min(args.steps, 64), args.warmup)
+        record["e2e"] = {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d_bytes"],
+                         "d2h_bytes_per_step": e2e["d2h_bytes"], "ms_per_step": round(e2e["ms_per_step"], 4)}
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

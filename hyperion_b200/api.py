@@ -12,12 +12,16 @@ from typing import Any, Optional, Sequence
 
 import torch
 
-from .cache.manager import CacheManager
+from .cache.manager import CacheManager, OutOfPages
 from .config.generation import GenerationDefaults, read_generation_defaults
-from .engine.batch import StepEntry
+from .engine.batch import BadStep, StepEntry
 from .engine.runner import ModelRunner
 from .models import DecoderModel, get_architecture, read_model_config
+from .parts.base import RequestState
+from .sampling import Sampler, SamplingParams, pack_options
 from .weights import init_random, load_weights
+
+SAMPLER_STATE = -1  # the cache manager's user id of the sampler's per-request record
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -48,8 +52,12 @@ class Engine:
         self.page_size = page_size
         self.defaults = defaults or GenerationDefaults(eos_token_ids=tuple(getattr(config, "eos_token_ids", ()) or ()))
         num_pages = max(1, -(-max_tokens // page_size))
-        self.cache = CacheManager(model.cache_users(), page_size, num_pages, max_requests, dtype=model.dtype, device=model.device)
+        vocab = model.spec.vocab_size
+        users = model.cache_users() + [(SAMPLER_STATE, RequestState((Sampler.seen_words(vocab),), torch.int32))]
+        self.cache = CacheManager(users, page_size, num_pages, max_requests, dtype=model.dtype, device=model.device)
         self.runner = ModelRunner(model, self.cache)
+        self.sampler = Sampler(vocab, model.device, seen=self.cache.state_storage(SAMPLER_STATE))
+        self._token_staging = torch.empty(max(1, max_requests), dtype=torch.int32, pin_memory=True)
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -87,6 +95,90 @@ class Engine:
 
     def finish(self, request) -> None:
         self.runner.finish(request)
+
+    # ------------------------------------------------------------------ generation
+    def generate(self, prompts: Sequence[Sequence[int]], sampling=None, *, max_batch: Optional[int] = None,
+                 max_batch_tokens: int = 2048, prefill_chunk_busy: int = 512, max_seq_len: Optional[int] = None,
+                 on_token=None, return_reasons: bool = False):
+        """Generate a continuation for every prompt (lists of token ids) with continuous batching.
+
+        ``sampling`` is one :class:`SamplingParams` for all prompts or one per prompt; missing fields
+        take the model folder's ``generation_config.json`` defaults.  Returns the generated ids per
+        prompt (with ``return_reasons`` also why each ended: ``stop``, ``length`` or a failure text).
+        ``on_token(index, token)`` is called as tokens appear.
+        """
+        from .engine.scheduler import Request, Scheduler, SchedulerConfig
+
+        prompts = [list(p) for p in prompts]
+        if sampling is None:
+            d = self.defaults
+            sampling = SamplingParams(temperature=d.temperature, top_p=d.top_p, top_k=d.top_k, repetition_penalty=d.repetition_penalty)
+        per_prompt = list(sampling) if isinstance(sampling, (list, tuple)) else [sampling] * len(prompts)
+        if len(per_prompt) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        limit = self.model.spec.max_positions
+        if max_seq_len is not None:
+            if not 0 < max_seq_len <= limit:
+                raise ValueError(f"max_seq_len {max_seq_len} is outside 1..={limit} (the model's limit)")
+            limit = max_seq_len
+        scheduler = Scheduler(SchedulerConfig(
+            num_pages=self.cache.num_pages, page_size=self.page_size, max_seq_len=limit,
+            max_batch=min(max_batch or self.cache.max_requests, self.cache.max_requests), max_batch_tokens=max_batch_tokens,
+            prefill_chunk_busy=prefill_chunk_busy, eos_token_ids=tuple(self.defaults.eos_token_ids)))
+        for index, (prompt, params) in enumerate(zip(prompts, per_prompt)):
+            scheduler.enqueue(Request(index, prompt, params.validated()))
+        outputs: list[list[int]] = [[] for _ in prompts]
+        reasons: list[Optional[str]] = [None] * len(prompts)
+        params_of = {index: request.params for index, request in enumerate(scheduler.waiting)}
+
+        def handle(events):
+            for event in events:
+                if event.kind == "token":
+                    outputs[event.request].append(event.token)
+                    if on_token is not None:
+                        on_token(event.request, event.token)
+                else:
+                    reasons[event.request] = event.reason
+
+        while True:
+            plan = scheduler.next_plan()
+            handle(scheduler.take_events())
+            if plan is None:
+                if scheduler.idle:
+                    break
+                raise RuntimeError("the scheduler has requests but plans nothing")
+            entries, options = [], []
+            for row in plan.rows:
+                if not self.cache.has(row.request):
+                    self.cache.add_request(row.request)
+                entries.append(StepEntry(row.request, row.tokens, [len(row.tokens) - 1] if row.sample else []))
+                if row.sample:
+                    options.extend(pack_options(params_of[row.request], row.sampled_before, self.cache.slot(row.request)))
+            try:
+                logits = self.runner.step(entries, {"sampling_options": (options, (len(options) // 8, 8))} if options else None)
+            except Exception as error:  # the step's requests fail, the others go on
+                handle(scheduler.fail(plan, f"{type(error).__name__}: {error}"))
+                self._free_released(scheduler)
+                if not isinstance(error, (OutOfPages, BadStep)):
+                    raise
+                continue
+            sampled = {}
+            if logits is not None:
+                tokens = self.sampler.sample(logits, self.runner.last_context.extra["sampling_options"])
+                host = self._token_staging[: tokens.numel()]
+                host.copy_(tokens, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                chosen = host.tolist()
+                sampled = {row.request: chosen[i] for i, row in enumerate(r for r in plan.rows if r.sample)}
+            handle(scheduler.complete(plan, sampled))
+            self._free_released(scheduler)
+        self.check()
+        return (outputs, reasons) if return_reasons else outputs
+
+    def _free_released(self, scheduler) -> None:
+        for request in scheduler.take_released():
+            if self.cache.has(request):
+                self.cache.free(request)
 
     def check(self) -> None:
         """Wait for the device and raise if a kernel flagged a problem."""

@@ -56,7 +56,7 @@ class ModelRunner:
                 raise BadStep(f"request {entry.request!r} would reach position {length + count}, the model's limit is {limit}")
 
     # ------------------------------------------------------------------ the batch on the device
-    def _context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _context(self, entries: Sequence[StepEntry], extra_arrays=None) -> StepContext:
         rows: list[Row] = []
         token_ids: list[int] = []
         positions: list[int] = []
@@ -89,6 +89,8 @@ class ModelRunner:
         host = {"positions": positions, "token_row": token_row, "want": want}
         for key, plan in self.planners.items():
             plan(rows, packer, host)
+        for name, (values, shape) in (extra_arrays or {}).items():
+            packer.add(name, values, shape)
         arrays = packer.finish()
         extra = {k: v for k, v in arrays.items() if k not in ("token_ids", "positions", "token_row", "row_start", "slots", "want")
                  and not k.startswith("table")}
@@ -98,9 +100,11 @@ class ModelRunner:
                            slots=arrays["slots"], extra=extra, host=host)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], extra_arrays=None) -> Optional[torch.Tensor]:
         """Run the entries as one batch.  Returns float logits [wanted, vocab] on the device, in the
-        order of the entries and of each entry's ``want``, or None when nothing was wanted."""
+        order of the entries and of each entry's ``want``, or None when nothing was wanted.
+        ``extra_arrays`` ({name: (int32 values, shape)}) ride along in the step's one host-to-device
+        copy and are found in ``self.last_context.extra`` afterwards."""
         entries = list(entries)
         self._validate(entries)
         added = []
@@ -114,7 +118,8 @@ class ModelRunner:
             for request in added:
                 self.cache.free(request)
             raise
-        context = self._context(entries)
+        context = self._context(entries, extra_arrays)
+        self.last_context = context
         logits = self.model.forward(context, self.cache)
         for entry in entries:
             self.cache.advance(entry.request, len(entry.tokens))

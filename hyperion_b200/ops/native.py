@@ -37,8 +37,12 @@ def require_cuda(*tensors: torch.Tensor | None) -> None:
             raise KernelError("the kernels run on a CUDA device only; got a tensor on " + str(tensor.device))
 
 
+LAUNCHES = [0]  # launcher calls that succeeded, for reports of how much of a step is this package's own code
+
+
 def check(code: int, what: str) -> None:
     if code == 0:
+        LAUNCHES[0] += 1
         return
     if code < 0:
         raise KernelError(f"{what}: launcher refused its arguments ({_REFUSALS.get(code, code)})")
