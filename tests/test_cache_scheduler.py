@@ -1,0 +1,284 @@
+"""The cache manager's accounting and the scheduler's decisions (no GPU)."""
+from __future__ import annotations
+
+import random
+
+import pytest
+
+from hyperion_b200.cache import NO_PAGE, CacheError, CacheManager, OutOfPages, PagePool
+from hyperion_b200.engine.scheduler import Request, Scheduler, SchedulerConfig
+from hyperion_b200.parts.base import PagedKV, RequestState
+from hyperion_b200.sampling import SamplingParams
+
+
+def manager(num_pages=8, page_size=4, max_requests=3, window=0):
+    users = [(0, PagedKV(2, 16)), (1, PagedKV(2, 16)), (2, PagedKV(2, 16, window=window) if window else PagedKV(2, 16)),
+             (3, RequestState((5,)))]
+    return CacheManager(users, page_size, num_pages, max_requests)
+
+
+def test_pool_gives_pages_back_in_fifo_order_and_detects_double_free():
+    pool = PagePool(3)
+    a, b, c = pool.take(), pool.take(), pool.take()
+    assert (a, b, c) == (0, 1, 2) and pool.available == 0
+    with pytest.raises(OutOfPages):
+        pool.take()
+    pool.give_back(b)
+    pool.give_back(a)
+    with pytest.raises(CacheError):
+        pool.give_back(a)
+    assert pool.take() == b and pool.take() == a
+    pool.check()
+
+
+def test_groups_by_need():
+    m = manager(window=6)
+    assert len(m.paged) == 2 and m.paged[0].users == [0, 1] and m.paged[1].users == [2]
+    assert m.where(1) == ("paged", 0, 1) and m.where(2) == ("paged", 1, 0) and m.where(3) == ("state", 0, 0)
+    same = manager()
+    assert len(same.paged) == 1 and same.paged[0].users == [0, 1, 2]
+
+
+def test_growth_by_pages_and_release_at_the_end():
+    m = manager()
+    m.add_request("a")
+    m.extend("a", 5)
+    assert m.table(0, "a") == [0, 1]
+    m.advance("a", 5)
+    m.extend("a", 3)  # positions 5..7 fit the second page
+    assert m.table(0, "a") == [0, 1]
+    m.advance("a", 3)
+    m.extend("a", 1)
+    assert m.table(0, "a") == [0, 1, 2] and m.free_pages() == 5
+    m.advance("a", 1)
+    m.check()
+    m.free("a")
+    assert m.free_pages() == 8
+    with pytest.raises(CacheError):
+        m.free("a")
+    m.check()
+
+
+def test_extend_takes_nothing_when_it_cannot_take_all():
+    m = manager(num_pages=4)
+    m.add_request("a")
+    m.add_request("b")
+    m.extend("a", 9)  # 3 pages
+    with pytest.raises(OutOfPages):
+        m.extend("b", 8)  # needs 2, 1 free
+    assert m.table(0, "b") == [] and m.free_pages() == 1
+    m.extend_all([("a", 3), ("b", 4)])  # a needs none (positions 9..11 are in its third page), b one
+    assert m.free_pages() == 0
+    m.check()
+
+
+def test_extend_all_is_all_or_nothing():
+    m = manager(num_pages=4)
+    m.add_request("a")
+    m.add_request("b")
+    with pytest.raises(OutOfPages):
+        m.extend_all([("a", 9), ("b", 8)])  # 3 + 2 > 4
+    assert m.table(0, "a") == [] and m.table(0, "b") == [] and m.free_pages() == 4
+    m.extend_all([("a", 9), ("b", 4)])
+    assert m.free_pages() == 0
+    m.check()
+
+
+def test_request_slots_are_bounded_and_reused():
+    m = manager(max_requests=2)
+    assert m.add_request("a") == 0 and m.add_request("b") == 1
+    with pytest.raises(OutOfPages):
+        m.add_request("c")
+    with pytest.raises(CacheError):
+        m.add_request("a")
+    m.free("a")
+    assert m.add_request("c") == 0
+    m.check()
+
+
+def test_window_group_gives_pages_back_while_the_request_lives():
+    m = manager(num_pages=6, page_size=4, window=6)
+    m.add_request("a")
+    full, windowed = 0, 1
+    for step in range(20):
+        m.extend("a", 1)
+        m.advance("a", 1)
+        m.check()
+    # length 20: the next query (position 20) reads keys 15..20, so blocks 0..2 (positions 0..11) are gone
+    assert m.table(windowed, "a")[:3] == [NO_PAGE] * 3 and all(p != NO_PAGE for p in m.table(windowed, "a")[3:])
+    assert all(p != NO_PAGE for p in m.table(full, "a")) and len(m.table(full, "a")) == 5
+    assert m.paged[windowed].pool.available == 6 - 2
+    # a long portion needs pages for all its positions during the step and gives most back after it
+    m.add_request("b")
+    with pytest.raises(OutOfPages):
+        m.extend("b", 17)  # 5 pages, the full group has 1 free
+    m.free("a")
+    m.extend("b", 17)
+    m.advance("b", 17)
+    assert m.paged[windowed].pool.available == 6 - 2
+    m.check()
+
+
+def test_random_orders_never_lose_or_share_a_page():
+    rng = random.Random(7)
+    m = manager(num_pages=24, page_size=4, max_requests=5, window=10)
+    live: dict[str, int] = {}
+    counter = 0
+    for _ in range(2000):
+        action = rng.random()
+        if action < 0.2 and len(live) < 5:
+            name = f"r{counter}"
+            counter += 1
+            m.add_request(name)
+            live[name] = 0
+        elif action < 0.85 and live:
+            name = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 2, 3, 7, 13])
+            try:
+                m.extend(name, n)
+                m.advance(name, n)
+                live[name] += n
+                assert m.length(name) == live[name]
+            except OutOfPages:
+                pass
+        elif live:
+            name = rng.choice(list(live))
+            m.free(name)
+            del live[name]
+        m.check()
+    for name in list(live):
+        m.free(name)
+    m.check()
+    assert all(g.pool.available == 24 for g in m.paged)
+
+
+# ---------------------------------------------------------------------------------- scheduler
+def params(max_tokens=4, **kw):
+    return SamplingParams(temperature=0.0, max_tokens=max_tokens, **kw).validated()
+
+
+def drive(scheduler, token_of=lambda request, n: 100 + n, limit=1000):
+    """Run plans to the end with a stub that 'samples' token_of(request, count so far)."""
+    plans, events = [], []
+    counts: dict = {}
+    for _ in range(limit):
+        plan = scheduler.next_plan()
+        events += scheduler.take_events()
+        if plan is None:
+            assert scheduler.idle
+            return plans, events
+        plans.append(plan)
+        sampled = {}
+        for row in plan.rows:
+            if row.sample:
+                counts[row.request] = counts.get(row.request, 0) + 1
+                sampled[row.request] = token_of(row.request, counts[row.request])
+        events += scheduler.complete(plan, sampled)
+    raise AssertionError("the scheduler did not finish")
+
+
+def test_prompt_is_cut_under_the_token_budget_then_decoded():
+    s = Scheduler(SchedulerConfig(num_pages=100, page_size=4, max_seq_len=64, max_batch_tokens=8))
+    s.enqueue(Request("a", list(range(19)), params(3)))
+    plans, events = drive(s)
+    assert [len(p.rows[0].tokens) for p in plans] == [8, 8, 3, 1, 1]
+    assert [p.rows[0].sample for p in plans] == [False, False, True, True, True]
+    assert [e.token for e in events if e.kind == "token"] == [101, 102, 103]
+    assert events[-1].kind == "finished" and events[-1].reason == "length"
+    assert s.take_released() == ["a"]
+
+
+def test_decode_rows_ride_with_prompt_portions_limited_while_busy():
+    s = Scheduler(SchedulerConfig(num_pages=100, page_size=4, max_seq_len=128, max_batch_tokens=16, prefill_chunk_busy=5))
+    s.enqueue(Request("a", list(range(6)), params(10)))
+    first = s.next_plan()
+    s.complete(first, {"a": 50})
+    s.enqueue(Request("b", list(range(20)), params(2)))
+    plan = s.next_plan()
+    assert [(r.request, len(r.tokens), r.sample) for r in plan.rows] == [("a", 1, True), ("b", 5, False)]
+    assert plan.rows[0].tokens == [50] and plan.rows[0].sampled_before == 1
+    s.complete(plan, {"a": 51})
+    plan = s.next_plan()
+    assert [(r.request, len(r.tokens)) for r in plan.rows] == [("a", 1), ("b", 5)]
+
+
+def test_oldest_prompt_first_and_budget_shared():
+    s = Scheduler(SchedulerConfig(num_pages=100, page_size=4, max_seq_len=128, max_batch_tokens=10))
+    s.enqueue(Request("a", list(range(7)), params()))
+    s.enqueue(Request("b", list(range(7)), params()))
+    plan = s.next_plan()
+    assert [(r.request, len(r.tokens), r.sample) for r in plan.rows] == [("a", 7, True), ("b", 3, False)]
+
+
+def test_eos_ends_a_request_without_emitting_it_unless_ignored():
+    config = SchedulerConfig(num_pages=100, page_size=4, max_seq_len=64, eos_token_ids=(9,))
+    s = Scheduler(config)
+    s.enqueue(Request("a", [1, 2], params(10)))
+    _, events = drive(s, token_of=lambda r, n: 9 if n == 3 else 5)
+    assert [e.token for e in events if e.kind == "token"] == [5, 5] and events[-1].reason == "stop"
+    s = Scheduler(config)
+    s.enqueue(Request("a", [1, 2], params(4, ignore_eos=True)))
+    _, events = drive(s, token_of=lambda r, n: 9)
+    assert [e.token for e in events if e.kind == "token"] == [9, 9, 9, 9] and events[-1].reason == "length"
+
+
+def test_context_limit_ends_with_length():
+    s = Scheduler(SchedulerConfig(num_pages=100, page_size=4, max_seq_len=8))
+    s.enqueue(Request("a", [1, 2, 3, 4, 5], params(100)))
+    _, events = drive(s)
+    assert len([e for e in events if e.kind == "token"]) == 3 and events[-1].reason == "length"
+
+
+def test_admission_reserves_the_worst_case_and_waits_for_pages():
+    # 6 pages of 4 tokens; each request needs ceil((6 + 6) / 4) = 3 pages: two run, the third waits
+    s = Scheduler(SchedulerConfig(num_pages=6, page_size=4, max_seq_len=64, max_batch_tokens=64))
+    for name in "abc":
+        s.enqueue(Request(name, list(range(6)), params(6)))
+    plan = s.next_plan()
+    assert [r.request for r in plan.rows] == ["a", "b"] and s.reserved_pages == 6 and len(s.waiting) == 1
+    plans, events = [plan], []
+    events += s.complete(plan, {"a": 1, "b": 1})
+    more, later = drive(s)
+    started = next(i for i, p in enumerate(more) if any(r.request == "c" for r in p.rows))
+    finished_before = [e.request for e in events + later if e.kind == "finished"]
+    assert set(finished_before) == {"a", "b", "c"}
+    # c started only after a or b had finished
+    assert all(all(r.request != "c" for r in p.rows) for p in more[:started])
+    assert s.idle
+
+
+def test_a_request_that_can_never_fit_fails_at_once_and_others_go_on():
+    s = Scheduler(SchedulerConfig(num_pages=4, page_size=4, max_seq_len=64))
+    s.enqueue(Request("big", list(range(30)), params(4)))
+    s.enqueue(Request("empty", [], params(4)))
+    s.enqueue(Request("ok", [1, 2, 3], params(2)))
+    plans, events = drive(s)
+    failed = {e.request: e.reason for e in events if e.kind == "failed"}
+    assert "needs 9 pages, the pool has 4" in failed["big"] and "empty" in failed
+    assert [e.token for e in events if e.kind == "token" and e.request == "ok"] == [101, 102]
+
+
+def test_cancel_and_fail_release_only_their_requests():
+    s = Scheduler(SchedulerConfig(num_pages=100, page_size=4, max_seq_len=64))
+    s.enqueue(Request("a", [1, 2, 3], params(5)))
+    s.enqueue(Request("b", [4, 5], params(5)))
+    plan = s.next_plan()
+    s.complete(plan, {"a": 7, "b": 8})
+    assert s.cancel("a") and not s.cancel("zzz")
+    assert s.take_released() == ["a"]
+    plan = s.next_plan()
+    assert [r.request for r in plan.rows] == ["b"]
+    events = s.fail(plan, "device error")
+    assert [(e.request, e.kind) for e in events if e.kind == "failed"] == [("b", "failed")]
+    assert s.take_released() == ["b"] and s.idle
+
+
+def test_same_trace_gives_the_same_plans():
+    def run():
+        s = Scheduler(SchedulerConfig(num_pages=40, page_size=4, max_seq_len=64, max_batch_tokens=12, prefill_chunk_busy=4, max_batch=3))
+        for i, n in enumerate([9, 17, 3, 25, 6]):
+            s.enqueue(Request(i, list(range(n)), params(3 + i)))
+        plans, _ = drive(s)
+        return [[(r.request, tuple(r.tokens), r.sample, r.sampled_before) for r in p.rows] for p in plans]
+
+    assert run() == run()

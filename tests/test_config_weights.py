@@ -1,0 +1,187 @@
+"""Configuration reading, the architecture registry, safetensors reading and weight errors (no GPU)."""
+from __future__ import annotations
+
+import json
+import struct
+
+import pytest
+import torch
+
+from helpers import TINY_A, TINY_B
+
+from hyperion_b200.config import ConfigError, Qwen2Config, read_generation_defaults
+from hyperion_b200.models import DecoderModel, architecture_of, get_architecture, read_model_config
+from hyperion_b200.weights import SafetensorsError, WeightsError, check_tensors, read_all, read_header, read_model_index, write_file, write_model_folder
+
+QWEN25_7B = {
+    "architectures": ["Qwen2ForCausalLM"], "hidden_act": "silu", "hidden_size": 3584, "intermediate_size": 18944,
+    "max_position_embeddings": 32768, "max_window_layers": 28, "model_type": "qwen2", "num_attention_heads": 28,
+    "num_hidden_layers": 28, "num_key_value_heads": 4, "rms_norm_eps": 1e-06, "rope_theta": 1000000.0, "sliding_window": 131072,
+    "tie_word_embeddings": False, "use_sliding_window": False, "vocab_size": 152064, "eos_token_id": 151645,
+}
+
+
+def test_reads_the_7b_config_with_defaults():
+    config = Qwen2Config.from_hf_dict(QWEN25_7B)
+    assert (config.num_hidden_layers, config.hidden_size, config.head_dim, config.num_key_value_heads) == (28, 3584, 128, 4)
+    assert config.rope_theta == 1e6 and config.rms_norm_eps == 1e-6 and not config.tie_word_embeddings
+    assert config.eos_token_ids == (151645,)
+    assert config.attention_scale == pytest.approx(128 ** -0.5)
+
+
+def test_round_trip_through_config_json():
+    for config in (TINY_A, TINY_B):
+        assert Qwen2Config.from_hf_dict(config.to_hf_dict()) == config
+
+
+def test_rope_theta_from_rope_parameters():
+    document = {k: v for k, v in QWEN25_7B.items() if k != "rope_theta"}
+    document["rope_parameters"] = {"rope_theta": 12345.0, "rope_type": "default"}
+    assert Qwen2Config.from_hf_dict(document).rope_theta == 12345.0
+    document["rope_parameters"]["rope_type"] = "yarn"
+    with pytest.raises(ConfigError) as error:
+        Qwen2Config.from_hf_dict(document)
+    assert "rope_type" in str(error.value)
+
+
+@pytest.mark.parametrize("change, key", [
+    ({"rms_norm_eps": None}, "rms_norm_eps"), ({"tie_word_embeddings": None}, "tie_word_embeddings"),
+    ({"rope_scaling": {"type": "linear", "factor": 2}}, "rope_scaling"), ({"use_sliding_window": True}, "use_sliding_window"),
+    ({"hidden_act": "gelu"}, "hidden_act"), ({"partial_rotary_factor": 0.5}, "partial_rotary_factor"),
+    ({"num_key_value_heads": 5}, "num_key_value_heads"), ({"vocab_size": 0}, "vocab_size"), ({"num_hidden_layers": True}, "num_hidden_layers"),
+    ({"architectures": ["LlamaForCausalLM"]}, "architectures"), ({"query_pre_attn_scalar": 64}, "query_pre_attn_scalar"),
+    ({"rope_theta": -1}, "rope_theta"),
+])
+def test_refusals_name_the_key(change, key):
+    document = dict(QWEN25_7B)
+    document.update(change)
+    document = {k: v for k, v in document.items() if v is not None}
+    with pytest.raises(ConfigError) as error:
+        Qwen2Config.from_hf_dict(document)
+    assert error.value.key == key
+
+
+def test_registry_picks_the_model_by_architecture_name(tmp_path):
+    assert architecture_of(QWEN25_7B).name == "Qwen2ForCausalLM"
+    with pytest.raises(ConfigError):
+        architecture_of({"architectures": ["NoSuchModel"]})
+    with pytest.raises(KeyError):
+        get_architecture("NoSuchModel")
+    folder = write_model_folder(tmp_path / "m", "Qwen2ForCausalLM", TINY_A, seed=0)
+    architecture, config = read_model_config(folder)
+    assert config == TINY_A
+    spec = architecture.build_spec(config)
+    assert len(spec.layers) == 2 and [run.layer for run in spec.schedule] == [0, 1]
+    assert spec.layers[0].mixer.params["heads"] == 4 and spec.layers[1].feed_forward.params["intermediate_size"] == 176
+
+
+def test_generation_defaults_merge_eos_ids(tmp_path):
+    folder = tmp_path / "g"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps({**QWEN25_7B, "eos_token_id": 7}))
+    (folder / "generation_config.json").write_text(json.dumps({"eos_token_id": [7, 9], "temperature": 0.7, "top_k": 20, "top_p": 0.8,
+                                                                 "repetition_penalty": 1.05}))
+    defaults = read_generation_defaults(folder)
+    assert defaults.eos_token_ids == (7, 9) and defaults.temperature == 0.7 and defaults.top_k == 20
+    (folder / "generation_config.json").write_text(json.dumps({"temperature": -1}))
+    with pytest.raises(ConfigError):
+        read_generation_defaults(folder)
+
+
+def test_random_folder_has_every_tensor_in_bfloat16(tmp_path):
+    folder = write_model_folder(tmp_path / "b", "Qwen2ForCausalLM", TINY_B, seed=1)
+    tensors = read_all(folder)
+    assert "lm_head.weight" in tensors and tensors["lm_head.weight"].shape == (523, 192)
+    assert all(t.dtype == torch.bfloat16 for t in tensors.values())
+    assert tensors["model.layers.2.self_attn.k_proj.bias"].shape == (32,)
+    norm = tensors["model.norm.weight"].float()
+    assert abs(norm.mean() - 1.0) < 0.02 and norm.std() > 0.005  # 1 + N(0, 0.02)
+    again = read_all(write_model_folder(tmp_path / "b2", "Qwen2ForCausalLM", TINY_B, seed=1))
+    assert all(torch.equal(tensors[n], again[n]) for n in tensors)
+    other = read_all(write_model_folder(tmp_path / "b3", "Qwen2ForCausalLM", TINY_B, seed=2))
+    assert not torch.equal(tensors["lm_head.weight"], other["lm_head.weight"])
+    tied = read_all(write_model_folder(tmp_path / "a", "Qwen2ForCausalLM", TINY_A, seed=0))
+    assert "lm_head.weight" not in tied
+
+
+def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
+    folder = write_model_folder(tmp_path / "m", "Qwen2ForCausalLM", TINY_A, seed=0)
+    tensors = read_all(folder)
+    del tensors["model.layers.1.mlp.up_proj.weight"]
+    del tensors["model.norm.weight"]
+    tensors["model.layers.0.self_attn.q_norm.weight"] = torch.zeros(16, dtype=torch.bfloat16)
+    tensors["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(64, 65, dtype=torch.bfloat16)
+    tensors["model.layers.0.input_layernorm.weight"] = torch.zeros(64, dtype=torch.int32)
+    (folder / "model.safetensors").unlink()
+    write_file(folder / "model.safetensors", tensors)
+    architecture, config = read_model_config(folder)
+    model = DecoderModel(architecture.build_spec(config), torch.float32, torch.device("meta"))
+    with pytest.raises(WeightsError) as error:
+        check_tensors(read_model_index(folder), model.expected_tensors(), model.spec.tolerated)
+    text = str(error.value)
+    assert error.value.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
+    assert error.value.unexpected == ["model.layers.0.self_attn.q_norm.weight"]
+    assert "model.layers.0.self_attn.q_proj.weight is [64, 65], expected [64, 64]" in text
+    assert "model.layers.0.input_layernorm.weight is torch.int32" in text
+    assert "missing tensors (2)" in text and "unexpected tensors (1)" in text
+
+
+def test_tied_checkpoint_may_still_carry_the_head(tmp_path):
+    folder = write_model_folder(tmp_path / "m", "Qwen2ForCausalLM", TINY_A, seed=0)
+    tensors = read_all(folder)
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    (folder / "model.safetensors").unlink()
+    write_file(folder / "model.safetensors", tensors)
+    architecture, config = read_model_config(folder)
+    model = DecoderModel(architecture.build_spec(config), torch.float32, torch.device("meta"))
+    check_tensors(read_model_index(folder), model.expected_tensors(), model.spec.tolerated)
+
+
+def _raw_file(path, header: dict, payload: bytes):
+    text = json.dumps(header).encode()
+    path.write_bytes(struct.pack("<Q", len(text)) + text + payload)
+
+
+def test_malformed_safetensors_are_refused(tmp_path):
+    path = tmp_path / "x.safetensors"
+    path.write_bytes(b"\x01\x02")
+    with pytest.raises(SafetensorsError):
+        read_header(path)
+    path.write_bytes(struct.pack("<Q", 1 << 40) + b"{}")
+    with pytest.raises(SafetensorsError):
+        read_header(path)
+    _raw_file(path, {"a": {"dtype": "BF16", "shape": [4], "data_offsets": [0, 6]}}, b"\0" * 8)
+    with pytest.raises(SafetensorsError, match="needs 8"):
+        read_header(path)
+    _raw_file(path, {"a": {"dtype": "BF16", "shape": [4], "data_offsets": [0, 8]}}, b"\0" * 4)
+    with pytest.raises(SafetensorsError, match="outside the payload"):
+        read_header(path)
+    _raw_file(path, {"a": {"dtype": "BF16", "shape": [2], "data_offsets": [0, 4]}, "b": {"dtype": "BF16", "shape": [2], "data_offsets": [2, 6]}}, b"\0" * 8)
+    with pytest.raises(SafetensorsError, match="overlap"):
+        read_header(path)
+    _raw_file(path, {"a": {"dtype": "Q4", "shape": [2], "data_offsets": [0, 4]}}, b"\0" * 4)
+    with pytest.raises(SafetensorsError, match="unsupported dtype"):
+        read_header(path)
+    _raw_file(path, {"__metadata__": {"format": "pt"}, "a": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]}}, struct.pack("<f", 2.5))
+    assert read_header(path)["a"].shape == (1,)
+
+
+def test_sharded_folders_and_their_errors(tmp_path):
+    folder = tmp_path / "s"
+    folder.mkdir()
+    write_file(folder / "p1.safetensors", {"a": torch.ones(3), "b": torch.zeros(2, 2)})
+    write_file(folder / "p2.safetensors", {"c": torch.arange(4, dtype=torch.int32)})
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"a": "p1.safetensors", "b": "p1.safetensors", "c": "p2.safetensors"}}))
+    assert set(read_model_index(folder)) == {"a", "b", "c"}
+    assert torch.equal(read_all(folder)["c"], torch.arange(4, dtype=torch.int32))
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"a": "p1.safetensors", "c": "p2.safetensors"}}))
+    with pytest.raises(SafetensorsError, match="beyond the index"):
+        read_model_index(folder)
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"a": "../p1.safetensors"}}))
+    with pytest.raises(SafetensorsError, match="bare file name"):
+        read_model_index(folder)
+    write_file(folder / "model.safetensors", {"a": torch.ones(1)})
+    with pytest.raises(SafetensorsError, match="both"):
+        read_model_index(folder)
+    with pytest.raises(FileNotFoundError):
+        read_model_index(tmp_path / "nothing")
