@@ -1,0 +1,83 @@
+"""Tensor-core attention over the paged bfloat16 cache: planning on the host and the two launches.
+
+A step's rows are divided by length: rows of more than ``TOKEN_SHAPE_MAX`` tokens are cut into tiles
+of ``tile_tokens`` tokens (times the heads of one key/value group = up to 64 rows of a block); the
+tokens of shorter rows (decoded tokens, very short portions) each get blocks of their own, with the
+keys split over several blocks when the batch alone would not fill the GPU.
+"""
+from __future__ import annotations
+
+import torch
+
+from .basic import status_word
+from .native import KernelError, check, f32, i32, library, ptr, require_cuda, stream_ptr
+
+TOKEN_SHAPE_MAX = 4
+TILE_ROWS = 64
+KEY_TILE = 64
+TARGET_BLOCKS = 148 * 3
+
+
+def supported(head_dim: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+def tile_tokens(heads: int, kv_heads: int) -> int:
+    return TILE_ROWS // min(heads // kv_heads, TILE_ROWS)
+
+
+def plan(rows, tokens_per_tile: int) -> tuple[list[int], list[int]]:
+    """(tiles as flat triples [first token, count, batch row], items = flat token indices)."""
+    tiles: list[int] = []
+    items: list[int] = []
+    for index, row in enumerate(rows):
+        if row.count <= TOKEN_SHAPE_MAX:
+            items.extend(range(row.start, row.start + row.count))
+            continue
+        for first in range(0, row.count, tokens_per_tile):
+            tiles.extend((row.start + first, min(tokens_per_tile, row.count - first), index))
+    return tiles, items
+
+
+def choose_splits(n_items: int, heads: int, kv_heads: int, longest_context: int) -> int:
+    """Splits of the keys for the token shape: enough blocks to fill the GPU, at least 4 key tiles each."""
+    group = heads // kv_heads
+    blocks = n_items * kv_heads * ((group + 15) // 16)
+    key_tiles = -(-longest_context // KEY_TILE)
+    return max(1, min(-(-TARGET_BLOCKS // max(1, blocks)), key_tiles // 4, 64))
+
+
+def _common(q, out, cache, block_table, token_row, positions):
+    require_cuda(q, out, cache, block_table, token_row, positions)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or q.stride(-1) != 1 or not cache.is_contiguous():
+        raise KernelError("attention (bfloat16): queries and cache must be dense bfloat16")
+
+
+def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n_tiles, scale, window, out):
+    _common(q, out, cache, block_table, token_row, positions)
+    pages, _, kv_heads, page_size, head_dim = cache.shape
+    lib = library("attention_bf16", HB_HEAD_DIM=head_dim)
+    check(lib.hb_attention_tiles(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
+                                 i32(block_table.shape[1]), ptr(token_row), ptr(positions), ptr(tiles), i32(n_tiles), i32(heads),
+                                 i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale), i32(window or 0),
+                                 ptr(status_word(q.device)), stream_ptr()), "attention_tiles")
+
+
+def attention_tokens(q, heads, cache, block_table, token_row, positions, items, n_items, splits, scale, window, out, workspace=None):
+    _common(q, out, cache, block_table, token_row, positions)
+    pages, _, kv_heads, page_size, head_dim = cache.shape
+    lib = library("attention_bf16", HB_HEAD_DIM=head_dim)
+    if splits > 1:
+        need = n_items * heads * splits * (head_dim + 2)
+        if workspace is None:
+            workspace = torch.empty(need, dtype=torch.float32, device=q.device)
+        elif workspace.numel() < need or workspace.dtype != torch.float32:
+            raise KernelError(f"attention_tokens: workspace of {need} floats needed")
+    check(lib.hb_attention_tokens(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
+                                  i32(block_table.shape[1]), ptr(token_row), ptr(positions), ptr(items), i32(n_items), i32(splits),
+                                  ptr(workspace), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale),
+                                  i32(window or 0), ptr(status_word(q.device)), stream_ptr()), "attention_tokens")
+    if splits > 1:
+        from . import native
+
+        native.LAUNCHES[0] += 1  # the merge kernel

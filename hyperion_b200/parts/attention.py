@@ -19,6 +19,7 @@ from typing import Mapping
 import torch
 
 from .. import ops
+from ..ops import attention as fast_attention
 from .base import POSITIONS, BuildContext, Mixer, PagedKV, WeightSpec, make, register_mixer
 from .spec import PartSpec
 
@@ -46,7 +47,9 @@ class GroupedQueryAttention(Mixer):
         self.position = make(POSITIONS, p["position"], build) if p.get("position") is not None else None
         self.q_width = self.heads * self.head_dim
         self.kv_width = self.kv_heads * self.head_dim
-        self.fast = self.dtype == torch.bfloat16 and self.head_dim % 16 == 0 and self.head_dim <= 256
+        # the tensor-core kernels take bfloat16 and head sizes in steps of 16; other head sizes use the generic kernel
+        self.fast = self.dtype == torch.bfloat16 and fast_attention.supported(self.head_dim)
+        self.tile_tokens = fast_attention.tile_tokens(self.heads, self.kv_heads)
 
     def weights(self) -> dict[str, WeightSpec]:
         names = {"q_proj.weight": WeightSpec((self.q_width, self.hidden)), "o_proj.weight": WeightSpec((self.hidden, self.q_width))}
@@ -72,7 +75,8 @@ class GroupedQueryAttention(Mixer):
         return None if self.shares_kv else PagedKV(self.kv_heads, self.head_dim, self.window)
 
     def kernel_modules(self):
-        modules = [("elementwise", {}), ("attention_generic", {})]
+        modules = [("elementwise", {})]
+        modules.append(("attention_bf16", {"HB_HEAD_DIM": self.head_dim}) if self.fast else ("attention_generic", {}))
         if self.dtype == torch.float32:
             modules.append(("sgemm_f32", {}))
         if self.position is not None:
@@ -88,8 +92,45 @@ class GroupedQueryAttention(Mixer):
             self.position.apply_(qkv, rotated, self.head_dim, step.positions)
         if own_cache and not self.shares_kv:
             ops.kv_store(qkv, self.q_width, self.q_width + self.kv_width, cache.kv, cache.block_table, step.token_row, step.positions)
-        attn = ops.attention_generic(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions, self.scale, self.window)
+        if self.fast:
+            attn = self._attend_fast(qkv, step, cache)
+        else:
+            attn = ops.attention_generic(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions, self.scale, self.window)
         return ops.linear(attn, self.w_o, None, self.dtype)
+
+    # ------------------------------------------------------------------ the tensor-core path
+    def step_plans(self):
+        """Per-step metadata: the rows cut into tiles and single tokens (shared by all layers with the same tile size)."""
+        if not self.fast:
+            return {}
+        tokens_per_tile = self.tile_tokens
+
+        def plan(rows, packer, host):
+            tiles, items = fast_attention.plan(rows, tokens_per_tile)
+            host[f"attn_tiles_{tokens_per_tile}"] = len(tiles) // 3
+            host["attn_items"] = len(items)
+            if tiles:
+                packer.add(f"attn_tiles_{tokens_per_tile}", tiles)
+            if items and "attn_items" not in [name for name, *_ in packer._items]:
+                packer.add("attn_items", items)
+
+        return {("attention_plan", tokens_per_tile): plan}
+
+    def _attend_fast(self, qkv, step, cache):
+        out = torch.empty((step.n_tokens, self.q_width), dtype=self.dtype, device=qkv.device)
+        key = f"attn_tiles_{self.tile_tokens}"
+        n_tiles, n_items = step.host.get(key, 0), step.host.get("attn_items", 0)
+        if n_tiles:
+            fast_attention.attention_tiles(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions,
+                                           step.extra[key], n_tiles, self.scale, self.window, out)
+        if n_items:
+            longest = max(row.position + row.count for row in step.rows if row.count <= fast_attention.TOKEN_SHAPE_MAX)
+            if self.window:
+                longest = min(longest, self.window + fast_attention.KEY_TILE)
+            splits = fast_attention.choose_splits(n_items, self.heads, self.kv_heads, longest)
+            fast_attention.attention_tokens(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions,
+                                            step.extra["attn_items"], n_items, splits, self.scale, self.window, out)
+        return out
 
 
 register_mixer("gqa_attention", GroupedQueryAttention)
