@@ -1,0 +1,344 @@
+"""Each kernel alone against a plain float64 computation, at sizes other than the tiny models'."""
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def ops():
+    from hyperion_b200 import ops as module
+
+    return module
+
+
+def rnd(*shape, seed=0, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def test_embedding_copies_rows_exactly():
+    for dtype in (torch.float32, torch.bfloat16):
+        table = rnd(301, 72, seed=1, dtype=dtype)
+        ids = torch.tensor([5, 300, 0, 17, 5], dtype=torch.int32)
+        out = ops().embedding(table.to(DEV), ids.to(DEV))
+        assert out.dtype == torch.float32 and torch.equal(out.cpu(), table[ids.long()].float())
+
+
+def test_embedding_flags_a_bad_token_instead_of_faulting():
+    from hyperion_b200.ops import KernelError, raise_on_status
+
+    table = rnd(10, 8).to(DEV)
+    ops().embedding(table, torch.tensor([3, 10], dtype=torch.int32, device=DEV))
+    with pytest.raises(KernelError, match="token id"):
+        raise_on_status(table.device)
+    raise_on_status(table.device)  # cleared
+
+
+@pytest.mark.parametrize("hidden, eps", [(72, 1e-6), (1000, 1e-5), (4104, 1e-6)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(hidden, eps, out_dtype):
+    h = rnd(7, hidden, seed=2, scale=3.0)
+    delta = rnd(7, hidden, seed=3).to(out_dtype)
+    w = 1 + rnd(hidden, seed=4, scale=0.1)
+    hd = h.to(DEV).clone()
+    x = ops().add_rmsnorm(hd, delta.to(DEV), w.to(DEV), eps, out_dtype)
+    total = h.double() + delta.double()
+    want = plain.rmsnorm(total, w.double(), eps)
+    assert torch.allclose(hd.cpu().double(), total, rtol=0, atol=1e-6)  # the residual stream holds the float sum
+    tolerance = 2e-6 if out_dtype == torch.float32 else 2 ** -8
+    assert (x.cpu().double() - want).abs().max() <= tolerance * want.abs().max()
+    # without delta, and gathered rows that leave h alone
+    before = hd.clone()
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    y = ops().add_rmsnorm(hd, delta.to(DEV), w.to(DEV), eps, out_dtype, rows)
+    assert torch.equal(hd, before)
+    want_rows = plain.rmsnorm(before.cpu().double()[rows.cpu().long()] + delta.double()[rows.cpu().long()], w.double(), eps)
+    assert (y.cpu().double() - want_rows).abs().max() <= tolerance * want_rows.abs().max()
+    z = ops().add_rmsnorm(hd, None, w.to(DEV), eps, out_dtype)
+    want_z = plain.rmsnorm(before.cpu().double(), w.double(), eps)
+    assert (z.cpu().double() - want_z).abs().max() <= tolerance * want_z.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(dtype):
+    gate_up = rnd(5, 2 * 330, seed=5, scale=2.0, dtype=dtype)
+    out = ops().swiglu(gate_up.to(DEV))
+    g, u = gate_up.double()[:, :330], gate_up.double()[:, 330:]
+    want = g / (1 + torch.exp(-g)) * u
+    tolerance = 1e-6 if dtype == torch.float32 else 2 ** -8
+    assert (out.cpu().double() - want).abs().max() <= tolerance * want.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("head_dim, theta", [(48, 1e4), (80, 1e6)])
+def test_rope_rotates_only_the_leading_heads(dtype, head_dim, theta):
+    from hyperion_b200.parts.rope import rotary_table
+
+    heads, extra = 5, 24
+    positions = torch.tensor([0, 1, 999, 37, 4095], dtype=torch.int32)
+    x = rnd(5, heads * head_dim + extra, seed=6, dtype=dtype)
+    table = rotary_table(head_dim, theta, 4096)
+    xd = x.to(DEV).clone()
+    ops().rope_(xd, heads, head_dim, positions.to(DEV), table.to(DEV))
+    cos, sin = plain.rope_tables(positions, head_dim, theta)
+    want = plain.rope(x.double()[:, : heads * head_dim].view(5, heads, head_dim), cos, sin).reshape(5, -1)
+    tolerance = 1e-6 if dtype == torch.float32 else 2 ** -8
+    got = xd.cpu().double()
+    assert (got[:, : heads * head_dim] - want).abs().max() <= tolerance * want.abs().max()
+    assert torch.equal(xd.cpu()[:, heads * head_dim:], x[:, heads * head_dim:])  # the rest of the row is untouched
+
+
+def test_rope_flags_a_position_beyond_the_table():
+    from hyperion_b200.ops import KernelError, raise_on_status
+    from hyperion_b200.parts.rope import rotary_table
+
+    x = rnd(2, 32).to(DEV)
+    ops().rope_(x, 1, 32, torch.tensor([0, 64], dtype=torch.int32, device=DEV), rotary_table(32, 1e4, 64).to(DEV))
+    with pytest.raises(KernelError, match="position"):
+        raise_on_status(x.device)
+
+
+@pytest.mark.parametrize("m", [1, 3, 64, 130])
+def test_sgemm_f32_matches_float64_and_does_not_depend_on_the_batch(m):
+    k, n = 331, 203
+    x, w, b = rnd(130, k, seed=7), rnd(n, k, seed=8), rnd(n, seed=9)
+    full = ops().sgemm_f32(x.to(DEV), w.to(DEV), b.to(DEV)).cpu()
+    want = x.double() @ w.double().t() + b.double()
+    assert (full.double() - want).abs().max() <= 2e-6 * want.abs().max() * math.sqrt(k)
+    part = ops().sgemm_f32(x[:m].to(DEV), w.to(DEV), b.to(DEV)).cpu()
+    assert torch.equal(part, full[:m])  # bit for bit: a row's result does not depend on its neighbours
+    strided = x.to(DEV)[:, : k - 3]
+    got = ops().sgemm_f32(strided, w[:, : k - 3].contiguous().to(DEV)).cpu()
+    assert torch.allclose(got.double(), x.double()[:, : k - 3] @ w.double()[:, : k - 3].t(), atol=1e-4)
+
+
+def paged_case(kv_heads, head_dim, page_size, contexts, dtype, seed=0, pages_extra=5):
+    """Random keys/values for requests of the given context lengths scattered over shuffled pages."""
+    g = torch.Generator().manual_seed(seed)
+    blocks = [-(-c // page_size) for c in contexts]
+    pages = sum(blocks) + pages_extra
+    order = torch.randperm(pages, generator=g).tolist()
+    cache = torch.full((pages, 2, kv_heads, page_size, head_dim), float("nan"), dtype=dtype)  # unowned slots hold NaN
+    width = max(blocks) + 2
+    table = torch.full((len(contexts), width), -1, dtype=torch.int32)
+    keys, values = [], []
+    for r, c in enumerate(contexts):
+        k = rnd(c, kv_heads, head_dim, seed=seed * 100 + 2 * r, dtype=dtype)
+        v = rnd(c, kv_heads, head_dim, seed=seed * 100 + 2 * r + 1, dtype=dtype)
+        keys.append(k)
+        values.append(v)
+        for b in range(blocks[r]):
+            page = order.pop()
+            table[r, b] = page
+            n = min(page_size, c - b * page_size)
+            cache[page, 0, :, :n] = k[b * page_size : b * page_size + n].transpose(0, 1)
+            cache[page, 1, :, :n] = v[b * page_size : b * page_size + n].transpose(0, 1)
+            cache[page, :, :, n:] = 0  # slots of a held page past the context are zero in the engine (never NaN keys at masked places)
+    return cache, table, keys, values
+
+
+def test_kv_store_writes_where_the_table_says_and_nowhere_else():
+    kv_heads, head_dim, page_size = 3, 16, 8
+    cache = torch.zeros(6, 2, kv_heads, page_size, head_dim)
+    table = torch.tensor([[4, 1, -1], [2, 5, 0]], dtype=torch.int32)
+    token_row = torch.tensor([0, 0, 1, 1, 1], dtype=torch.int32)
+    positions = torch.tensor([7, 8, 15, 16, 17], dtype=torch.int32)
+    width = kv_heads * head_dim
+    src = rnd(5, 10 + 2 * width, seed=11)
+    cd = cache.to(DEV)
+    ops().kv_store(src.to(DEV), 10, 10 + width, cd, table.to(DEV), token_row.to(DEV), positions.to(DEV))
+    want = cache.clone()
+    for t in range(5):
+        page = table[token_row[t], positions[t] // page_size]
+        slot = positions[t] % page_size
+        want[page, 0, :, slot] = src[t, 10 : 10 + width].view(kv_heads, head_dim)
+        want[page, 1, :, slot] = src[t, 10 + width :].view(kv_heads, head_dim)
+    assert torch.equal(cd.cpu(), want)
+
+
+def reference_attention(q, keys, values, rows, scale, window):
+    """q [T, heads, d] float64; rows: list of (request index, first position, count)."""
+    outs = []
+    at = 0
+    for request, first, count in rows:
+        k, v = keys[request].double(), values[request].double()
+        qp = torch.arange(first, first + count)
+        kp = torch.arange(k.shape[0])
+        outs.append(plain.attention(q[at : at + count], k, v, qp, kp, scale, window))
+        at += count
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("heads, kv_heads, head_dim, page_size, window", [(6, 2, 24, 8, 0), (5, 5, 40, 16, 0), (20, 2, 16, 4, 0), (4, 1, 72, 32, 37)])
+def test_attention_generic_float32(heads, kv_heads, head_dim, page_size, window):
+    contexts = [150, 9, 77]
+    cache, table, keys, values = paged_case(kv_heads, head_dim, page_size, contexts, torch.float32, seed=3)
+    rows = [(0, 150 - 20, 20), (1, 8, 1), (2, 0, 77)]
+    tokens = sum(r[2] for r in rows)
+    q = rnd(tokens, heads * head_dim + 8, seed=12)
+    token_row = torch.tensor([i for i, r in enumerate(rows) for _ in range(r[2])], dtype=torch.int32)
+    positions = torch.tensor([p for r in rows for p in range(r[1], r[1] + r[2])], dtype=torch.int32)
+    scale = head_dim ** -0.5
+    out = ops().attention_generic(q.to(DEV), heads, cache.to(DEV), table.to(DEV), token_row.to(DEV), positions.to(DEV), scale, window)
+    want = reference_attention(q[:, : heads * head_dim].double().view(tokens, heads, head_dim), keys, values, rows, scale, window)
+    assert (out.cpu().double().view(tokens, heads, head_dim) - want).abs().max() <= 5e-6 * want.abs().max()
+    # one token alone gives the same bits as inside the batch
+    pick = 25
+    alone = ops().attention_generic(q[pick : pick + 1].to(DEV), heads, cache.to(DEV), table.to(DEV), token_row[pick : pick + 1].to(DEV),
+                                    positions[pick : pick + 1].to(DEV), scale, window)
+    assert torch.equal(alone.cpu()[0], out.cpu()[pick])
+
+
+def run_fast_attention(q, heads, cache, table, rows, scale, window):
+    from hyperion_b200.engine.batch import Row
+    from hyperion_b200.ops import attention as fast
+
+    kv_heads = cache.shape[2]
+    step_rows, start = [], 0
+    for i, (request, first, count) in enumerate(rows):
+        step_rows.append(Row(request, start, count, first, i))
+        start += count
+    tiles, items = fast.plan(step_rows, fast.tile_tokens(heads, kv_heads))
+    token_row = torch.tensor([i for i, r in enumerate(rows) for _ in range(r[2])], dtype=torch.int32, device=DEV)
+    positions = torch.tensor([p for r in rows for p in range(r[1], r[1] + r[2])], dtype=torch.int32, device=DEV)
+    batch_table = table[[r[0] for r in rows]].contiguous().to(DEV)
+    out = torch.full((q.shape[0], heads * cache.shape[-1]), float("nan"), dtype=torch.bfloat16, device=DEV)
+    qd, cd = q.to(DEV), cache.to(DEV)
+    if tiles:
+        fast.attention_tiles(qd, heads, cd, batch_table, token_row, positions, torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                             len(tiles) // 3, scale, window, out)
+    outs = {}
+    if items:
+        items_dev = torch.tensor(items, dtype=torch.int32, device=DEV)
+        for splits in (1, 3):
+            o = out.clone()
+            fast.attention_tokens(qd, heads, cd, batch_table, token_row, positions, items_dev, len(items), splits, scale, window, o)
+            outs[splits] = o
+    else:
+        outs[1] = out
+    return outs
+
+
+@pytest.mark.parametrize("heads, kv_heads, head_dim, page_size, window", [(14, 2, 64, 16, 0), (6, 1, 32, 8, 0), (8, 8, 80, 16, 0),
+                                                                          (20, 1, 16, 4, 0), (4, 2, 128, 32, 100), (3, 1, 48, 16, 70)])
+def test_attention_bf16_tiles_and_tokens(heads, kv_heads, head_dim, page_size, window):
+    from hyperion_b200.ops import raise_on_status
+
+    contexts = [300, 9, 130, 64, 513]
+    cache, table, keys, values = paged_case(kv_heads, head_dim, page_size, contexts, torch.bfloat16, seed=5)
+    rows = [(0, 300 - 70, 70), (1, 8, 1), (2, 0, 130), (3, 62, 2), (4, 512, 1), (0, 0, 0)][:5]
+    tokens = sum(r[2] for r in rows)
+    q = rnd(tokens, (heads + 2 * kv_heads) * head_dim, seed=13, dtype=torch.bfloat16)
+    scale = head_dim ** -0.5
+    outs = run_fast_attention(q, heads, cache, table, rows, scale, window)
+    raise_on_status(torch.device(DEV))
+    want = reference_attention(q[:, : heads * head_dim].double().view(tokens, heads, head_dim), keys, values, rows, scale, window)
+    for splits, out in outs.items():
+        got = out.cpu().double().view(tokens, heads, head_dim)
+        assert torch.isfinite(got).all(), f"splits {splits}: not finite"
+        assert (got - want).abs().max() <= 2 ** -7 * want.abs().max(), f"splits {splits}"
+
+
+def test_attention_bf16_finds_one_far_key_among_hundreds():
+    """Random scores would average a lost key away: make one distant key dominate every query."""
+    heads, kv_heads, head_dim, page_size = 8, 2, 64, 16
+    contexts = [700, 700]
+    cache, table, keys, values = paged_case(kv_heads, head_dim, page_size, contexts, torch.bfloat16, seed=6)
+    for far in (3, 64 * 5 + 63, 699 - 64):  # near the start, at a tile's edge, in the last full tile
+        k = [x.clone() for x in keys]
+        direction = rnd(head_dim, seed=far).to(torch.bfloat16)
+        c = cache.clone()
+        for r in range(2):
+            k[r][far] = direction * 4
+            c[table[r, far // page_size], 0, :, far % page_size] = direction * 4
+        rows = [(0, 650, 50), (1, 699, 1)]
+        tokens = 51
+        q = (direction.float() * 4).repeat(tokens, heads + 2 * kv_heads).to(torch.bfloat16)
+        outs = run_fast_attention(q, heads, c, table, rows, head_dim ** -0.5, 0)
+        want = reference_attention(q[:, : heads * head_dim].double().view(tokens, heads, head_dim), k, values, rows, head_dim ** -0.5, None)
+        for out in outs.values():
+            got = out.cpu().double().view(tokens, heads, head_dim)
+            assert (got - want).abs().max() <= 2 ** -7 * want.abs().max()
+            # the output is essentially the far key's value
+            assert (got[0, 0] - values[0][far, 0].double()).abs().max() < 0.05
+
+
+@pytest.mark.parametrize("vocab", [523, 152064])
+def test_sampler_greedy_ties_and_nan(vocab):
+    from hyperion_b200.sampling import GREEDY, Sampler, pack_options
+
+    logits = rnd(4, vocab, seed=14)
+    logits[0, [7, 300]] = 9.0  # a tie: the lower index wins
+    logits[1, 5] = float("nan")
+    logits[1, 400] = 8.0
+    logits[2] = float("-inf")
+    logits[2, vocab - 1] = -5.0
+    sampler = Sampler(vocab, torch.device(DEV))
+    options = torch.tensor([pack_options(GREEDY, 0, -1) for _ in range(4)], dtype=torch.int32, device=DEV)
+    got = sampler.sample(logits.to(DEV), options).cpu().tolist()
+    assert got[:3] == [7, 400, vocab - 1] and got[3] == int(torch.argmax(logits[3]))
+
+
+@pytest.mark.parametrize("vocab, params", [
+    (523, dict(temperature=0.8)), (523, dict(temperature=1.3, top_k=40)), (523, dict(temperature=0.7, top_p=0.9)),
+    (523, dict(temperature=1.0, top_k=50, top_p=0.5, repetition_penalty=1.3)), (152064, dict(temperature=0.8, top_k=50, top_p=0.95)),
+    (152064, dict(temperature=1.0)), (1000, dict(temperature=1.0, top_k=1)),
+])
+def test_sampler_matches_the_host_rule(vocab, params):
+    """The device token must be the host reference's token, or the draw must lie within float rounding
+    of the boundary between the two (the device sums in float, the reference in double)."""
+    import numpy as np
+
+    from hyperion_b200.sampling import Sampler, SamplingParams, pack_options, reference_sample
+
+    rows = 48
+    logits = rnd(rows, vocab, seed=15, scale=3.0)
+    logits[:, 11] = logits[:, 12]  # ties inside the candidate set
+    sampling = SamplingParams(seed=1234567890123, **params).validated()
+    generated = [3, 11, 77, 500]
+    seen = torch.zeros(rows, (vocab + 31) // 32, dtype=torch.int32)
+    for token in generated:
+        seen[:, token // 32] |= 1 << (token % 32)
+    sampler = Sampler(vocab, torch.device(DEV), seen=seen.to(DEV))
+    options = torch.tensor([pack_options(sampling, step, step) for step in range(rows)], dtype=torch.int32, device=DEV)
+    got = sampler.sample(logits.to(DEV), options).cpu().tolist()
+    exact = 0
+    for row in range(rows):
+        token, info = reference_sample(logits[row].numpy(), sampling, row, generated)
+        if got[row] == token:
+            exact += 1
+            continue
+        kept = info["kept"].tolist()
+        assert got[row] in kept, f"row {row}: device token {got[row]} is outside the kept set"
+        j = kept.index(got[row])
+        lower = info["cdf"][j - 1] if j else 0.0
+        assert lower - 1e-5 <= info["u"] <= info["cdf"][j] + 1e-5, f"row {row}: draw {info['u']} does not select token {got[row]}"
+    assert exact >= rows - 2
+    # the chosen tokens are recorded in the per-request bitmaps
+    bitmap = sampler.seen.cpu()
+    assert all((int(bitmap[row, got[row] // 32]) >> (got[row] % 32)) & 1 for row in range(rows))
+
+
+def test_sampler_frequencies_follow_the_softmax():
+    import numpy as np
+
+    from hyperion_b200.sampling import Sampler, SamplingParams, pack_options
+
+    vocab, draws = 16, 4000
+    logits = torch.tensor([[2.0, 1.0, 0.5, 0.0, -1.0] + [-3.0] * 11])
+    sampling = SamplingParams(temperature=1.0, seed=99).validated()
+    sampler = Sampler(vocab, torch.device(DEV))
+    options = torch.tensor([pack_options(sampling, step, -1) for step in range(draws)], dtype=torch.int32, device=DEV)
+    got = sampler.sample(logits.expand(draws, vocab).contiguous().to(DEV), options).cpu().numpy()
+    observed = np.bincount(got, minlength=vocab)
+    expected = torch.softmax(logits[0].double(), 0).numpy() * draws
+    chi2 = float(((observed - expected) ** 2 / expected).sum())
+    assert chi2 < 45.0  # 15 degrees of freedom: p = 0.0001 at 42.6... a wrong sampler lands in the hundreds
