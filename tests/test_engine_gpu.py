@@ -1,0 +1,202 @@
+"""The engine on the GPU beyond replay: long decoding, the first tokens of a sequence, generation
+through the Python entry point with greedy and temperature sampling, and what happens when pages
+run out."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TINY, TOLERANCE, make_folder, plain_logits, random_ids
+from plain import qwen2_plain
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("engine_models")
+    return {name: make_folder(root, name) for name in TINY}
+
+
+def engine_for(folder, dtype, **options):
+    from hyperion_b200.api import Engine
+
+    options.setdefault("page_size", 16)
+    options.setdefault("max_tokens", 2048)
+    options.setdefault("max_requests", 8)
+    return Engine.from_folder(folder, dtype=dtype, **options)
+
+
+def relative_error(got: np.ndarray, want: np.ndarray) -> float:
+    return float(np.abs(got - want).max() / np.abs(want).max())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decoding_token_by_token(folders, name, dtype):
+    from hyperion_b200.engine.batch import StepEntry
+
+    config, seed = TINY[name]
+    ids = random_ids(seed + 40, 330, config.vocab_size)
+    want = plain_logits(folders[name], ids)
+    engine = engine_for(folders[name], dtype, page_size=8 if name == "A" else 32, max_tokens=384)
+    logits = engine.step([StepEntry("r", ids[:10], [9])])
+    worst = relative_error(logits.cpu().numpy()[0], want[9])
+    for k in range(10, len(ids)):
+        logits = engine.step([StepEntry("r", [ids[k]], [0])])
+        worst = max(worst, relative_error(logits.cpu().numpy()[0], want[k]))
+    engine.check()
+    assert worst <= TOLERANCE[dtype], worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(folders, dtype):
+    from hyperion_b200.engine.batch import StepEntry
+
+    config, seed = TINY["B"]
+    ids = random_ids(77, 6, config.vocab_size)
+    want = plain_logits(folders["B"], ids)
+    engine = engine_for(folders["B"], dtype)
+    for k, token in enumerate(ids):  # positions 0, 1, 2, ... one at a time: a one-token prompt, then decoding
+        logits = engine.step([StepEntry("one", [token], [0])])
+        assert relative_error(logits.cpu().numpy()[0], want[k]) <= TOLERANCE[dtype]
+    single = engine.step([StepEntry("single", [ids[0]], [0])])  # a prompt of exactly one token
+    assert relative_error(single.cpu().numpy()[0], want[0]) <= TOLERANCE[dtype]
+    pair = engine.step([StepEntry("pair", ids[:2], [0, 1])])
+    assert relative_error(pair.cpu().numpy(), want[:2]) <= TOLERANCE[dtype]
+
+
+def test_float32_logits_are_bit_identical_however_the_work_is_cut(folders):
+    from hyperion_b200.engine.batch import StepEntry
+
+    config, _ = TINY["A"]
+    ids = random_ids(5, 90, config.vocab_size)
+    other = random_ids(6, 50, config.vocab_size)
+    engine = engine_for(folders["A"], "float32", page_size=4)
+    whole = engine.step([StepEntry("w", ids, list(range(90)))]).cpu()
+    pieces = []
+    at = 0
+    engine.step([StepEntry("noise", other[:17], [])])
+    for n in (3, 1, 40, 2, 44):
+        out = engine.step([StepEntry("p", ids[at:at + n], list(range(n))), StepEntry("noise", other[17 + at // 4: 18 + at // 4], [0])])
+        pieces.append(out.cpu()[:n])
+        at += n
+    assert torch.equal(torch.cat(pieces), whole)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_matches_the_plain_implementation(folders, name):
+    from hyperion_b200.sampling import SamplingParams
+
+    config, seed = TINY[name]
+    prompts = [random_ids(200 + i, n, config.vocab_size) for i, n in enumerate([5, 17, 31])]
+    plain_config, weights = qwen2_plain.read_model_folder(folders[name])
+    want = [qwen2_plain.greedy(plain_config, weights, prompt, 8) for prompt in prompts]
+    engine = engine_for(folders[name], "float32")
+    got = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    assert got == want
+    # bfloat16: teacher-forced on its own tokens, every choice must be the plain argmax or within the
+    # bfloat16 tolerance of it (a near tie may flip)
+    engine = engine_for(folders[name], "bfloat16")
+    got = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for prompt, tokens in zip(prompts, got):
+        logits = plain_logits(folders[name], prompt + tokens)
+        for i, token in enumerate(tokens):
+            row = logits[len(prompt) + i - 1]
+            assert row.max() - row[token] <= 2 * TOLERANCE["bfloat16"] * np.abs(row).max()
+
+
+def test_temperature_sampling_follows_the_host_rule_under_chunked_mixed_steps(folders):
+    """Four prompts of 1, 9, 40 and 63 tokens, prompt portions of at most 16 tokens mixed with
+    decoding, 12 tokens each at temperature 0.8: every token the engine picked is the token the host
+    rule picks from the plain implementation's logits, with the same seed and draw counter."""
+    from hyperion_b200.sampling import SamplingParams, reference_sample
+
+    config, _ = TINY["B"]
+    prompts = [random_ids(300 + i, n, config.vocab_size) for i, n in enumerate([1, 9, 40, 63])]
+    params = [SamplingParams(temperature=0.8, seed=1000 + i, max_tokens=12, ignore_eos=True) for i in range(4)]
+    engine = engine_for(folders["B"], "float32")
+    got = engine.generate(prompts, params, max_batch_tokens=16, prefill_chunk_busy=16)
+    assert [len(g) for g in got] == [12] * 4
+    for prompt, tokens, p in zip(prompts, got, params):
+        logits = plain_logits(folders["B"], prompt + tokens)
+        for i, token in enumerate(tokens):
+            want, info = reference_sample(logits[len(prompt) + i - 1], p.validated(), i, tokens[:i])
+            if want != token:
+                kept = info["kept"].tolist()
+                j = kept.index(token)
+                assert (info["cdf"][j - 1] if j else 0.0) - 1e-5 <= info["u"] <= info["cdf"][j] + 1e-5
+    # the same seeds give the same tokens whatever else is in the batch
+    alone = engine.generate([prompts[2]], params[2])
+    assert alone[0] == got[2]
+
+
+def test_top_k_top_p_penalty_through_generate(folders):
+    from hyperion_b200.sampling import SamplingParams
+
+    config, _ = TINY["A"]
+    prompt = random_ids(9, 12, config.vocab_size)
+    engine = engine_for(folders["A"], "float32")
+    params = SamplingParams(temperature=1.5, top_k=1, seed=5, max_tokens=6, ignore_eos=True)
+    greedy = engine.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    assert engine.generate([prompt], params) == greedy  # top_k = 1 is the argmax whatever the temperature
+    penalised = engine.generate([prompt], SamplingParams(temperature=1.0, top_k=1, repetition_penalty=50.0, seed=5, max_tokens=20, ignore_eos=True))[0]
+    assert len(set(penalised)) >= 15  # a heavy penalty keeps generated tokens from coming back
+
+
+def test_eos_stops_and_is_not_emitted(folders, tmp_path):
+    import json
+    import shutil
+
+    from hyperion_b200.sampling import SamplingParams
+
+    config, _ = TINY["A"]
+    prompt = random_ids(10, 7, config.vocab_size)
+    engine = engine_for(folders["A"], "float32")
+    free_run = engine.generate([prompt], SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))[0]
+    folder = tmp_path / "with_eos"
+    shutil.copytree(folders["A"], folder)
+    document = json.loads((folder / "config.json").read_text())
+    document["eos_token_id"] = free_run[4]
+    (folder / "config.json").write_text(json.dumps(document))
+    engine = engine_for(folder, "float32")
+    tokens, reasons = engine.generate([prompt], SamplingParams(temperature=0.0, max_tokens=10), return_reasons=True)
+    first = free_run.index(free_run[4])
+    assert tokens[0] == free_run[:first] and reasons == ["stop"]
+
+
+def test_small_pool_makes_requests_wait_and_a_hopeless_one_fail(folders):
+    from hyperion_b200.sampling import SamplingParams
+
+    config, _ = TINY["A"]
+    prompts = [random_ids(400 + i, n, config.vocab_size) for i, n in enumerate([30, 50, 20, 45, 300, 25])]
+    params = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    roomy = engine_for(folders["A"], "float32", max_tokens=4096)
+    want = roomy.generate(prompts, params)
+    tight = engine_for(folders["A"], "float32", page_size=16, max_tokens=128, max_requests=4)  # 8 pages
+    got, reasons = tight.generate(prompts, params, return_reasons=True)
+    assert reasons[4].startswith("needs 20 pages") and got[4] == []
+    for i in (0, 1, 2, 3, 5):
+        assert got[i] == want[i] and reasons[i] == "length"
+    tight.cache.check()
+    assert tight.cache.free_pages() == 8 and not tight.cache.live_requests
+
+
+def test_a_bad_step_is_refused_whole(folders):
+    from hyperion_b200.cache import OutOfPages
+    from hyperion_b200.engine.batch import BadStep, StepEntry
+
+    config, _ = TINY["A"]
+    engine = engine_for(folders["A"], "float32", max_tokens=64)
+    engine.step([StepEntry("a", [1, 2, 3], [])])
+    for bad in ([StepEntry("a", [4], [0]), StepEntry("a", [5], [0])], [StepEntry("b", [], [])], [StepEntry("b", [config.vocab_size], [])],
+                [StepEntry("b", [1], [1])], []):
+        with pytest.raises(BadStep):
+            engine.step(bad)
+    with pytest.raises(OutOfPages):
+        engine.step([StepEntry("a", [7], [0]), StepEntry("c", list(range(100)), [])])
+    assert engine.cache.length("a") == 3 and not engine.cache.has("b") and not engine.cache.has("c")
+    engine.cache.check()
+    out = engine.step([StepEntry("a", [7], [0])])
+    assert out.shape == (1, config.vocab_size)

@@ -1,0 +1,352 @@
+"""The parts alone against their plain formulas, and the generality of the composition: a model with
+different mixers in different layers, a layer that runs twice, a layer that reads another layer's
+cache, a windowed cache group; and a toy mixer with state of its own that is defined here, registered
+and stepped without touching the package."""
+from __future__ import annotations
+
+import json
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda", 0)
+
+
+def build_context(dtype, max_positions=512):
+    from hyperion_b200.parts import BuildContext
+
+    return BuildContext(dtype=dtype, device=DEV, max_positions=max_positions, shared={})
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 2 ** -7
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from hyperion_b200.parts import NORMS, PartSpec, base
+
+    part = base.make(NORMS, PartSpec("rmsnorm", "n.", {"hidden_size": 200, "eps": 1e-5}), build_context(dtype))
+    assert part.weights()["weight"].shape == (200,)
+    w = (1 + rnd(200, seed=1, scale=0.1)).to(torch.bfloat16)
+    part.load({"weight": w.to(DEV)})
+    h, delta = rnd(5, 200, seed=2), rnd(5, 200, seed=3).to(dtype)
+    hd = h.to(DEV)
+    out = part.forward(hd, delta.to(DEV))
+    want = plain.rmsnorm(h.double() + delta.double(), w.double(), 1e-5)
+    assert (out.cpu().double() - want).abs().max() <= tol(dtype) * want.abs().max()
+    assert torch.allclose(hd.cpu(), h + delta.float(), atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    from hyperion_b200.parts import FEED_FORWARDS, PartSpec, base
+
+    part = base.make(FEED_FORWARDS, PartSpec("swiglu", "m.", {"hidden_size": 96, "intermediate_size": 200}), build_context(dtype))
+    names = part.weights()
+    assert names["gate_proj.weight"].shape == (200, 96) and names["down_proj.weight"].shape == (96, 200)
+    tensors = {n: rnd(*s.shape, seed=i, scale=0.1).to(torch.bfloat16) for i, (n, s) in enumerate(names.items())}
+    part.load({n: (t.float() if dtype == torch.float32 else t).to(DEV) for n, t in tensors.items()})
+    x = rnd(7, 96, seed=9).to(dtype)
+    out = part.forward(x.to(DEV), None)
+    want = plain.swiglu_mlp(x.double(), *(tensors[n].double() for n in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
+    assert (out.cpu().double() - want).abs().max() <= tol(dtype) * want.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_position_part(dtype):
+    from hyperion_b200.parts import POSITIONS, PartSpec, base
+
+    part = base.make(POSITIONS, PartSpec("rope", "", {"head_dim": 24, "base": 5e5, "max_positions": 300}), build_context(dtype))
+    x = rnd(4, 3 * 24 + 10, seed=4).to(dtype)
+    positions = torch.tensor([0, 7, 150, 299], dtype=torch.int32)
+    xd = x.to(DEV).clone()
+    part.apply_(xd, 3, 24, positions.to(DEV))
+    cos, sin = plain.rope_tables(positions, 24, 5e5)
+    want = plain.rope(x.double()[:, :72].view(4, 3, 24), cos, sin).reshape(4, 72)
+    assert (xd.cpu().double()[:, :72] - want).abs().max() <= tol(dtype) * want.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_head_parts(dtype):
+    from hyperion_b200.parts import EMBEDDINGS, HEADS, PartSpec, base
+
+    sizes = {"vocab_size": 301, "hidden_size": 40}
+    embedding = base.make(EMBEDDINGS, PartSpec("token_embedding", "e.", sizes), build_context(dtype))
+    head = base.make(HEADS, PartSpec("linear_head", "h.", {**sizes, "tied": True}), build_context(dtype))
+    assert head.weights() == {}
+    table = rnd(301, 40, seed=5).to(torch.bfloat16)
+    embedding.load({"weight": (table.float() if dtype == torch.float32 else table).to(DEV)})
+    head.tie(embedding.table)
+    ids = torch.tensor([300, 0, 17], dtype=torch.int32)
+    h = embedding.forward(ids.to(DEV))
+    assert torch.equal(h.cpu(), table.float()[ids.long()])
+    x = rnd(3, 40, seed=6).to(dtype)
+    logits = head.forward(x.to(DEV))
+    assert logits.dtype == torch.float32
+    want = x.double() @ table.double().t()
+    assert (logits.cpu().double() - want).abs().max() <= tol(dtype) * want.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_part_alone(dtype):
+    """The attention part with a cache of its own: a prompt portion, then two more steps."""
+    from hyperion_b200.cache import CacheManager
+    from hyperion_b200.engine.batch import PagedView
+    from hyperion_b200.parts import MIXERS, PartSpec, base
+
+    hidden, heads, kv_heads, d = 80, 6, 3, 16
+    spec = PartSpec("gqa_attention", "a.", {"hidden_size": hidden, "heads": heads, "kv_heads": kv_heads, "head_dim": d, "bias": True,
+                                            "position": PartSpec("rope", "", {"head_dim": d, "base": 1e4, "max_positions": 128})})
+    part = base.make(MIXERS, spec, build_context(dtype, 128))
+    tensors = {n: rnd(*s.shape, seed=20 + i, scale=0.15).to(torch.bfloat16) for i, (n, s) in enumerate(part.weights().items())}
+    part.load({n: (t.float() if dtype == torch.float32 else t).to(DEV) for n, t in tensors.items()})
+    cache = CacheManager([(0, part.cache_request())], page_size=8, num_pages=6, max_requests=2, dtype=dtype, device=DEV)
+    cache.add_request("r")
+    x = rnd(21, hidden, seed=30).to(dtype)
+    w = {"a." + n: t for n, t in tensors.items()}
+    dims = {"heads": heads, "kv_heads": kv_heads, "head_dim": d, "theta": 1e4}
+    want = plain.attention_block(x.double(), {k: v.double() for k, v in w.items()}, "a.", dims, torch.arange(21))
+
+    @dataclass
+    class Step:
+        n_tokens: int
+        positions: torch.Tensor
+        token_row: torch.Tensor
+        rows: list
+        host: dict
+        extra: dict
+
+    from hyperion_b200.engine.batch import MetadataPacker, Row
+
+    at = 0
+    for count in (17, 1, 3):
+        cache.extend("r", count)
+        rows = [Row("r", 0, count, at, cache.slot("r"))]
+        packer = MetadataPacker(DEV)
+        packer.begin()
+        host: dict = {}
+        for plan in part.step_plans().values():
+            plan(rows, packer, host)
+        extra = packer.finish()
+        step = Step(count, torch.arange(at, at + count, dtype=torch.int32, device=DEV), torch.zeros(count, dtype=torch.int32, device=DEV),
+                    rows, host, extra)
+        table = torch.tensor([cache.table(0, "r")], dtype=torch.int32, device=DEV)
+        out = part.forward(x[at:at + count].to(DEV), step, PagedView(cache.paged_storage(0), table, 8, 0), True)
+        assert (out.cpu().double() - want[at:at + count]).abs().max() <= 2 * tol(dtype) * want.abs().max()
+        cache.advance("r", count)
+        at += count
+
+
+# ------------------------------------------------------------------------------------------------
+# A model whose layers differ: full attention, windowed attention run twice, and a layer that reads
+# the first layer's cache.  Its architecture is registered here, not in the package.
+MIXED = {"architectures": ["TestMixedLM"], "hidden": 96, "vocab": 211, "inter": 136, "eps": 1e-5, "window": 24, "max_positions": 256}
+
+
+def mixed_spec(c):
+    from hyperion_b200.parts import LayerSpec, ModelSpec, PartSpec, Run
+
+    rope = PartSpec("rope", "", {"head_dim": 16, "base": 1e4, "max_positions": c["max_positions"]})
+
+    def attention(prefix, kv_heads, **more):
+        return PartSpec("gqa_attention", prefix, {"hidden_size": c["hidden"], "heads": 6, "kv_heads": kv_heads, "head_dim": 16,
+                                                   "bias": True, "position": rope, **more})
+
+    def layer(i, mixer):
+        p = f"layers.{i}."
+        norm = {"hidden_size": c["hidden"], "eps": c["eps"]}
+        return LayerSpec("prenorm", mixer, PartSpec("swiglu", p + "mlp.", {"hidden_size": c["hidden"], "intermediate_size": c["inter"]}),
+                         {"input": PartSpec("rmsnorm", p + "n1.", norm), "post_mixer": PartSpec("rmsnorm", p + "n2.", norm)})
+
+    layers = (layer(0, attention("layers.0.attn.", 2)), layer(1, attention("layers.1.attn.", 3, window=c["window"])),
+              layer(2, attention("layers.2.attn.", 2, shares_kv=True)))
+    sizes = {"vocab_size": c["vocab"], "hidden_size": c["hidden"]}
+    return ModelSpec("TestMixedLM", c["hidden"], c["vocab"], c["max_positions"], PartSpec("token_embedding", "embed.", sizes), layers,
+                     (Run(0), Run(1), Run(1), Run(2, reads_cache_of=0)), PartSpec("rmsnorm", "norm.", {"hidden_size": c["hidden"], "eps": c["eps"]}),
+                     PartSpec("linear_head", "head.", {**sizes, "tied": False}))
+
+
+def mixed_plain(c, w, ids):
+    """The same model with the plain functions, whole sequence."""
+    w = {k: v.double() for k, v in w.items()}
+    t = len(ids)
+    positions = torch.arange(t)
+    cos, sin = plain.rope_tables(positions, 16, 1e4)
+    h = plain.embedding(w["embed.weight"], torch.tensor(ids))
+    kept = {}
+
+    def attend(layer, x, kv_heads, window=None, shared=None):
+        p = f"layers.{layer}.attn."
+        q = plain.rope(plain.linear(x, w[p + "q_proj.weight"], w[p + "q_proj.bias"]).view(t, 6, 16), cos, sin)
+        if shared is None:
+            k = plain.rope(plain.linear(x, w[p + "k_proj.weight"], w[p + "k_proj.bias"]).view(t, kv_heads, 16), cos, sin)
+            v = plain.linear(x, w[p + "v_proj.weight"], w[p + "v_proj.bias"]).view(t, kv_heads, 16)
+            kept[layer] = (k, v)
+        else:
+            k, v = kept[shared]
+        a = plain.attention(q, k, v, positions, positions, 0.25, window)
+        return plain.linear(a.reshape(t, -1), w[p + "o_proj.weight"])
+
+    for layer, kv_heads, window, shared in ((0, 2, None, None), (1, 3, c["window"], None), (1, 3, c["window"], None), (2, 2, None, 0)):
+        p = f"layers.{layer}."
+        h = h + attend(layer, plain.rmsnorm(h, w[p + "n1.weight"], c["eps"]), kv_heads, window, shared)
+        x = plain.rmsnorm(h, w[p + "n2.weight"], c["eps"])
+        h = h + plain.swiglu_mlp(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return plain.linear(plain.rmsnorm(h, w["norm.weight"], c["eps"]), w["head.weight"])
+
+
+@pytest.fixture(scope="module")
+def mixed_folder(tmp_path_factory):
+    from hyperion_b200.models import Architecture, register_architecture
+    from hyperion_b200.weights import write_model_folder
+
+    register_architecture(Architecture("TestMixedLM", lambda document: dict(document), mixed_spec, lambda config: dict(config)))
+    return write_model_folder(tmp_path_factory.mktemp("mixed") / "m", "TestMixedLM", MIXED, seed=4, std=0.08)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_of_different_kinds_twice_run_and_shared_cache(mixed_folder, dtype):
+    from hyperion_b200.api import Engine
+    from hyperion_b200.engine.batch import StepEntry
+    from hyperion_b200.weights import read_all
+
+    weights = read_all(mixed_folder)
+    assert "layers.2.attn.k_proj.weight" not in weights and "layers.1.attn.k_proj.bias" in weights
+    g = torch.Generator().manual_seed(0)
+    requests = {name: torch.randint(0, MIXED["vocab"], (n,), generator=g).tolist() for name, n in (("a", 120), ("b", 75), ("c", 140))}
+    want = {name: mixed_plain(MIXED, weights, ids).numpy() for name, ids in requests.items()}
+    engine = Engine.from_folder(mixed_folder, dtype=dtype, page_size=8, max_tokens=232, max_requests=3)
+    cache = engine.cache
+    assert len(cache.paged) == 2 and cache.paged[0].users == [0] and cache.paged[1].users == [1, 2]  # entry 3 owns no cache
+    tolerance = 2e-5 if dtype == "float32" else 2.5e-2
+    fed = {name: 0 for name in requests}
+    sizes = [9, 2, 30, 1, 5, 17, 1, 1, 40, 3]
+    k = 0
+    order = ["a", "b"]
+    while order:
+        entries = []
+        for name in list(order):
+            n = min(sizes[k % len(sizes)], len(requests[name]) - fed[name])
+            k += 1
+            entries.append(StepEntry(name, requests[name][fed[name]:fed[name] + n], list(range(n))))
+        logits = engine.step(entries).cpu().numpy()
+        row = 0
+        for entry in entries:
+            n = len(entry.tokens)
+            ref = want[entry.request][fed[entry.request]:fed[entry.request] + n]
+            assert np.abs(logits[row:row + n] - ref).max() <= tolerance * np.abs(ref).max(), (entry.request, fed[entry.request])
+            row += n
+            fed[entry.request] += n
+            if fed[entry.request] == len(requests[entry.request]):
+                engine.finish(entry.request)
+                order.remove(entry.request)
+                if entry.request == "b":
+                    order.append("c")  # takes over the pages b and the windows gave back
+        cache.check()
+    engine.check()
+    # the windowed group held far fewer pages than the full one at the end of a long request
+    assert cache.paged[1].pool.available == cache.paged[1].pool.num_pages
+
+
+# ------------------------------------------------------------------------------------------------
+# A toy mixer with state of its own: an exponential moving sum per request, kept in a state slot.
+TOY = {"architectures": ["TestToyStateLM"], "hidden": 48, "vocab": 97, "inter": 64, "eps": 1e-6, "decay": 0.9, "max_positions": 128}
+
+
+def register_toy():
+    from hyperion_b200.models import Architecture, register_architecture
+    from hyperion_b200.parts import LayerSpec, Mixer, ModelSpec, PartSpec, RequestState, Run, WeightSpec, register_mixer
+
+    class MovingSum(Mixer):
+        """y_t = (s_t) W_out with s_t = decay * s_{t-1} + x_t W_in; s lives in the request's state slot."""
+
+        def __init__(self, spec, build):
+            super().__init__(spec, build)
+            self.hidden, self.decay = spec.params["hidden_size"], spec.params["decay"]
+
+        def weights(self):
+            return {"in.weight": WeightSpec((self.hidden, self.hidden)), "out.weight": WeightSpec((self.hidden, self.hidden))}
+
+        def load(self, tensors):
+            self.w_in, self.w_out = tensors["in.weight"].float(), tensors["out.weight"].float()
+
+        def cache_request(self):
+            return RequestState((self.hidden,), torch.float32)
+
+        def forward(self, x, step, cache, own_cache):
+            u = x.float() @ self.w_in.t()
+            out = torch.empty_like(u)
+            for row in step.rows:
+                s = cache.state[row.slot]
+                for t in range(row.start, row.start + row.count):
+                    s = self.decay * s + u[t]
+                    out[t] = s
+                cache.state[row.slot] = s
+            return (out @ self.w_out.t()).to(self.dtype)
+
+    def spec(c):
+        sizes = {"vocab_size": c["vocab"], "hidden_size": c["hidden"]}
+        norm = {"hidden_size": c["hidden"], "eps": c["eps"]}
+        layers = tuple(LayerSpec("prenorm", PartSpec("test_moving_sum", f"l{i}.mix.", {"hidden_size": c["hidden"], "decay": c["decay"]}),
+                                 PartSpec("swiglu", f"l{i}.mlp.", {"hidden_size": c["hidden"], "intermediate_size": c["inter"]}),
+                                 {"input": PartSpec("rmsnorm", f"l{i}.n1.", norm), "post_mixer": PartSpec("rmsnorm", f"l{i}.n2.", norm)})
+                       for i in range(2))
+        return ModelSpec("TestToyStateLM", c["hidden"], c["vocab"], c["max_positions"], PartSpec("token_embedding", "embed.", sizes), layers,
+                         (Run(0), Run(1)), PartSpec("rmsnorm", "norm.", norm), PartSpec("linear_head", "head.", {**sizes, "tied": True}))
+
+    register_mixer("test_moving_sum", MovingSum)
+    register_architecture(Architecture("TestToyStateLM", lambda document: dict(document), spec, lambda config: dict(config)))
+
+
+def toy_plain(c, w, ids):
+    w = {k: v.double() for k, v in w.items()}
+    h = plain.embedding(w["embed.weight"], torch.tensor(ids))
+    for i in range(2):
+        x = plain.rmsnorm(h, w[f"l{i}.n1.weight"], c["eps"])
+        u = x @ w[f"l{i}.mix.in.weight"].t()
+        s = torch.zeros(c["hidden"], dtype=torch.float64)
+        states = []
+        for t in range(len(ids)):
+            s = c["decay"] * s + u[t]
+            states.append(s)
+        h = h + torch.stack(states) @ w[f"l{i}.mix.out.weight"].t()
+        x = plain.rmsnorm(h, w[f"l{i}.n2.weight"], c["eps"])
+        h = h + plain.swiglu_mlp(x, w[f"l{i}.mlp.gate_proj.weight"], w[f"l{i}.mlp.up_proj.weight"], w[f"l{i}.mlp.down_proj.weight"])
+    return plain.linear(plain.rmsnorm(h, w["norm.weight"], c["eps"]), w["embed.weight"])
+
+
+def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path):
+    from hyperion_b200.api import Engine
+    from hyperion_b200.engine.batch import StepEntry
+    from hyperion_b200.weights import read_all, write_model_folder
+
+    register_toy()
+    folder = write_model_folder(tmp_path / "toy", "TestToyStateLM", TOY, seed=8, std=0.1)
+    weights = read_all(folder)
+    engine = Engine.from_folder(folder, dtype="float32", page_size=16, max_tokens=64, max_requests=2)
+    assert not engine.cache.paged and [s.users for s in engine.cache.states][0] == [0, 1]
+    g = torch.Generator().manual_seed(1)
+    a, b, c = (torch.randint(0, TOY["vocab"], (n,), generator=g).tolist() for n in (30, 22, 18))
+    want = {"a": toy_plain(TOY, weights, a).numpy(), "b": toy_plain(TOY, weights, b).numpy(), "c": toy_plain(TOY, weights, c).numpy()}
+    got_a = [engine.step([StepEntry("a", a[:11], list(range(11)))]).cpu().numpy()]
+    mixed = engine.step([StepEntry("a", a[11:12], [0]), StepEntry("b", b, list(range(22)))]).cpu().numpy()
+    got_a.append(mixed[:1])
+    assert np.abs(mixed[1:] - want["b"]).max() <= 1e-4 * np.abs(want["b"]).max()
+    engine.finish("b")
+    # c takes b's slot: its state must start from zero, not from what b left
+    mixed = engine.step([StepEntry("c", c, list(range(18))), StepEntry("a", a[12:], list(range(18)))]).cpu().numpy()
+    assert engine.cache.slot("c") == 1
+    got_a.append(mixed[18:])
+    assert np.abs(mixed[:18] - want["c"]).max() <= 1e-4 * np.abs(want["c"]).max()
+    assert np.abs(np.concatenate(got_a) - want["a"]).max() <= 1e-4 * np.abs(want["a"]).max()
