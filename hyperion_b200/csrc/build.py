@@ -60,7 +60,8 @@ def _build_dir() -> Path:
 
 def _key(module: str, defines: Mapping[str, object]) -> str:
     digest = hashlib.sha256()
-    for path in [SOURCE_DIR / f"{module}.cu", *sorted(SOURCE_DIR.glob("*.cuh"))]:
+    includes = sorted(p for p in SOURCE_DIR.iterdir() if p.suffix in (".cuh", ".h") or (p.suffix == ".cu" and f'"{p.name}"' in (SOURCE_DIR / f"{module}.cu").read_text()))
+    for path in [SOURCE_DIR / f"{module}.cu", *includes]:
         digest.update(path.name.encode())
         digest.update(path.read_bytes())
     digest.update(repr(sorted(defines.items())).encode())
