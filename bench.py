@@ -211,6 +211,7 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=28, help="fewer than the configuration's 28 only to save memory or time")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points, prefill and e2e")
+    parser.add_argument("--only", default=None, choices=["prefill"], help="time one part alone (for profiling)")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -232,6 +233,11 @@ def main() -> int:
     tokens_needed = largest * (PROMPT + 64 + max(args.steps + args.warmup, 64 + 8)) + PROMPT
     engine = Engine.from_random("Qwen2ForCausalLM", config, seed=0, dtype="bfloat16", page_size=16,
                                 max_tokens=tokens_needed, max_requests=max(largest, 8))
+    if args.only == "prefill":  # for profiling: the prefill step alone
+        prefill = time_prefill(engine, reps=max(1, args.steps), warmup=args.warmup)
+        print(json.dumps({"only": "prefill", "layers": args.layers, "tokens": PROMPT, "ms": round(prefill["ms"], 3),
+                          "tokens_per_s": round(PROMPT / (prefill["ms"] / 1e3), 1)}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     main_run = time_decode(engine, args.batch, args.steps, args.warmup)
