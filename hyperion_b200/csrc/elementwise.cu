@@ -92,9 +92,33 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     out[(size_t)t * inter + i] = from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores, 8 elements per thread.
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter) {
+    const int t = blockIdx.y;
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= inter) return;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gate_up + (size_t)t * 2 * inter + i);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gate_up + (size_t)t * 2 * inter + inter + i);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
+        o2[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * inter + i) = o4;
+}
+
 HB_EXPORT int hb_swiglu(const void* gate_up, void* out, int is_bf16, int tokens, int inter, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (tokens > 65535) return HB_UNSUPPORTED_SIZE;
+    if (is_bf16 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+        dim3 grid8((inter / 8 + 255) / 256, tokens);
+        swiglu_bf16x8_kernel<<<grid8, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
+        return launch_status();
+    }
     dim3 grid((inter + 255) / 256, tokens);
     if (is_bf16)
         swiglu_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
@@ -167,6 +191,67 @@ __global__ void kv_store_kernel(const T* __restrict__ src, int stride, int k_off
         const T v = row[(which ? v_offset : k_offset) + c];
         cache[page_base + (((size_t)which * kv_heads + head) * page_size + slot) * head_dim + d] = v;
     }
+}
+
+// ---------------------------------------------------------------- rotation fused with the cache write
+// One pass over a token's [q | k | v] row: the query heads are rotated in place, the key heads are
+// rotated on their way into the cache (the row's own copy of k is left as it was: nothing reads it
+// again), the value heads are copied.  Same arithmetic as rope_kernel followed by kv_store_kernel.
+template <typename T>
+__global__ void rope_kv_store_kernel(T* __restrict__ x, int stride, int q_heads, int kv_heads, int head_dim,
+                                     const int* __restrict__ positions, const float2* __restrict__ table, int max_positions,
+                                     T* __restrict__ cache, const int* __restrict__ block_table, int table_width,
+                                     const int* __restrict__ token_row, int page_size, int pages, int* status) {
+    const int t = blockIdx.x;
+    const int half = head_dim >> 1;
+    const int pos = positions[t];
+    if (pos < 0 || pos >= max_positions) {
+        if (threadIdx.x == 0) atomicOr(status, HB_STATUS_BAD_POSITION);
+        return;
+    }
+    const int block = pos / page_size;
+    const int page = block < table_width ? block_table[(size_t)token_row[t] * table_width + block] : -1;
+    const bool page_ok = page >= 0 && page < pages;
+    if (!page_ok && threadIdx.x == 0) atomicOr(status, HB_STATUS_BAD_PAGE);
+    const int slot = pos - block * page_size;
+    T* row = x + (size_t)t * stride;
+    const float2* cs = table + (size_t)pos * half;
+    const size_t page_base = (size_t)(page_ok ? page : 0) * 2 * kv_heads * page_size * head_dim;
+    const int rotated = (q_heads + kv_heads) * half;
+    for (int e = threadIdx.x; e < rotated + kv_heads * half; e += blockDim.x) {
+        if (e < rotated) {
+            const int head = e / half, i = e - head * half;
+            const float2 c = cs[i];
+            T* p = row + head * head_dim + i;
+            const float x1 = to_float(p[0]), x2 = to_float(p[half]);
+            const T y1 = from_float<T>(x1 * c.x - x2 * c.y), y2 = from_float<T>(x2 * c.x + x1 * c.y);
+            if (head < q_heads) {
+                p[0] = y1; p[half] = y2;
+            } else if (page_ok) {
+                T* dst = cache + page_base + (((size_t)(head - q_heads)) * page_size + slot) * head_dim + i;
+                dst[0] = y1; dst[half] = y2;
+            }
+        } else if (page_ok) {  // values: two elements per thread
+            const int f = e - rotated, head = f / half, i = (f - head * half) * 2;
+            const T* p = row + (q_heads + kv_heads + head) * head_dim + i;
+            T* dst = cache + page_base + (((size_t)(kv_heads + head)) * page_size + slot) * head_dim + i;
+            dst[0] = p[0]; dst[1] = p[1];
+        }
+    }
+}
+
+HB_EXPORT int hb_rope_kv_store(void* x, int is_bf16, int tokens, int stride, int q_heads, int kv_heads, int head_dim,
+                               const int* positions, const float* table, int max_positions, void* cache, const int* block_table,
+                               int table_width, const int* token_row, int page_size, int pages, int* status, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (head_dim & 1) return HB_UNSUPPORTED_SIZE;
+    if (is_bf16)
+        rope_kv_store_kernel<<<tokens, 256, 0, stream>>>((__nv_bfloat16*)x, stride, q_heads, kv_heads, head_dim, positions, (const float2*)table,
+                                                         max_positions, (__nv_bfloat16*)cache, block_table, table_width, token_row, page_size, pages, status);
+    else
+        rope_kv_store_kernel<<<tokens, 256, 0, stream>>>((float*)x, stride, q_heads, kv_heads, head_dim, positions, (const float2*)table,
+                                                         max_positions, (float*)cache, block_table, table_width, token_row, page_size, pages, status);
+    return launch_status();
 }
 
 HB_EXPORT int hb_kv_store(const void* src, int is_bf16, int tokens, int stride, int k_offset, int v_offset, void* cache,

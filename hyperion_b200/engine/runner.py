@@ -20,17 +20,26 @@ from ..models.model import DecoderModel
 from .batch import BadStep, MetadataPacker, Row, StepContext, StepEntry
 
 
+GRAPH_TABLE_STEP = 64  # block-table widths of graphed steps are multiples of this many pages
+MAX_GRAPHS = 96
+
+
 class ModelRunner:
-    def __init__(self, model: DecoderModel, cache: CacheManager):
+    def __init__(self, model: DecoderModel, cache: CacheManager, use_graphs: bool = True):
         if model.device.type != "cuda":
             raise RuntimeError("the engine runs on a CUDA device only (no CPU path exists)")
         self.model = model
         self.cache = cache
         self.device = model.device
-        self.packer = MetadataPacker(self.device)
+        self.packer = MetadataPacker(self.device, capacity=1 << 20)  # never reallocated below this: graphs keep its address
         self.planners = model.step_planners()
         build.build_many(model.kernel_modules())
         self.steps_run = 0
+        self.use_graphs = use_graphs
+        self.graphs: dict = {}
+        self._graph_seen: dict = {}
+        self._graph_pool = None
+        self.graph_launches = 0  # launches of this package's kernels inside replayed graphs
 
     # ------------------------------------------------------------------ validation
     def _validate(self, entries: Sequence[StepEntry]) -> None:
@@ -56,7 +65,7 @@ class ModelRunner:
                 raise BadStep(f"request {entry.request!r} would reach position {length + count}, the model's limit is {limit}")
 
     # ------------------------------------------------------------------ the batch on the device
-    def _context(self, entries: Sequence[StepEntry], extra_arrays=None) -> StepContext:
+    def _context(self, entries: Sequence[StepEntry], extra_arrays=None, pad_tables: bool = False) -> StepContext:
         rows: list[Row] = []
         token_ids: list[int] = []
         positions: list[int] = []
@@ -81,12 +90,16 @@ class ModelRunner:
         for group in range(len(self.cache.paged)):
             tables = [self.cache.table(group, row.request) for row in rows]
             width = max(1, max(len(t) for t in tables))
+            if pad_tables:  # a replayed graph needs the same layout for many steps: widths in steps of GRAPH_TABLE_STEP
+                width = -(-width // GRAPH_TABLE_STEP) * GRAPH_TABLE_STEP
             flat: list[int] = []
             for table in tables:
                 flat.extend(table)
                 flat.extend([NO_PAGE] * (width - len(table)))
             packer.add(f"table{group}", flat, (len(rows), width))
         host = {"positions": positions, "token_row": token_row, "want": want}
+        if pad_tables:
+            host["context_cap"] = width * self.cache.page_size if self.cache.paged else 0
         for key, plan in self.planners.items():
             plan(rows, packer, host)
         for name, (values, shape) in (extra_arrays or {}).items():
@@ -118,12 +131,52 @@ class ModelRunner:
             for request in added:
                 self.cache.free(request)
             raise
-        context = self._context(entries, extra_arrays)
+        key = self._graph_key(entries, extra_arrays)
+        context = self._context(entries, extra_arrays, pad_tables=key is not None)
         self.last_context = context
-        logits = self.model.forward(context, self.cache)
+        logits = self.model.forward(context, self.cache) if key is None else self._replay(key, context)
         for entry in entries:
             self.cache.advance(entry.request, len(entry.tokens))
         self.steps_run += 1
+        return logits
+
+    # ------------------------------------------------------------------ CUDA graphs for decode steps
+    def _graph_key(self, entries: Sequence[StepEntry], extra_arrays):
+        """Steps of single decoded tokens whose logits are all wanted repeat with the same shape: their
+        launches are captured once per (rows, table width, extra arrays) and replayed, which removes
+        the host's launch cost (the reference captures a graph per decode bucket for the same reason:
+        helios/crates/helios-hal/src/backends/hopper_sm90/session.rs:510-551)."""
+        if not self.use_graphs or any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+            return None
+        widths = []
+        for group in range(len(self.cache.paged)):
+            blocks = max(-(-(self.cache.length(e.request) + 1) // self.cache.page_size) for e in entries)
+            blocks = max(blocks, max(len(self.cache.table(group, e.request)) for e in entries))
+            widths.append(-(-blocks // GRAPH_TABLE_STEP) * GRAPH_TABLE_STEP)
+        extras = tuple((name, len(values)) for name, (values, _) in (extra_arrays or {}).items())
+        return (len(entries), tuple(widths), extras)
+
+    def _replay(self, key, context: StepContext):
+        entry = self.graphs.get(key)
+        if entry is None:
+            seen = self._graph_seen.get(key, 0) + 1
+            self._graph_seen[key] = seen
+            if seen < 2 or len(self.graphs) >= MAX_GRAPHS:  # the first step of a shape runs directly (it also warms the libraries up)
+                return self.model.forward(context, self.cache)
+            from ..ops import native
+
+            before = native.LAUNCHES[0]
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                logits = self.model.forward(context, self.cache)
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            entry = (graph, logits, native.LAUNCHES[0] - before)
+            native.LAUNCHES[0] = before
+            self.graphs[key] = entry
+        graph, logits, launches = entry
+        graph.replay()
+        self.graph_launches += launches
         return logits
 
     def finish(self, request: Hashable) -> None:

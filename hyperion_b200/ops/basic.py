@@ -100,6 +100,20 @@ def kv_store(src: torch.Tensor, k_offset: int, v_offset: int, cache: torch.Tenso
                           i32(head_dim), i32(page_size), i32(pages), ptr(status_word(src.device)), stream_ptr()), "kv_store")
 
 
+def rope_kv_store_(x: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, positions: torch.Tensor, table: torch.Tensor,
+                   cache: torch.Tensor, block_table: torch.Tensor, token_row: torch.Tensor) -> None:
+    """RoPE on the q heads of ``x`` = [q | k | v] in place, rotated keys and the values written to ``cache``."""
+    require_cuda(x, positions, table, cache, block_table, token_row)
+    pages, two, cache_heads, page_size, cache_dim = cache.shape
+    if (x.dtype != cache.dtype or x.stride(-1) != 1 or table.dtype != torch.float32 or table.shape[1] * 2 != head_dim
+            or cache_heads != kv_heads or cache_dim != head_dim or not cache.is_contiguous()):
+        raise KernelError("rope_kv_store: bad layout")
+    lib = library("elementwise")
+    check(lib.hb_rope_kv_store(ptr(x), i32(is_bf16(x)), i32(x.shape[0]), i32(x.stride(0)), i32(q_heads), i32(kv_heads), i32(head_dim),
+                               ptr(positions), ptr(table), i32(table.shape[0]), ptr(cache), ptr(block_table), i32(block_table.shape[1]),
+                               ptr(token_row), i32(page_size), i32(pages), ptr(status_word(x.device)), stream_ptr()), "rope_kv_store")
+
+
 def attention_generic(q: torch.Tensor, heads: int, cache: torch.Tensor, block_table: torch.Tensor, token_row: torch.Tensor,
                       positions: torch.Tensor, scale: float, window: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of every token over its request's pages; q is [tokens, >= heads*d] (a view is fine)."""

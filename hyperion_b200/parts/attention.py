@@ -87,11 +87,14 @@ class GroupedQueryAttention(Mixer):
         if cache is None:
             raise ValueError("attention needs a paged cache; the schedule gave it none")
         qkv = ops.linear(x, self.w_qkv, self.b_qkv, self.dtype)
-        rotated = self.heads if self.shares_kv else self.heads + self.kv_heads
-        if self.position is not None:
-            self.position.apply_(qkv, rotated, self.head_dim, step.positions)
-        if own_cache and not self.shares_kv:
-            ops.kv_store(qkv, self.q_width, self.q_width + self.kv_width, cache.kv, cache.block_table, step.token_row, step.positions)
+        stores = own_cache and not self.shares_kv
+        if self.position is not None and stores:
+            self.position.apply_and_store_(qkv, self.heads, self.kv_heads, self.head_dim, step.positions, cache, step.token_row)
+        else:
+            if self.position is not None:
+                self.position.apply_(qkv, self.heads if self.shares_kv else self.heads + self.kv_heads, self.head_dim, step.positions)
+            if stores:
+                ops.kv_store(qkv, self.q_width, self.q_width + self.kv_width, cache.kv, cache.block_table, step.token_row, step.positions)
         if self.fast:
             attn = self._attend_fast(qkv, step, cache)
         else:
@@ -124,7 +127,9 @@ class GroupedQueryAttention(Mixer):
             fast_attention.attention_tiles(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions,
                                            step.extra[key], n_tiles, self.scale, self.window, out)
         if n_items:
-            longest = max(row.position + row.count for row in step.rows if row.count <= fast_attention.TOKEN_SHAPE_MAX)
+            # a step replayed from a CUDA graph fixes its launch shape for every context its tables can hold
+            longest = step.host.get("context_cap") or max(row.position + row.count for row in step.rows
+                                                          if row.count <= fast_attention.TOKEN_SHAPE_MAX)
             if self.window:
                 longest = min(longest, self.window + fast_attention.KEY_TILE)
             splits = fast_attention.choose_splits(n_items, self.heads, self.kv_heads, longest)

@@ -89,6 +89,16 @@ class PositionEncoding(Part):
         """Encode the positions into the first ``heads`` heads of every row of ``x``, in place."""
         raise NotImplementedError
 
+    def apply_and_store_(self, x: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, positions: torch.Tensor, cache: Any,
+                         token_row: torch.Tensor) -> None:
+        """``x`` = [q | k | v] per token: encode q (in place) and k, and write k and v to the paged
+        ``cache``.  A position encoding may fuse the three; this default does them one after the other."""
+        from .. import ops
+
+        self.apply_(x, q_heads + kv_heads, head_dim, positions)
+        width = kv_heads * head_dim
+        ops.kv_store(x, q_heads * head_dim, q_heads * head_dim + width, cache.kv, cache.block_table, token_row, positions)
+
 
 class Mixer(Part):
     def cache_request(self) -> PagedKV | RequestState | None:

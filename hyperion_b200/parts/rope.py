@@ -44,5 +44,10 @@ class RotaryEncoding(PositionEncoding):
             raise ValueError(f"rotary encoding built for head_dim {self.head_dim}, used with {head_dim}")
         ops.rope_(x, heads, head_dim, positions, self.table)
 
+    def apply_and_store_(self, x, q_heads, kv_heads, head_dim, positions, cache, token_row):
+        if head_dim != self.head_dim:
+            raise ValueError(f"rotary encoding built for head_dim {self.head_dim}, used with {head_dim}")
+        ops.rope_kv_store_(x, q_heads, kv_heads, head_dim, positions, self.table, cache.kv, cache.block_table, token_row)
+
 
 register_position("rope", RotaryEncoding)

@@ -164,6 +164,27 @@ def test_kv_store_writes_where_the_table_says_and_nowhere_else():
     assert torch.equal(cd.cpu(), want)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_rope_and_cache_write_equals_the_two_steps(dtype):
+    from hyperion_b200.parts.rope import rotary_table
+
+    q_heads, kv_heads, head_dim, page_size = 5, 3, 24, 4
+    table = torch.tensor([[2, 0, 5, -1], [1, 3, 4, 6]], dtype=torch.int32).to(DEV)
+    token_row = torch.tensor([0, 0, 0, 1, 1], dtype=torch.int32).to(DEV)
+    positions = torch.tensor([3, 4, 11, 0, 15], dtype=torch.int32).to(DEV)
+    rope_table = rotary_table(head_dim, 1e4, 64).to(DEV)
+    x = rnd(5, (q_heads + 2 * kv_heads) * head_dim, seed=21, dtype=dtype).to(DEV)
+    a, b = x.clone(), x.clone()
+    cache_a = torch.zeros(7, 2, kv_heads, page_size, head_dim, dtype=dtype, device=DEV)
+    cache_b = cache_a.clone()
+    ops().rope_(a, q_heads + kv_heads, head_dim, positions, rope_table)
+    ops().kv_store(a, q_heads * head_dim, (q_heads + kv_heads) * head_dim, cache_a, table, token_row, positions)
+    ops().rope_kv_store_(b, q_heads, kv_heads, head_dim, positions, rope_table, cache_b, table, token_row)
+    assert torch.equal(cache_a, cache_b)
+    assert torch.equal(a[:, : q_heads * head_dim], b[:, : q_heads * head_dim])
+    assert torch.equal(b[:, q_heads * head_dim:], x[:, q_heads * head_dim:])  # the row's own k and v are left alone
+
+
 def reference_attention(q, keys, values, rows, scale, window):
     """q [T, heads, d] float64; rows: list of (request index, first position, count)."""
     outs = []
