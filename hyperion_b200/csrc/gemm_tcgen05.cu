@@ -1,0 +1,393 @@
+// bfloat16 matrix products on the 5th-generation tensor cores: C = A * W^T with A [M, K] and W [N, K],
+// both K-contiguous, accumulated in float in tensor memory.
+//
+// One block computes one tile.  Warp 0 (one lane) is the producer: it fetches 128 x 64 and BN x 64
+// operand tiles with TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a ring of
+// shared-memory stages.  Warp 1 owns tensor memory (tcgen05.alloc / dealloc) and one of its lanes
+// issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16) four times per stage, releasing the stage
+// with tcgen05.commit.  Warps 2-5 are the epilogue: each reads its quarter of the accumulator's 128
+// lanes with tcgen05.ld and writes the result.  Epilogues: bfloat16 (+ bias), float (+ bias), SwiGLU
+// over a tile whose first half are gate columns and second half the matching up columns, and a float
+// partial for split-K.  With `swap` the roles of the operands are exchanged (the weight matrix
+// supplies the 128 rows, a small batch the BN columns) and the tile is stored transposed: that is
+// the shape of decode, where M is 1..64 and the weights stream from HBM once.
+//
+// Every wait on an mbarrier is bounded: when a wait runs out, the kernel records it in the status
+// word, all roles leave their loops, tensor memory is freed and the block returns.
+//
+// The reference leaves these products to cuBLAS (helios/crates/helios-hal/src/cuda/cublas.rs:158-188,
+// cuda/cublaslt.rs:203-212) and applies bias and SwiGLU in separate kernels
+// (helios/crates/helios-hal/kernels/elementwise.cu:29,134).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr unsigned WAIT_LIMIT = 1u << 24;
+
+enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
+
+struct GemmParams {
+    void* c;              // output
+    const float* bias_f;  // bias as float (or null)
+    const bf16* bias_h;   // bias as bfloat16 (or null)
+    float* partial;       // split-K partials [splits, rows_out, cols_out] float
+    int m, n, k;          // problem: A [m, k], W [n, k]; output [m, n] (SwiGLU: [m, n / 2])
+    int ldc;              // row stride of the output in elements
+    int k_blocks_per_split;
+    int* status;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when the limit ran out or another role failed.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* failed) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned spin = 0; spin < WAIT_LIMIT; ++spin) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spin & 1023) == 1023 && *failed) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(tile) & 0x3FFFFu) >> 4);  // start address
+    d |= 1ull << 16;                                               // leading offset: unused for swizzled K-major tiles
+    d |= (unsigned long long)(1024 >> 4) << 32;                    // stride between 8-row groups
+    d |= 1ull << 46;                                               // descriptor version of sm_100
+    d |= 2ull << 61;                                               // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor of kind::f16: float accumulator, bfloat16 operands, both K-major, M = 128, N = bn.
+__device__ __forceinline__ unsigned umma_idesc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 16 consecutive float columns of this thread's accumulator lane.
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
+    unsigned r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN>
+struct Layout {
+    static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN >= 256) ? 4 : ((BN >= 128) ? 6 : 8);
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + 256;
+};
+
+__device__ __forceinline__ float bias_at(const GemmParams& p, int i) {
+    return p.bias_f ? p.bias_f[i] : (p.bias_h ? __bfloat162float(p.bias_h[i]) : 0.f);
+}
+
+// map_a: the operand that supplies the tile's 128 rows (TMEM lanes); map_b: the operand that supplies its BN
+// columns.  Without SWAP map_a = activations and map_b = weights; with SWAP the other way round.
+template <int BN, int EPI, bool SWAP>
+__global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                                       const GemmParams p) {
+    using L = Layout<BN>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(tiles + (size_t)L::STAGES * L::STAGE_BYTES);
+    unsigned long long* empty = full + L::STAGES;
+    unsigned long long* acc_full = empty + L::STAGES;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_full + 1);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // blockIdx.x runs fastest over the tiles of map_a's rows, so blocks that are resident together share map_b's tile in L2
+    const int row0 = blockIdx.x * BM;  // first row of map_a's operand
+    const int col0 = blockIdx.y * BN;  // first row of map_b's operand
+    const int k_blocks_total = (p.k + BK - 1) / BK;
+    const int kb_begin = blockIdx.z * p.k_blocks_per_split;
+    const int kb_end = min(k_blocks_total, kb_begin + p.k_blocks_per_split);
+    const int n_kb = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < L::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(L::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {  // producer
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % L::STAGES;
+                if (!mbar_wait(&empty[s], ((i / L::STAGES) & 1) ^ 1, failed)) { *failed = 1; break; }
+                unsigned char* a_tile = tiles + (size_t)s * L::STAGE_BYTES;
+                mbar_expect_tx(&full[s], L::STAGE_BYTES);
+                tma_load_2d(a_tile, &map_a, &full[s], (kb_begin + i) * BK, row0);
+                tma_load_2d(a_tile + L::A_BYTES, &map_b, &full[s], (kb_begin + i) * BK, col0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {  // tensor-core issuer
+            const unsigned idesc = umma_idesc(BN);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % L::STAGES;
+                if (!mbar_wait(&full[s], (i / L::STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
+                tc_fence_after();
+                unsigned char* a_tile = tiles + (size_t)s * L::STAGE_BYTES;
+                const unsigned long long da = umma_desc(a_tile), db = umma_desc(a_tile + L::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma_bf16(tmem, da + (unsigned long long)(k * UMMA_K * 2 / 16), db + (unsigned long long)(k * UMMA_K * 2 / 16), idesc,
+                              (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);  // the stage is free once these products have read it
+            }
+            if (ok) umma_commit(acc_full);
+        }
+    } else {  // epilogue: warps 2..5 read TMEM lane quarters 2, 3, 0, 1
+        const int quarter = warp & 3;
+        const int r = row0 + quarter * 32 + lane;  // row of map_a's operand this thread holds
+        bool ok = n_kb > 0 ? mbar_wait(acc_full, 0, failed) : true;
+        if (!ok) *failed = 1;
+        tc_fence_after();
+        if (ok) {
+            const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
+            constexpr int COLS = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+#pragma unroll 1
+            for (int c = 0; c < COLS; c += 16) {
+                float v[16];
+                if (n_kb > 0) {
+                    tmem_ld16(lane_addr + c, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                }
+                if constexpr (EPI == EPI_SWIGLU) {  // columns [0, BN/2) are gates, [BN/2, BN) the matching up columns
+                    float u[16];
+                    tmem_ld16(lane_addr + BN / 2 + c, u);
+                    const int out_col = blockIdx.y * (BN / 2) + c;
+                    if (r < p.m) {
+                        bf16* dst = reinterpret_cast<bf16*>(p.c) + (size_t)r * p.ldc + out_col;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float g = __bfloat162float(__float2bfloat16_rn(v[j])), uu = __bfloat162float(__float2bfloat16_rn(u[j]));
+                            v[j] = g / (1.0f + expf(-g)) * uu;
+                        }
+                        if (out_col + 16 <= p.n / 2 && (p.ldc & 7) == 0) {
+                            uint4 w[2];
+                            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(w);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            reinterpret_cast<uint4*>(dst)[0] = w[0];
+                            reinterpret_cast<uint4*>(dst)[1] = w[1];
+                        } else {
+                            for (int j = 0; j < 16; ++j)
+                                if (out_col + j < p.n / 2) dst[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    }
+                } else if constexpr (SWAP) {
+                    // lanes are output columns (weight rows r), TMEM columns are output rows (batch): store transposed
+                    if (r < p.n) {
+                        const float b = (EPI == EPI_PARTIAL) ? 0.f : bias_at(p, r);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int mrow = col0 + c + j;
+                            if (mrow >= p.m) break;
+                            if constexpr (EPI == EPI_BF16) reinterpret_cast<bf16*>(p.c)[(size_t)mrow * p.ldc + r] = __float2bfloat16_rn(v[j] + b);
+                            else if constexpr (EPI == EPI_F32) reinterpret_cast<float*>(p.c)[(size_t)mrow * p.ldc + r] = v[j] + b;
+                            else p.partial[((size_t)blockIdx.z * p.m + mrow) * p.n + r] = v[j];
+                        }
+                    }
+                } else {
+                    const int col = col0 + c;
+                    if (r < p.m && col < p.n) {
+                        if constexpr (EPI == EPI_BF16) {
+                            bf16* dst = reinterpret_cast<bf16*>(p.c) + (size_t)r * p.ldc + col;
+                            if (col + 16 <= p.n && (p.ldc & 7) == 0) {
+                                uint4 w[2];
+                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(w);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j] + bias_at(p, col + 2 * j), v[2 * j + 1] + bias_at(p, col + 2 * j + 1));
+                                reinterpret_cast<uint4*>(dst)[0] = w[0];
+                                reinterpret_cast<uint4*>(dst)[1] = w[1];
+                            } else {
+                                for (int j = 0; j < 16 && col + j < p.n; ++j) dst[j] = __float2bfloat16_rn(v[j] + bias_at(p, col + j));
+                            }
+                        } else if constexpr (EPI == EPI_F32) {
+                            float* dst = reinterpret_cast<float*>(p.c) + (size_t)r * p.ldc + col;
+                            for (int j = 0; j < 16 && col + j < p.n; ++j) dst[j] = v[j] + bias_at(p, col + j);
+                        } else {
+                            float* dst = p.partial + ((size_t)blockIdx.z * p.m + r) * p.n + col;
+                            for (int j = 0; j < 16 && col + j < p.n; ++j) dst[j] = v[j];
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *failed) atomicOr(p.status, HB_STATUS_WAIT_EXPIRED);
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(L::TMEM_COLS) : "memory");
+    }
+}
+
+// Sum the split-K partials in split order, add the bias, store as bfloat16 or float.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int m, int n, void* c, int ldc, int out_is_f32,
+                                     const float* bias_f, const bf16* bias_h) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)m * n) return;
+    const int row = (int)(i / n), col = (int)(i - (size_t)row * n);
+    float sum = 0.f;
+    for (int s = 0; s < splits; ++s) sum += partial[(size_t)s * m * n + i];
+    sum += bias_f ? bias_f[col] : (bias_h ? __bfloat162float(bias_h[col]) : 0.f);
+    if (out_is_f32) reinterpret_cast<float*>(c)[(size_t)row * ldc + col] = sum;
+    else reinterpret_cast<bf16*>(c)[(size_t)row * ldc + col] = __float2bfloat16_rn(sum);
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* found = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &found, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(found);
+    }
+    return fn;
+}
+
+// A [rows, k] bfloat16 matrix with row stride ld, fetched in boxes of box_rows x 64 elements with the 128-byte swizzle;
+// rows and columns beyond the matrix read as zero.
+int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return HB_BAD_ARGUMENT;
+    if (((uintptr_t)base & 15) || (ld % 8) || box_rows > 256) return HB_UNSUPPORTED_SIZE;
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : HB_BAD_ARGUMENT;
+}
+
+template <int BN, int EPI, bool SWAP>
+int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, EPI, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Layout<BN>::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    gemm_kernel<BN, EPI, SWAP><<<grid, THREADS, Layout<BN>::SMEM, stream>>>(map_a, map_b, p);
+    return launch_status();
+}
+
+template <int BN>
+int launch_swap(int epi, const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+    if (epi == EPI_BF16) return launch<BN, EPI_BF16, true>(map_w, map_x, p, grid, stream);
+    if (epi == EPI_F32) return launch<BN, EPI_F32, true>(map_w, map_x, p, grid, stream);
+    return launch<BN, EPI_PARTIAL, true>(map_w, map_x, p, grid, stream);
+}
+}  // namespace
+
+// Workspace floats hb_gemm_bf16 needs for `splits` > 1.
+HB_EXPORT long long hb_gemm_bf16_workspace(int m, int n, int splits) { return splits > 1 ? (long long)splits * m * n : 0; }
+
+// C = A W^T (+ bias).  a [m, k] (row stride lda), w [n, k] (row stride ldw), bfloat16, k-contiguous.
+//   epilogue 0: c bfloat16 [m, n]; 1: c float [m, n]; 2: SwiGLU, c bfloat16 [m, n / 2] where every 256 rows of w
+//   are 128 gate rows followed by their 128 up rows (n a multiple of 256).
+//   batch_tile 0: the activations supply the 128-row side (m large).  batch_tile 16 / 32 / 64: the weights supply it
+//   and up to batch_tile rows of a form the other side (m <= batch_tile); then `splits` may divide k, with a float
+//   workspace of hb_gemm_bf16_workspace(m, n, splits) elements.
+HB_EXPORT int hb_gemm_bf16(const void* a, int lda, const void* w, int ldw, void* c, int ldc, const float* bias_f, const void* bias_h,
+                           int m, int n, int k, int epilogue, int batch_tile, int splits, float* workspace, int* status,
+                           cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (k <= 0 || splits < 1) return HB_BAD_ARGUMENT;
+    GemmParams p{c, bias_f, (const bf16*)bias_h, workspace, m, n, k, ldc, 0, status};
+    const int k_blocks = (k + BK - 1) / BK;
+    CUtensorMap map_x, map_w;
+    if (batch_tile == 0) {
+        if (splits != 1) return HB_BAD_ARGUMENT;
+        if (epilogue == EPI_SWIGLU && n % 256) return HB_UNSUPPORTED_SIZE;
+        p.k_blocks_per_split = k_blocks;
+        if (int code = make_map(&map_x, a, m, k, lda, BM)) return code;
+        if (int code = make_map(&map_w, w, n, k, ldw, 256)) return code;
+        dim3 grid((m + BM - 1) / BM, (n + 255) / 256, 1);
+        if (grid.y > 65535) return HB_UNSUPPORTED_SIZE;
+        if (epilogue == EPI_BF16) return launch<256, EPI_BF16, false>(map_x, map_w, p, grid, stream);
+        if (epilogue == EPI_F32) return launch<256, EPI_F32, false>(map_x, map_w, p, grid, stream);
+        if (epilogue == EPI_SWIGLU) return launch<256, EPI_SWIGLU, false>(map_x, map_w, p, grid, stream);
+        return HB_BAD_ARGUMENT;
+    }
+    if ((batch_tile != 16 && batch_tile != 32 && batch_tile != 64) || m > batch_tile || epilogue == EPI_SWIGLU) return HB_BAD_ARGUMENT;
+    if (splits > k_blocks) splits = k_blocks;
+    if (splits > 1 && !workspace) return HB_BAD_ARGUMENT;
+    p.k_blocks_per_split = (k_blocks + splits - 1) / splits;
+    if (int code = make_map(&map_w, w, n, k, ldw, BM)) return code;
+    if (int code = make_map(&map_x, a, m, k, lda, batch_tile)) return code;
+    dim3 grid((n + BM - 1) / BM, 1, splits);
+    const int epi = splits > 1 ? (int)EPI_PARTIAL : epilogue;
+    int code = batch_tile == 16 ? launch_swap<16>(epi, map_w, map_x, p, grid, stream)
+             : batch_tile == 32 ? launch_swap<32>(epi, map_w, map_x, p, grid, stream)
+                                : launch_swap<64>(epi, map_w, map_x, p, grid, stream);
+    if (code || splits == 1) return code;
+    const size_t total = (size_t)m * n;
+    splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(workspace, splits, m, n, c, ldc, epilogue == EPI_F32, bias_f,
+                                                                             (const bf16*)bias_h);
+    return launch_status();
+}
