@@ -95,7 +95,6 @@ class Sampler:
         self.vocab = vocab
         self.device = device
         self.seen = seen
-        self.lib = library("sampling")
 
     @staticmethod
     def seen_words(vocab: int) -> int:
@@ -110,6 +109,6 @@ class Sampler:
         if out is None:
             out = torch.empty(rows, dtype=torch.int32, device=logits.device)
         seen_words = self.seen.shape[-1] if self.seen is not None else 0
-        check(self.lib.hb_sample(ptr(logits), i32(logits.stride(0)), i32(rows), i32(self.vocab), ptr(options), ptr(self.seen),
+        check(library("sampling").hb_sample(ptr(logits), i32(logits.stride(0)), i32(rows), i32(self.vocab), ptr(options), ptr(self.seen),
                                  i32(seen_words), ptr(out), stream_ptr()), "sample")
         return out
