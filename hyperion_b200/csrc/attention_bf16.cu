@@ -27,6 +27,7 @@ constexpr int THREADS = 128;
 constexpr int LDS = D + 8;         // padded row of a shared-memory tile, in elements (odd count of 16-byte chunks)
 constexpr int CHUNKS = D / 8;      // 16-byte chunks per row
 constexpr int LOADS = BN * CHUNKS / THREADS;  // chunks per thread per tile
+constexpr int TOKEN_STAGES = (D <= 128) ? 3 : 2;  // key/value tiles in the ring of the token shape (two blocks of it fit an SM)
 static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
 static_assert((BN * CHUNKS) % THREADS == 0, "tile loads must divide evenly");
 
@@ -156,25 +157,29 @@ __device__ __forceinline__ void process_keys(RowState& st, const bf16* qs, const
 // [need_lo, need_hi] or without a page are zero-filled; a missing page inside the range sets the status.
 __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const bf16* cache, const int* table, int table_width, int base,
                                              int need_lo, int need_hi, int kvh, int kv_heads, int page_size, int pages, int* status) {
+    // page_size is a power of two (the launcher refuses anything else).  All table entries are fetched first and the
+    // copies issued afterwards, so the table reads of a tile overlap instead of each standing in front of its copy.
+    const int shift = 31 - __clz(page_size);
     const size_t head_stride = (size_t)page_size * D;
     const size_t page_stride = 2 * (size_t)kv_heads * head_stride;
+    int page[LOADS];
+#pragma unroll
+    for (int i = 0; i < LOADS; ++i) {
+        const int pos = base + (i * THREADS + (int)threadIdx.x) / CHUNKS;
+        const int block = pos >> shift;
+        page[i] = (pos >= need_lo && pos <= need_hi) ? (block < table_width ? max(__ldg(table + block), -2) : -2) : -3;
+    }
 #pragma unroll
     for (int i = 0; i < LOADS; ++i) {
         const int chunk = i * THREADS + threadIdx.x;
         const int key = chunk / CHUNKS, c = chunk - key * CHUNKS;
         const int pos = base + key;
-        bool valid = pos >= need_lo && pos <= need_hi;
-        const bf16* src = cache;
-        if (valid) {
-            const int block = pos / page_size;
-            const int page = block < table_width ? table[block] : -1;
-            if (page < 0 || page >= pages) {
-                atomicOr(status, HB_STATUS_BAD_PAGE);
-                valid = false;
-            } else {
-                src = cache + (size_t)page * page_stride + (size_t)kvh * head_stride + (size_t)(pos - block * page_size) * D + c * 8;
-            }
-        }
+        const bool wanted = page[i] != -3;
+        const bool valid = page[i] >= 0 && page[i] < pages;
+        if (wanted && !valid) atomicOr(status, HB_STATUS_BAD_PAGE);
+        const bf16* src = valid ? cache + (size_t)page[i] * page_stride + (size_t)kvh * head_stride +
+                                      (size_t)(pos & (page_size - 1)) * D + c * 8
+                                : cache;
         cp_async16(ks + key * LDS + c * 8, src, valid);
         cp_async16(vs + key * LDS + c * 8, valid ? src + (size_t)kv_heads * head_stride : src, valid);
     }
@@ -301,22 +306,29 @@ __global__ void __launch_bounds__(THREADS) attention_tokens_kernel(AttnArgs a, c
     }
     RowState st;
     st.init();
-    if (first < last) {
-        load_kv_tile(kv, kv + BN * LDS, a.cache, table, a.table_width, start + first * BN, need_lo, pos, kvh, a.kv_heads, a.page_size, a.pages, a.status);
-    }
-    cp_async_commit();
-    for (int it = first; it < last; ++it) {
-        bf16* ks = kv + ((it - first) & 1) * 2 * BN * LDS;
-        if (it + 1 < last) {
-            bf16* nk = kv + ((it + 1 - first) & 1) * 2 * BN * LDS;
-            load_kv_tile(nk, nk + BN * LDS, a.cache, table, a.table_width, start + (it + 1) * BN, need_lo, pos, kvh, a.kv_heads, a.page_size,
+    // A ring of TOKEN_STAGES key/value tiles: TOKEN_STAGES - 1 tiles are in flight while one is consumed, which is
+    // what keeps a block streaming from HBM (one tile in flight leaves it waiting a memory latency per tile).
+    // A group is committed every iteration, empty or not, so that wait_group counts tiles.
+#pragma unroll
+    for (int s = 0; s < TOKEN_STAGES - 1; ++s) {
+        if (first + s < last) {
+            bf16* nk = kv + s * 2 * BN * LDS;
+            load_kv_tile(nk, nk + BN * LDS, a.cache, table, a.table_width, start + (first + s) * BN, need_lo, pos, kvh, a.kv_heads, a.page_size,
                          a.pages, a.status);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
         }
+        cp_async_commit();
+    }
+    for (int it = first; it < last; ++it) {
+        const int ahead = it + TOKEN_STAGES - 1;
+        if (ahead < last) {
+            bf16* nk = kv + ((ahead - first) % TOKEN_STAGES) * 2 * BN * LDS;
+            load_kv_tile(nk, nk + BN * LDS, a.cache, table, a.table_width, start + ahead * BN, need_lo, pos, kvh, a.kv_heads, a.page_size,
+                         a.pages, a.status);
+        }
+        cp_async_commit();
+        cp_async_wait<TOKEN_STAGES - 1>();
         __syncthreads();
+        bf16* ks = kv + ((it - first) % TOKEN_STAGES) * 2 * BN * LDS;
         const int base = start + it * BN;
         if (base + warp * 16 <= pos) process_keys<2>(st, qs, ks, ks + BN * LDS, warp * 16, base, hi, lo, a.scale_log2);
         __syncthreads();
@@ -380,7 +392,7 @@ __global__ void attention_merge_kernel(const int* __restrict__ items, const floa
 }
 
 constexpr size_t TILES_SMEM = (size_t)(BM + 4 * BN) * LDS * sizeof(bf16);
-constexpr size_t TOKENS_KV_SMEM = (size_t)4 * BN * LDS * sizeof(bf16);
+constexpr size_t TOKENS_KV_SMEM = (size_t)TOKEN_STAGES * 2 * BN * LDS * sizeof(bf16);
 constexpr size_t TOKENS_MERGE_SMEM = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
 constexpr size_t TOKENS_SMEM = 16 * LDS * sizeof(bf16) + (TOKENS_KV_SMEM > TOKENS_MERGE_SMEM ? TOKENS_KV_SMEM : TOKENS_MERGE_SMEM);
 
@@ -389,6 +401,7 @@ int fill_args(AttnArgs& a, const void* q, int q_stride, void* out, int out_strid
               int pages, float scale, int window, int* status) {
     if (head_dim != D) return HB_UNSUPPORTED_SIZE;
     if (kv_heads <= 0 || heads % kv_heads || page_size <= 0 || q_stride % 8 || out_stride % 2) return HB_BAD_ARGUMENT;
+    if (page_size & (page_size - 1)) return HB_UNSUPPORTED_SIZE;  // pages hold a power of two of tokens
     if (((uintptr_t)q | (uintptr_t)cache) & 15) return HB_BAD_ARGUMENT;
     a = AttnArgs{(const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_width, token_row, positions,
                  heads, kv_heads, page_size, pages, window, scale * 1.4426950408889634f, status};
