@@ -22,6 +22,17 @@ def supported(head_dim: int) -> bool:
     return head_dim % 16 == 0 and 16 <= head_dim <= 256
 
 
+def uses_tma(head_dim: int, page_size: int) -> bool:
+    """Head sizes that are multiples of 64 with pages of 8 to 64 tokens take the TMA-fed kernels."""
+    return head_dim % 64 == 0 and 8 <= page_size <= 64
+
+
+def _entry(head_dim: int, page_size: int, shape: str):
+    if uses_tma(head_dim, page_size):
+        return getattr(library("attention_tma", HB_HEAD_DIM=head_dim), f"hb_attention_tma_{shape}")
+    return getattr(library("attention_bf16", HB_HEAD_DIM=head_dim), f"hb_attention_{shape}")
+
+
 def tile_tokens(heads: int, kv_heads: int) -> int:
     return TILE_ROWS // min(heads // kv_heads, TILE_ROWS)
 
@@ -56,8 +67,7 @@ def _common(q, out, cache, block_table, token_row, positions):
 def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n_tiles, scale, window, out):
     _common(q, out, cache, block_table, token_row, positions)
     pages, _, kv_heads, page_size, head_dim = cache.shape
-    lib = library("attention_bf16", HB_HEAD_DIM=head_dim)
-    check(lib.hb_attention_tiles(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
+    check(_entry(head_dim, page_size, "tiles")(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
                                  i32(block_table.shape[1]), ptr(token_row), ptr(positions), ptr(tiles), i32(n_tiles), i32(heads),
                                  i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale), i32(window or 0),
                                  ptr(status_word(q.device)), stream_ptr()), "attention_tiles")
@@ -66,14 +76,13 @@ def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n
 def attention_tokens(q, heads, cache, block_table, token_row, positions, items, n_items, splits, scale, window, out, workspace=None):
     _common(q, out, cache, block_table, token_row, positions)
     pages, _, kv_heads, page_size, head_dim = cache.shape
-    lib = library("attention_bf16", HB_HEAD_DIM=head_dim)
     if splits > 1:
         need = n_items * heads * splits * (head_dim + 2)
         if workspace is None:
             workspace = torch.empty(need, dtype=torch.float32, device=q.device)
         elif workspace.numel() < need or workspace.dtype != torch.float32:
             raise KernelError(f"attention_tokens: workspace of {need} floats needed")
-    check(lib.hb_attention_tokens(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
+    check(_entry(head_dim, page_size, "tokens")(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
                                   i32(block_table.shape[1]), ptr(token_row), ptr(positions), ptr(items), i32(n_items), i32(splits),
                                   ptr(workspace), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale),
                                   i32(window or 0), ptr(status_word(q.device)), stream_ptr()), "attention_tokens")

@@ -76,7 +76,12 @@ class GroupedQueryAttention(Mixer):
 
     def kernel_modules(self):
         modules = [("elementwise", {})]
-        modules.append(("attention_bf16", {"HB_HEAD_DIM": self.head_dim}) if self.fast else ("attention_generic", {}))
+        if self.fast:  # which of the two is launched depends on the page size of the cache it is given
+            modules.append(("attention_bf16", {"HB_HEAD_DIM": self.head_dim}))
+            if self.head_dim % 64 == 0:
+                modules.append(("attention_tma", {"HB_HEAD_DIM": self.head_dim}))
+        else:
+            modules.append(("attention_generic", {}))
         if self.dtype == torch.float32:
             modules.append(("sgemm_f32", {}))
         if self.position is not None:
