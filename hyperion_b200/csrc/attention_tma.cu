@@ -228,8 +228,15 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // the ring starts as zeros: pages that are never fetched must not leave NaN bit patterns under masked keys
-    for (int e = tid; e < STAGES * STAGE_BYTES / 16; e += THREADS) reinterpret_cast<uint4*>(ring)[e] = make_uint4(0, 0, 0, 0);
+    // Pages that are not fetched (before a window's start, beyond the last position) leave whatever the stage held
+    // before under masked keys; that is earlier key/value data, which is finite, unless the stage was never written.
+    // So a stage is zeroed when its first tile is one of the two that can be fetched in part.
+    for (int s = 0; s < STAGES && first + s < last; ++s) {
+        const int tile = first + s;
+        if (tile != n_tiles - 1 && !(tile == 0 && need_lo > start)) continue;
+        uint4* stage = reinterpret_cast<uint4*>(ring + (size_t)s * STAGE_BYTES);
+        for (int e = tid; e < STAGE_BYTES / 16; e += THREADS) stage[e] = make_uint4(0, 0, 0, 0);
+    }
     // queries: virtual row v = token * gc + head
     for (int e = tid; e < ROWS * (D / 8); e += THREADS) {
         const int v = e / (D / 8), c = e - v * (D / 8);
@@ -244,40 +251,48 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
 
     if (warp == CONSUMERS) {
         // ------------------------------------------------------------------ producer
-        if (lane == 0) {
-            const int shift = 31 - __clz(a.page_size);
-            const int pages_per_tile = BN >> shift;
-            const unsigned page_bytes = 2u * a.page_size * D * 2u;
-            for (int it = first; it < last; ++it) {
-                const int s = (it - first) % STAGES, round = (it - first) / STAGES;
-                if (!mbar_wait(&empty[s], (round & 1) ^ 1, failed)) { *failed = 1; atomicOr(a.status, HB_STATUS_WAIT_EXPIRED); break; }
-                const int base = start + it * BN;
-                int page[8];
-                unsigned valid = 0;
-#pragma unroll
-                for (int p = 0; p < 8; ++p) {
-                    page[p] = -1;
-                    const int k0 = base + p * a.page_size;
-                    if (p < pages_per_tile && k0 <= pos_last && k0 + a.page_size - 1 >= need_lo) {
-                        const int block = k0 >> shift;
-                        const int id = block < a.table_width ? __ldg(table + block) : -1;
-                        if (id >= 0 && id < a.pages) { page[p] = id; ++valid; }
-                        else atomicOr(a.status, HB_STATUS_BAD_PAGE);
-                    }
-                }
-                bf16* stage = reinterpret_cast<bf16*>(ring + (size_t)s * STAGE_BYTES);
+        // The whole warp takes part: lane p looks up page p of the tile, lane 0 arms the barrier with the byte count,
+        // then every lane issues one copy (page, K or V, 64-column panel), so the copies of a tile start together.
+        const int shift = 31 - __clz(a.page_size);
+        const int pages_per_tile = BN >> shift;
+        const int ops = pages_per_tile * 2 * HALVES;
+        const unsigned page_bytes = 2u * a.page_size * D * 2u;
+        if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
+        for (int it = first; it < last; ++it) {
+            const int s = (it - first) % STAGES, round = (it - first) / STAGES;
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(&empty[s], (round & 1) ^ 1, failed) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                if (lane == 0) { *failed = 1; atomicOr(a.status, HB_STATUS_WAIT_EXPIRED); }
+                break;
+            }
+            const int base = start + it * BN;
+            int my_page = -1;
+            const int k0 = base + lane * a.page_size;
+            if (lane < pages_per_tile && k0 <= pos_last && k0 + a.page_size - 1 >= need_lo) {
+                const int block = k0 >> shift;
+                const int id = block < a.table_width ? __ldg(table + block) : -1;
+                if (id >= 0 && id < a.pages) my_page = id;
+                else atomicOr(a.status, HB_STATUS_BAD_PAGE);
+            }
+#if defined(HB_EXPERIMENT) && HB_EXPERIMENT == 2
+            my_page = -1;  // timing experiment: nothing is fetched
+#endif
+            const unsigned valid = __popc(__ballot_sync(0xffffffffu, my_page >= 0));
+            if (lane == 0) {
                 if (valid) mbar_expect_tx(&full[s], valid * page_bytes); else mbar_arrive(&full[s]);
-#pragma unroll
-                for (int p = 0; p < 8; ++p) {
-                    if (page[p] < 0) continue;
-                    const int row_k = ((page[p] * 2 + 0) * a.kv_heads + kvh) * a.page_size;
-                    const int row_v = ((page[p] * 2 + 1) * a.kv_heads + kvh) * a.page_size;
-#pragma unroll
-                    for (int h = 0; h < HALVES; ++h) {
-                        tma_load_2d(stage + h * PANEL + p * a.page_size * 64, &kv_map, &full[s], h * 64, row_k);
-                        tma_load_2d(stage + TILE_ELEMS + h * PANEL + p * a.page_size * 64, &kv_map, &full[s], h * 64, row_v);
-                    }
-                }
+            }
+            __syncwarp();
+            bf16* stage = reinterpret_cast<bf16*>(ring + (size_t)s * STAGE_BYTES);
+            for (int op0 = 0; op0 < ops; op0 += 32) {
+                const int op = op0 + lane;
+                const int p = min(op, ops - 1) / (2 * HALVES), rest = op % (2 * HALVES);
+                const int which = rest / HALVES, h = rest - which * HALVES;
+                const int page = __shfl_sync(0xffffffffu, my_page, p);
+                if (op < ops && page >= 0)
+                    tma_load_2d(stage + which * TILE_ELEMS + h * PANEL + p * a.page_size * 64, &kv_map, &full[s], h * 64,
+                                ((page * 2 + which) * a.kv_heads + kvh) * a.page_size);
             }
         }
         return;
@@ -304,9 +319,13 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
         if (!mbar_wait(&full[s], round & 1, failed)) { *failed = 1; atomicOr(a.status, HB_STATUS_WAIT_EXPIRED); ok = false; break; }
         const bf16* ks = reinterpret_cast<const bf16*>(ring + (size_t)s * STAGE_BYTES);
         const int base = start + it * BN;
+#if defined(HB_EXPERIMENT) && HB_EXPERIMENT == 1
+        if (base < 0) {  // timing experiment: consumers only hand the stages back
+#else
         if (TOKENS) {
+#endif
             if (base + warp * 16 <= pos_last) process_keys<2>(st, qs, ks, ks + TILE_ELEMS, warp * 16, base, hi, lo, a.scale_log2);
-        } else {
+        } else if (!TOKENS) {
             if (warp_has_rows && base <= warp_hi && base + BN - 1 >= warp_lo)
                 process_keys<BN / 8>(st, qs + warp * 16 * LDQ, ks, ks + TILE_ELEMS, 0, base, hi, lo, a.scale_log2);
         }

@@ -15,7 +15,7 @@ from .native import KernelError, check, f32, i32, library, ptr, require_cuda, st
 TOKEN_SHAPE_MAX = 4
 TILE_ROWS = 64
 KEY_TILE = 64
-TARGET_BLOCKS = 148 * 3
+TARGET_BLOCKS = 148 * 2  # two blocks of the token shape fit one SM
 
 
 def supported(head_dim: int) -> bool:
@@ -51,11 +51,11 @@ def plan(rows, tokens_per_tile: int) -> tuple[list[int], list[int]]:
 
 
 def choose_splits(n_items: int, heads: int, kv_heads: int, longest_context: int) -> int:
-    """Splits of the keys for the token shape: enough blocks to fill the GPU, at least 4 key tiles each."""
+    """Splits of the keys for the token shape: about two blocks per SM in all, at least 3 key tiles each."""
     group = heads // kv_heads
     blocks = n_items * kv_heads * ((group + 15) // 16)
     key_tiles = -(-longest_context // KEY_TILE)
-    return max(1, min(-(-TARGET_BLOCKS // max(1, blocks)), key_tiles // 4, 64))
+    return max(1, min(TARGET_BLOCKS // max(1, blocks), key_tiles // 3, 64))
 
 
 def _common(q, out, cache, block_table, token_row, positions):
