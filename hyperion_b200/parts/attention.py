@@ -82,8 +82,7 @@ class GroupedQueryAttention(Mixer):
                 modules.append(("attention_tma", {"HB_HEAD_DIM": self.head_dim}))
         else:
             modules.append(("attention_generic", {}))
-        if self.dtype == torch.float32:
-            modules.append(("sgemm_f32", {}))
+        modules.append(("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {}))
         if self.position is not None:
             modules += self.position.kernel_modules()
         return modules

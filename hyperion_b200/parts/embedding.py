@@ -55,7 +55,7 @@ class LinearHead(Head):
         self.weight = table
 
     def kernel_modules(self):
-        return [("sgemm_f32", {})] if self.dtype == torch.float32 else []
+        return [("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
 
     def forward(self, x):
         return ops.linear(x, self.weight, None, torch.float32)

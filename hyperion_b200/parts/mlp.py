@@ -37,7 +37,7 @@ class SwiGLU(FeedForward):
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def kernel_modules(self):
-        return [("elementwise", {})] + ([("sgemm_f32", {})] if self.dtype == torch.float32 else [])
+        return [("elementwise", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
 
     def forward(self, x, step):
         gate_up = ops.linear(x, self.w_gate_up, None, self.dtype)

@@ -51,14 +51,14 @@ def random_ids(seed: int, count: int, vocab: int) -> list[int]:
     return torch.randint(0, vocab, (count,), generator=generator).tolist()
 
 
-def run_trace(folder: Path, dtype: str, steps: list[dict], out: Path, max_tokens: int, page_size: int = 16) -> dict[int, np.ndarray]:
+def run_trace(folder: Path, dtype: str, steps: list[dict], out: Path, max_tokens: int, page_size: int = 16, env: dict | None = None) -> dict[int, np.ndarray]:
     """Feed ``steps`` to bin/trace_run and read back the logits of every step that wanted some."""
     out = Path(out)
     out.mkdir(parents=True, exist_ok=True)
     text = "".join(json.dumps(step) + "\n" for step in steps)
     command = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
                "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
-    done = subprocess.run(command, input=text, capture_output=True, text=True, timeout=900)
+    done = subprocess.run(command, input=text, capture_output=True, text=True, timeout=900, env={**os.environ, **(env or {})})
     assert done.returncode == 0, f"trace_run failed:\n{done.stdout[-2000:]}\n{done.stderr[-4000:]}"
     finished = [line for line in done.stdout.splitlines() if line.startswith("done ")]
     assert [int(line.split()[1]) for line in finished] == [s["step"] for s in steps]

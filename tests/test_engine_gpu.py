@@ -200,3 +200,32 @@ def test_a_bad_step_is_refused_whole(folders):
     engine.cache.check()
     out = engine.step([StepEntry("a", [7], [0])])
     assert out.shape == (1, config.vocab_size)
+
+
+def test_real_layer_widths_against_the_plain_implementation(tmp_path):
+    """One layer with the widths of the 7B configuration (hidden 3584, 28/4 heads of 128, intermediate 18944,
+    vocabulary 152064, tied head): a 70-token prompt in two portions and four decoded tokens, float32 and
+    bfloat16, against the plain float64 implementation.  Tolerances declared beforehand: float32 1e-4 of
+    the largest logit (reductions of up to 18944 terms), bfloat16 as for the tiny models."""
+    from hyperion_b200.api import Engine
+    from hyperion_b200.config import Qwen2Config
+    from hyperion_b200.engine.batch import StepEntry
+    from hyperion_b200.weights import write_model_folder
+
+    config = Qwen2Config(num_hidden_layers=1, hidden_size=3584, intermediate_size=18944, num_attention_heads=28, num_key_value_heads=4,
+                         head_dim=128, vocab_size=152064, max_position_embeddings=4096, rope_theta=1e6, rms_norm_eps=1e-6,
+                         tie_word_embeddings=True)
+    folder = write_model_folder(tmp_path / "wide", "Qwen2ForCausalLM", config, seed=5, std=0.02)
+    ids = random_ids(55, 74, config.vocab_size)
+    want = plain_logits(folder, ids)
+    for dtype, tolerance in (("float32", 1e-4), ("bfloat16", TOLERANCE["bfloat16"])):
+        engine = Engine.from_folder(folder, dtype=dtype, page_size=16, max_tokens=256, max_requests=2)
+        got = [engine.step([StepEntry("r", ids[:47], [0, 46])]).cpu().numpy(), engine.step([StepEntry("r", ids[47:70], [22])]).cpu().numpy()]
+        assert relative_error(got[0], want[[0, 46]]) <= tolerance
+        assert relative_error(got[1], want[[69]]) <= tolerance
+        for k in range(70, 74):
+            logits = engine.step([StepEntry("r", [ids[k]], [0])]).cpu().numpy()
+            assert relative_error(logits, want[[k]]) <= tolerance, (dtype, k)
+        engine.check()
+        del engine
+        torch.cuda.empty_cache()

@@ -122,3 +122,12 @@ class TestReplay:
         assert peak < sum(round64(len(ids)) for ids in requests.values())  # the pool cannot hold all: pages are reused
         results = run_trace(folder, dtype, steps, tmp_path, max_tokens=peak)
         compare_steps(steps, results, reference, TOLERANCE[dtype])
+
+
+def test_mixed_replay_with_every_product_on_the_tcgen05_kernel(model, tmp_path):
+    """The same mixed trace in bfloat16 with HYPERION_B200_GEMM=own: every projection, large or small, goes through
+    the package's tcgen05 kernel instead of the library."""
+    name, folder, requests, reference = model
+    steps, peak = mixed_steps(requests)
+    results = run_trace(folder, "bfloat16", steps, tmp_path, max_tokens=peak, env={"HYPERION_B200_GEMM": "own"})
+    compare_steps(steps, results, reference, TOLERANCE["bfloat16"])
