@@ -365,3 +365,37 @@ def test_sampler_frequencies_follow_the_softmax():
     expected = torch.softmax(logits[0].double(), 0).numpy() * draws
     chi2 = float(((observed - expected) ** 2 / expected).sum())
     assert chi2 < 45.0  # 15 degrees of freedom: p = 0.0001 at 42.6... a wrong sampler lands in the hundreds
+
+
+@pytest.mark.parametrize("kind", ["float32", "bfloat16"])
+def test_attention_at_the_edges_of_window_page_and_tile(kind):
+    """One key is made to dominate (its score stands far above the rest) and placed just inside the window, just
+    outside it, on the last slot of a page and on the first slot of the next, at a key tile's edge: the output must be
+    that key's value when it is visible and must not contain it when it is not."""
+    heads, kv_heads, head_dim, page_size, window = 4, 2, 64, 16, 40
+    dtype = torch.float32 if kind == "float32" else torch.bfloat16
+    context = 200
+    query_pos = context - 1
+    direction = rnd(head_dim, seed=31).to(dtype)
+    for spot, visible in ((query_pos - window + 1, True), (query_pos - window, False), (175, True), (176, True), (191, True), (192, True),
+                          (query_pos, True), (query_pos - window - 17, False)):
+        cache, table, keys, values = paged_case(kv_heads, head_dim, page_size, [context], dtype, seed=9)
+        keys[0][spot] = direction * 4
+        cache[table[0, spot // page_size], 0, :, spot % page_size] = direction * 4
+        rows = [(0, query_pos - 5, 6)] if spot % 2 else [(0, query_pos, 1)]  # a short portion (tile shape) or one token
+        tokens = rows[0][2]
+        q = (direction.float() * 4).repeat(tokens, heads + 2 * kv_heads).to(dtype)
+        scale = head_dim ** -0.5
+        if kind == "float32":
+            token_row = torch.zeros(tokens, dtype=torch.int32)
+            positions = torch.arange(rows[0][1], rows[0][1] + tokens, dtype=torch.int32)
+            out = ops().attention_generic(q.to(DEV), heads, cache.to(DEV), table.to(DEV), token_row.to(DEV), positions.to(DEV), scale, window)
+            outs = {1: out}
+        else:
+            outs = run_fast_attention(q, heads, cache, table, rows, scale, window)
+        want = reference_attention(q[:, : heads * head_dim].double().view(tokens, heads, head_dim), keys, values, rows, scale, window)
+        for out in outs.values():
+            got = out.cpu().double().view(tokens, heads, head_dim)
+            assert (got - want).abs().max() <= (1e-5 if kind == "float32" else 2 ** -7) * want.abs().max(), (spot, visible)
+            distance = (got[-1, 0] - values[0][spot, 0].double()).abs().max()
+            assert (distance < 0.05) == visible, (spot, visible, float(distance))
