@@ -141,7 +141,7 @@ def time_decode(engine, batch: int, steps: int, warmup: int) -> dict:
     for s in range(warmup):
         one(s)
     torch.cuda.synchronize()
-    launches_before = native.LAUNCHES[0]
+    launches_before = native.LAUNCHES[0] + getattr(engine.runner, "graph_launches", 0)
     host_start = time.perf_counter()
     start.record()
     for s in range(warmup, warmup + steps):
@@ -150,7 +150,7 @@ def time_decode(engine, batch: int, steps: int, warmup: int) -> dict:
     torch.cuda.synchronize()
     host_ms = (time.perf_counter() - host_start) * 1e3
     ms = start.elapsed_time(stop)
-    launches = native.LAUNCHES[0] - launches_before + getattr(engine.runner, "graph_launches", 0)
+    launches = native.LAUNCHES[0] + getattr(engine.runner, "graph_launches", 0) - launches_before
     mean_context = PROMPT + warmup + (steps + 1) / 2
     h2d = engine.runner.packer._cursor * 4
     for name in names:

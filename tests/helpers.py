@@ -27,7 +27,11 @@ TINY_A = Qwen2Config(num_hidden_layers=2, hidden_size=64, intermediate_size=176,
 TINY_B = Qwen2Config(num_hidden_layers=3, hidden_size=192, intermediate_size=400, num_attention_heads=6, num_key_value_heads=1,
                      head_dim=32, vocab_size=523, max_position_embeddings=1024, rope_theta=1e6, rms_norm_eps=1e-5,
                      tie_word_embeddings=False)
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1)}
+# A third one whose head size (64) and page size take the TMA-fed attention kernels; A and B (16, 32) take the cp.async ones.
+TINY_C = Qwen2Config(num_hidden_layers=2, hidden_size=256, intermediate_size=264, num_attention_heads=4, num_key_value_heads=2,
+                     head_dim=64, vocab_size=300, max_position_embeddings=512, rope_theta=50000.0, rms_norm_eps=1e-6,
+                     tie_word_embeddings=False)
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
 WEIGHT_STD = 0.06  # larger than an initialiser's 0.02 so that attention is peaked and logits are O(1)
 
 # Declared before the first run. float32: the engine's fixed-order float arithmetic against the

@@ -9,7 +9,7 @@ from helpers import TINY, TOLERANCE, compare_steps, make_folder, plain_logits, r
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [70, 45, 100, 33, 90, 61], "B": [130, 40, 77, 200, 35, 96]}
+LENGTHS = {"A": [70, 45, 100, 33, 90, 61], "B": [130, 40, 77, 200, 35, 96], "C": [150, 37, 66, 210, 80, 129]}
 
 
 def requests_for(name: str) -> dict[str, list[int]]:
@@ -130,4 +130,23 @@ def test_mixed_replay_with_every_product_on_the_tcgen05_kernel(model, tmp_path):
     name, folder, requests, reference = model
     steps, peak = mixed_steps(requests)
     results = run_trace(folder, "bfloat16", steps, tmp_path, max_tokens=peak, env={"HYPERION_B200_GEMM": "own"})
+    compare_steps(steps, results, reference, TOLERANCE["bfloat16"])
+
+
+@pytest.fixture(scope="module")
+def model_c(tmp_path_factory):
+    folder = make_folder(tmp_path_factory.mktemp("model_C"), "C")
+    requests = requests_for("C")
+    return folder, requests, {rid: plain_logits(folder, ids) for rid, ids in requests.items()}
+
+
+@pytest.mark.parametrize("cutting", ["whole", "mixed"])
+def test_head_size_64_takes_the_tma_attention(model_c, cutting, tmp_path):
+    """A configuration with heads of 64 and pages of 16 tokens runs the TMA-fed attention kernels in bfloat16."""
+    folder, requests, reference = model_c
+    if cutting == "whole":
+        steps, peak = whole_steps(requests), round64(max(map(len, requests.values())))
+    else:
+        steps, peak = mixed_steps(requests)
+    results = run_trace(folder, "bfloat16", steps, tmp_path, max_tokens=peak)
     compare_steps(steps, results, reference, TOLERANCE["bfloat16"])
