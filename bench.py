@@ -136,7 +136,7 @@ def time_decode(engine, batch: int, steps: int, warmup: int) -> dict:
 
     def one(s):
         logits = engine.runner.step([StepEntry(name, [feed[s][i]], [0]) for i, name in enumerate(names)], options)
-        engine.sampler.sample(logits, engine.runner.last_context.extra["sampling_options"])
+        engine.sampler.sample(logits, engine.runner.last_context.extra["sampling_options"], all_greedy=True)
 
     for s in range(warmup):
         one(s)

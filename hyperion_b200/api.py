@@ -164,7 +164,8 @@ class Engine:
                 continue
             sampled = {}
             if logits is not None:
-                tokens = self.sampler.sample(logits, self.runner.last_context.extra["sampling_options"])
+                tokens = self.sampler.sample(logits, self.runner.last_context.extra["sampling_options"],
+                                             all_greedy=all(params_of[row.request].greedy for row in plan.rows if row.sample))
                 host = self._token_staging[: tokens.numel()]
                 host.copy_(tokens, non_blocking=True)
                 torch.cuda.current_stream().synchronize()

@@ -63,17 +63,60 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     }
 }
 
+// The same with a row's values held in registers between the two passes (rows of up to 8 values per thread): one trip
+// to memory instead of two, which is what counts when a decode step has only a handful of rows.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_cached_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ weight,
+                                          TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps, int write_h) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* hrow = h + (size_t)s * hidden;
+    const TD* drow = delta ? delta + (size_t)s * hidden : nullptr;
+    float v[8], w[8];
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        v[j] = 0.f;
+        w[j] = 0.f;
+        if (i < hidden) {
+            v[j] = hrow[i];
+            w[j] = weight[i];
+            if (drow) v[j] += to_float(drow[i]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {  // the same order of additions per thread as the uncached kernel
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < hidden) {
+            if (drow && write_h) hrow[i] = v[j];
+            sum = fmaf(v[j], v[j], sum);
+        }
+    }
+    const float total = block_sum(sum, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    TO* orow = out + (size_t)r * hidden;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < hidden) orow[i] = from_float<TO>(v[j] * inv * w[j]);
+    }
+}
+
 HB_EXPORT int hb_add_rmsnorm(float* h, const void* delta, int delta_is_bf16, const float* weight, void* out,
                              int out_is_bf16, const int* rows, int n_rows, int hidden, float eps, int write_h,
                              cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const int threads = hidden >= 4096 ? 1024 : (hidden >= 1024 ? 512 : 256);
-#define HB_NORM(TD, TO) \
-    add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, write_h)
+    const bool cached = hidden <= 8 * threads;  // both kernels add a thread's squares in the same order, so they agree bit for bit
+#define HB_NORM(TD, TO)                                                                                                                    \
+    if (cached) add_rmsnorm_cached_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, write_h); \
+    else add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, write_h)
     if (delta_is_bf16) {
-        if (out_is_bf16) HB_NORM(__nv_bfloat16, __nv_bfloat16); else HB_NORM(__nv_bfloat16, float);
+        if (out_is_bf16) { HB_NORM(__nv_bfloat16, __nv_bfloat16); } else { HB_NORM(__nv_bfloat16, float); }
     } else {
-        if (out_is_bf16) HB_NORM(float, __nv_bfloat16); else HB_NORM(float, float);
+        if (out_is_bf16) { HB_NORM(float, __nv_bfloat16); } else { HB_NORM(float, float); }
     }
 #undef HB_NORM
     return launch_status();
@@ -212,13 +255,15 @@ __global__ void rope_kv_store_kernel(T* __restrict__ x, int stride, int q_heads,
     const int block = pos / page_size;
     const int page = block < table_width ? block_table[(size_t)token_row[t] * table_width + block] : -1;
     const bool page_ok = page >= 0 && page < pages;
-    if (!page_ok && threadIdx.x == 0) atomicOr(status, HB_STATUS_BAD_PAGE);
+    if (!page_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, HB_STATUS_BAD_PAGE);
     const int slot = pos - block * page_size;
     T* row = x + (size_t)t * stride;
     const float2* cs = table + (size_t)pos * half;
     const size_t page_base = (size_t)(page_ok ? page : 0) * 2 * kv_heads * page_size * head_dim;
     const int rotated = (q_heads + kv_heads) * half;
-    for (int e = threadIdx.x; e < rotated + kv_heads * half; e += blockDim.x) {
+    // blockIdx.y cuts a token's work into slices of blockDim.x element pairs, so that a decode step of a few tokens
+    // still spreads over many blocks
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < rotated + kv_heads * half; e += gridDim.y * blockDim.x) {
         if (e < rotated) {
             const int head = e / half, i = e - head * half;
             const float2 c = cs[i];
@@ -245,12 +290,15 @@ HB_EXPORT int hb_rope_kv_store(void* x, int is_bf16, int tokens, int stride, int
                                int table_width, const int* token_row, int page_size, int pages, int* status, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (head_dim & 1) return HB_UNSUPPORTED_SIZE;
+    const int pairs = (q_heads + 2 * kv_heads) * (head_dim / 2);
+    const int slices = tokens >= 512 ? 1 : min(16, (pairs + 255) / 256);
+    const dim3 grid(tokens, slices);
     if (is_bf16)
-        rope_kv_store_kernel<<<tokens, 256, 0, stream>>>((__nv_bfloat16*)x, stride, q_heads, kv_heads, head_dim, positions, (const float2*)table,
-                                                         max_positions, (__nv_bfloat16*)cache, block_table, table_width, token_row, page_size, pages, status);
+        rope_kv_store_kernel<<<grid, 256, 0, stream>>>((__nv_bfloat16*)x, stride, q_heads, kv_heads, head_dim, positions, (const float2*)table,
+                                                       max_positions, (__nv_bfloat16*)cache, block_table, table_width, token_row, page_size, pages, status);
     else
-        rope_kv_store_kernel<<<tokens, 256, 0, stream>>>((float*)x, stride, q_heads, kv_heads, head_dim, positions, (const float2*)table,
-                                                         max_positions, (float*)cache, block_table, table_width, token_row, page_size, pages, status);
+        rope_kv_store_kernel<<<grid, 256, 0, stream>>>((float*)x, stride, q_heads, kv_heads, head_dim, positions, (const float2*)table,
+                                                       max_positions, (float*)cache, block_table, table_width, token_row, page_size, pages, status);
     return launch_status();
 }
 

@@ -253,6 +253,80 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     }
 #undef HB_KEPT
 }
+
+
+// Argmax of every row in two launches (for steps in which every row is greedy): `chunks` blocks per row find the best
+// of their slice, then one warp per row picks among them; lowest index on ties, NaN never wins.
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, int row_stride, int vocab, int chunks, float* __restrict__ best_value,
+                                      int* __restrict__ best_index) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const int row = blockIdx.x, chunk = blockIdx.y;
+    const int per = (vocab + chunks - 1) / chunks;
+    const int begin = chunk * per, end = min(vocab, begin + per);
+    const float* z = logits + (size_t)row * row_stride;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = z[i];
+        if (v > bv || (bi == 0x7fffffff && v == v)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (si[w] != 0x7fffffff && (bi == 0x7fffffff || sv[w] > bv || (sv[w] == bv && si[w] < bi))) { bv = sv[w]; bi = si[w]; }
+        best_value[row * chunks + chunk] = bv;
+        best_index[row * chunks + chunk] = bi;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ best_value, const int* __restrict__ best_index, int chunks,
+                                    const int* __restrict__ options_raw, unsigned* __restrict__ seen_all, int seen_words, int* __restrict__ tokens) {
+    const int row = blockIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = threadIdx.x; c < chunks; c += 32) {
+        const float ov = best_value[row * chunks + c];
+        const int oi = best_index[row * chunks + c];
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) {
+        if (bi == 0x7fffffff) bi = 0;
+        tokens[row] = bi;
+        const int slot = options_raw[row * 8 + 7];
+        if (seen_all && slot >= 0) atomicOr(&seen_all[(size_t)slot * seen_words + (bi >> 5)], 1u << (bi & 31));
+    }
+}
+}  // namespace
+
+// workspace: 2 * rows * chunks words (values then indices).
+HB_EXPORT int hb_argmax(const float* logits, int row_stride, int rows, int vocab, int chunks, void* workspace, const int* options,
+                        unsigned* seen, int seen_words, int* tokens, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || chunks < 1 || chunks > 1024 || !workspace) return HB_BAD_ARGUMENT;
+    float* values = reinterpret_cast<float*>(workspace);
+    int* indices = reinterpret_cast<int*>(workspace) + (size_t)rows * chunks;
+    argmax_partial_kernel<<<dim3(rows, chunks), 256, 0, stream>>>(logits, row_stride, vocab, chunks, values, indices);
+    int code = launch_status();
+    if (code) return code;
+    argmax_final_kernel<<<rows, 32, 0, stream>>>(values, indices, chunks, options, seen, seen_words, tokens);
+    return launch_status();
+}
+
+namespace {
 }  // namespace
 
 // options: 8 int32 words per row: temperature, top_p, repetition penalty (float bits), top_k, seed low,

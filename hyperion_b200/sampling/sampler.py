@@ -100,8 +100,12 @@ class Sampler:
     def seen_words(vocab: int) -> int:
         return (vocab + 31) // 32
 
-    def sample(self, logits: torch.Tensor, options: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``logits`` [rows, vocab] float32; ``options`` [rows, 8] int32 on the device (see ``pack_options``)."""
+    ARGMAX_CHUNKS = 32
+
+    def sample(self, logits: torch.Tensor, options: torch.Tensor, out: Optional[torch.Tensor] = None, all_greedy: bool = False) -> torch.Tensor:
+        """``logits`` [rows, vocab] float32; ``options`` [rows, 8] int32 on the device (see ``pack_options``).
+        ``all_greedy``: the caller knows every row has temperature 0; the argmax then runs spread over many blocks
+        per row instead of one."""
         require_cuda(logits, options)
         rows = logits.shape[0]
         if logits.dtype != torch.float32 or logits.stride(-1) != 1 or logits.shape[1] != self.vocab:
@@ -109,6 +113,12 @@ class Sampler:
         if out is None:
             out = torch.empty(rows, dtype=torch.int32, device=logits.device)
         seen_words = self.seen.shape[-1] if self.seen is not None else 0
+        if all_greedy:
+            chunks = self.ARGMAX_CHUNKS
+            workspace = torch.empty(2 * rows * chunks, dtype=torch.int32, device=logits.device)
+            check(library("sampling").hb_argmax(ptr(logits), i32(logits.stride(0)), i32(rows), i32(self.vocab), i32(chunks), ptr(workspace),
+                                                ptr(options), ptr(self.seen), i32(seen_words), ptr(out), stream_ptr()), "argmax")
+            return out
         check(library("sampling").hb_sample(ptr(logits), i32(logits.stride(0)), i32(rows), i32(self.vocab), ptr(options), ptr(self.seen),
                                  i32(seen_words), ptr(out), stream_ptr()), "sample")
         return out

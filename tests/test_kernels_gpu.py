@@ -308,6 +308,10 @@ def test_sampler_greedy_ties_and_nan(vocab):
     options = torch.tensor([pack_options(GREEDY, 0, -1) for _ in range(4)], dtype=torch.int32, device=DEV)
     got = sampler.sample(logits.to(DEV), options).cpu().tolist()
     assert got[:3] == [7, 400, vocab - 1] and got[3] == int(torch.argmax(logits[3]))
+    spread = sampler.sample(logits.to(DEV), options, all_greedy=True).cpu().tolist()  # the many-blocks-per-row argmax
+    assert spread == got
+    logits[0, [vocab - 2, 3]] = 11.0  # a tie across two blocks' slices
+    assert sampler.sample(logits.to(DEV), options, all_greedy=True).cpu().tolist()[0] == 3
 
 
 @pytest.mark.parametrize("vocab, params", [
