@@ -83,16 +83,20 @@ class MetadataPacker:
     def begin(self) -> None:
         self._items: list[tuple[str, int, int, tuple[int, ...]]] = []
         self._cursor = 0
-        self._pending: list[tuple[int, torch.Tensor]] = []
+        self._flat: list[int] = []
 
     def add(self, name: str, values: Any, shape: Optional[tuple[int, ...]] = None) -> None:
-        tensor = torch.as_tensor(values, dtype=torch.int32).reshape(-1)
-        count = tensor.numel()
+        """Append an int32 array (a list of ints, or a tensor); every array starts on a 16-byte boundary."""
+        if isinstance(values, torch.Tensor):
+            values = values.reshape(-1).tolist()
+        count = len(values)
         shape = shape or (count,)
-        start = self._cursor
-        self._cursor += (count + 3) // 4 * 4  # keep every array 16-byte aligned
-        self._items.append((name, start, count, shape))
-        self._pending.append((start, tensor))
+        self._items.append((name, self._cursor, count, shape))
+        self._flat.extend(values)
+        padding = -count % 4
+        if padding:
+            self._flat.extend((0,) * padding)
+        self._cursor += count + padding
 
     def finish(self) -> dict[str, torch.Tensor]:
         if self._cursor > self.capacity:
@@ -101,9 +105,8 @@ class MetadataPacker:
         if self.events[self._index] is not None:
             self.events[self._index].synchronize()
         host = self.hosts[self._index]
-        for start, tensor in self._pending:
-            host[start : start + tensor.numel()] = tensor
         if self._cursor:
+            host[: self._cursor] = torch.tensor(self._flat, dtype=torch.int32)  # one conversion for the whole step
             self.dev[: self._cursor].copy_(host[: self._cursor], non_blocking=True)
             if self.device.type == "cuda":
                 event = torch.cuda.Event()
