@@ -202,6 +202,44 @@ def time_e2e(engine, batch: int, steps: int, warmup: int) -> dict:
             "d2h_bytes": batch * 4}
 
 
+def other_workload(name: str) -> int:
+    """The two larger workloads: continuous batching through ``Engine.generate`` with host tokens in and out."""
+    import torch
+
+    from hyperion_b200.api import Engine
+    from hyperion_b200.config import Qwen2Config
+    from hyperion_b200.sampling import SamplingParams
+
+    if name == "mixed-1.5b":
+        config = Qwen2Config(num_hidden_layers=28, hidden_size=1536, intermediate_size=8960, num_attention_heads=12, num_key_value_heads=2,
+                             head_dim=128, vocab_size=151936, max_position_embeddings=32768, rope_theta=1e6, rms_norm_eps=1e-6,
+                             tie_word_embeddings=True)
+        lengths = torch.randint(16, 4097, (128,), generator=torch.Generator().manual_seed(0)).tolist()
+        new_tokens, max_batch, budget = 256, 128, 8192
+    else:
+        config = Qwen2Config(num_hidden_layers=64, hidden_size=5120, intermediate_size=27648, num_attention_heads=40, num_key_value_heads=8,
+                             head_dim=128, vocab_size=152064, max_position_embeddings=32768, rope_theta=1e6, rms_norm_eps=1e-6,
+                             tie_word_embeddings=False)
+        lengths = [4096] * 16
+        new_tokens, max_batch, budget = 512, 16, 8192
+    prompts = [random_prompt(i, n, config.vocab_size) for i, n in enumerate(lengths)]
+    cache_tokens = sum(-(-(n + new_tokens) // 16) * 16 for n in lengths)
+    engine = Engine.from_random("Qwen2ForCausalLM", config, seed=0, dtype="bfloat16", page_size=16, max_tokens=cache_tokens, max_requests=max_batch)
+    params = SamplingParams(temperature=0.0, max_tokens=new_tokens, ignore_eos=True)
+    engine.generate(prompts[:2], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))  # warm-up: compiles, library set-up
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    outputs = engine.generate(prompts, params, max_batch=max_batch, max_batch_tokens=budget, prefill_chunk_busy=2048)
+    seconds = time.perf_counter() - started
+    generated, prompt_tokens = sum(len(o) for o in outputs), sum(lengths)
+    print(json.dumps({"workload": name, "requests": len(prompts), "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+                      "seconds": round(seconds, 3), "generated_tokens_per_s": round(generated / seconds, 1),
+                      "all_tokens_per_s": round((generated + prompt_tokens) / seconds, 1), "steps": engine.runner.steps_run,
+                      "graphs": len(engine.runner.graphs), "dtype": "bf16", "data": "synthetic: random weights and token ids",
+                      "layers": config.num_hidden_layers, "hidden": config.hidden_size}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -212,9 +250,14 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points, prefill and e2e")
     parser.add_argument("--only", default=None, choices=["prefill"], help="time one part alone (for profiling)")
+    parser.add_argument("--workload", default=None, choices=["mixed-1.5b", "batch-32b"],
+                        help="one of the other workloads instead: 128 requests with prompts of 16..4096 tokens and 256 decoded tokens "
+                             "each through generate() at the 1.5B shape, or batch 16 with prompts of 4,096 and 512 decoded tokens at the 32B shape")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    if args.workload:
+        return other_workload(args.workload)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
             print("bench.py: this engine runs on one GPU; --gpus > 1 is not supported")
