@@ -350,3 +350,143 @@ def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path):
     got_a.append(mixed[18:])
     assert np.abs(mixed[:18] - want["c"]).max() <= 1e-4 * np.abs(want["c"]).max()
     assert np.abs(np.concatenate(got_a) - want["a"]).max() <= 1e-4 * np.abs(want["a"]).max()
+
+
+# ------------------------------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, both defined here.
+ROUTED = {"architectures": ["TestRoutedLM"], "hidden": 64, "vocab": 131, "inter": 96, "experts": 4, "expert_inter": 40, "eps": 1e-6,
+          "max_positions": 128}
+
+
+def register_routed():
+    from hyperion_b200.models import Architecture, register_architecture
+    from hyperion_b200.parts import (FeedForward, LayerSpec, ModelSpec, PartSpec, PositionEncoding, Run, WeightSpec, register_feed_forward,
+                                     register_position)
+
+    class TopOneExperts(FeedForward):
+        """Router logits in float; every token goes to its best expert (a small GELU MLP); output scaled by the router's softmax weight."""
+
+        def __init__(self, spec, build):
+            super().__init__(spec, build)
+            p = spec.params
+            self.hidden, self.experts, self.inter = p["hidden_size"], p["experts"], p["expert_inter"]
+
+        def weights(self):
+            return {"router.weight": WeightSpec((self.experts, self.hidden)), "w1": WeightSpec((self.experts, self.inter, self.hidden)),
+                    "w2": WeightSpec((self.experts, self.hidden, self.inter))}
+
+        def load(self, tensors):
+            self.router, self.w1, self.w2 = (tensors[n].float() for n in ("router.weight", "w1", "w2"))
+
+        def forward(self, x, step):
+            xf = x.float()
+            probs = torch.softmax(xf @ self.router.t(), dim=-1)
+            weight, choice = probs.max(dim=-1)
+            out = torch.zeros_like(xf)
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    hidden = torch.nn.functional.gelu(xf[rows] @ self.w1[e].t())
+                    out[rows] = (hidden @ self.w2[e].t()) * weight[rows, None]
+            return out.to(self.dtype)
+
+    class InterleavedRotary(PositionEncoding):
+        """Rotates the pairs (2i, 2i+1) of every head by position * base^(-2i/d): another convention than rotate-half."""
+
+        def __init__(self, spec, build):
+            super().__init__(spec, build)
+            d, base = spec.params["head_dim"], spec.params["base"]
+            inv = base ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)
+            angle = torch.arange(build.max_positions, dtype=torch.float64)[:, None] * inv[None]
+            self.cos, self.sin = angle.cos().float().to(build.device), angle.sin().float().to(build.device)
+
+        def apply_(self, x, heads, head_dim, positions):
+            t = x.shape[0]
+            view = x[:, : heads * head_dim].float().reshape(t, heads, head_dim // 2, 2)
+            c, s = self.cos[positions.long()][:, None, :], self.sin[positions.long()][:, None, :]
+            even, odd = view[..., 0] * c - view[..., 1] * s, view[..., 1] * c + view[..., 0] * s
+            x[:, : heads * head_dim] = torch.stack([even, odd], dim=-1).reshape(t, heads * head_dim).to(x.dtype)
+
+    def spec(c):
+        sizes = {"vocab_size": c["vocab"], "hidden_size": c["hidden"]}
+        norm = {"hidden_size": c["hidden"], "eps": c["eps"]}
+
+        def attention(i, position):
+            return PartSpec("gqa_attention", f"l{i}.attn.", {"hidden_size": c["hidden"], "heads": 4, "kv_heads": 2, "head_dim": 16, "bias": False,
+                                                              "position": position})
+
+        def norms(i):
+            return {"input": PartSpec("rmsnorm", f"l{i}.n1.", norm), "post_mixer": PartSpec("rmsnorm", f"l{i}.n2.", norm)}
+
+        layers = (
+            LayerSpec("prenorm", attention(0, PartSpec("test_interleaved_rope", "", {"head_dim": 16, "base": 500.0})),
+                      PartSpec("test_top1_experts", "l0.moe.", {"hidden_size": c["hidden"], "experts": c["experts"], "expert_inter": c["expert_inter"]}), norms(0)),
+            LayerSpec("prenorm", attention(1, PartSpec("rope", "", {"head_dim": 16, "base": 1e4, "max_positions": c["max_positions"]})),
+                      PartSpec("swiglu", "l1.mlp.", {"hidden_size": c["hidden"], "intermediate_size": c["inter"]}), norms(1)),
+        )
+        return ModelSpec("TestRoutedLM", c["hidden"], c["vocab"], c["max_positions"], PartSpec("token_embedding", "embed.", sizes), layers,
+                         (Run(0), Run(1)), PartSpec("rmsnorm", "norm.", norm), PartSpec("linear_head", "head.", {**sizes, "tied": False}))
+
+    register_feed_forward("test_top1_experts", TopOneExperts)
+    register_position("test_interleaved_rope", InterleavedRotary)
+    register_architecture(Architecture("TestRoutedLM", lambda document: dict(document), spec, lambda config: dict(config)))
+
+
+def routed_plain(c, w, ids):
+    w = {k: v.double() for k, v in w.items()}
+    t = len(ids)
+    positions = torch.arange(t)
+    h = plain.embedding(w["embed.weight"], torch.tensor(ids))
+
+    def interleaved(x):
+        inv = 500.0 ** (-torch.arange(0, 16, 2, dtype=torch.float64) / 16)
+        angle = positions.double()[:, None] * inv[None]
+        cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+        pairs = x.reshape(t, x.shape[1], 8, 2)
+        return torch.stack([pairs[..., 0] * cos - pairs[..., 1] * sin, pairs[..., 1] * cos + pairs[..., 0] * sin], dim=-1).reshape(x.shape)
+
+    for i in range(2):
+        x = plain.rmsnorm(h, w[f"l{i}.n1.weight"], c["eps"])
+        q = plain.linear(x, w[f"l{i}.attn.q_proj.weight"]).view(t, 4, 16)
+        k = plain.linear(x, w[f"l{i}.attn.k_proj.weight"]).view(t, 2, 16)
+        v = plain.linear(x, w[f"l{i}.attn.v_proj.weight"]).view(t, 2, 16)
+        if i == 0:
+            q, k = interleaved(q), interleaved(k)
+        else:
+            cos, sin = plain.rope_tables(positions, 16, 1e4)
+            q, k = plain.rope(q, cos, sin), plain.rope(k, cos, sin)
+        a = plain.attention(q, k, v, positions, positions, 0.25)
+        h = h + plain.linear(a.reshape(t, -1), w[f"l{i}.attn.o_proj.weight"])
+        x = plain.rmsnorm(h, w[f"l{i}.n2.weight"], c["eps"])
+        if i == 0:
+            probs = torch.softmax(x @ w["l0.moe.router.weight"].t(), dim=-1)
+            weight, choice = probs.max(dim=-1)
+            out = torch.zeros_like(x)
+            for tok in range(t):
+                e = int(choice[tok])
+                out[tok] = (torch.nn.functional.gelu(x[tok] @ w["l0.moe.w1"][e].t()) @ w["l0.moe.w2"][e].t()) * weight[tok]
+            h = h + out
+        else:
+            h = h + plain.swiglu_mlp(x, w["l1.mlp.gate_proj.weight"], w["l1.mlp.up_proj.weight"], w["l1.mlp.down_proj.weight"])
+    return plain.linear(plain.rmsnorm(h, w["norm.weight"], c["eps"]), w["head.weight"])
+
+
+def test_a_routed_feed_forward_and_another_position_encoding(tmp_path):
+    from hyperion_b200.api import Engine
+    from hyperion_b200.engine.batch import StepEntry
+    from hyperion_b200.weights import read_all, write_model_folder
+
+    register_routed()
+    folder = write_model_folder(tmp_path / "routed", "TestRoutedLM", ROUTED, seed=12, std=0.15)
+    weights = read_all(folder)
+    assert weights["l0.moe.w1"].shape == (4, 40, 64) and "l0.attn.q_proj.bias" not in weights
+    g = torch.Generator().manual_seed(2)
+    a, b = (torch.randint(0, ROUTED["vocab"], (n,), generator=g).tolist() for n in (60, 33))
+    want_a, want_b = routed_plain(ROUTED, weights, a).numpy(), routed_plain(ROUTED, weights, b).numpy()
+    engine = Engine.from_folder(folder, dtype="float32", page_size=8, max_tokens=128, max_requests=2)
+    got = [engine.step([StepEntry("a", a[:25], list(range(25)))]).cpu().numpy()]
+    mixed = engine.step([StepEntry("a", a[25:26], [0]), StepEntry("b", b, list(range(33)))]).cpu().numpy()
+    got.append(mixed[:1])
+    got.append(engine.step([StepEntry("a", a[26:], list(range(34)))]).cpu().numpy())
+    assert np.abs(np.concatenate(got) - want_a).max() <= 1e-4 * np.abs(want_a).max()
+    assert np.abs(mixed[1:] - want_b).max() <= 1e-4 * np.abs(want_b).max()
