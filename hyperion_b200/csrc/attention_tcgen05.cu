@@ -1,0 +1,417 @@
+// Prompt attention on the 5th-generation tensor cores: causal grouped-query attention of a tile of 128
+// "virtual rows" (tokens x heads of one key/value group) over the paged bfloat16 cache, with S = Q K^T and
+// O += P V issued as tcgen05.mma and S and O living in tensor memory.  Head sizes 64 and 128 (HB_HEAD_DIM),
+// pages of 8 to 64 tokens.
+//
+// Roles in a block of 192 threads:
+//   warp 0      producer: one cp.async.bulk.tensor per page and 64-column panel into a ring of key/value stages
+//               (the same layout and barriers as attention_tma.cu);
+//   warp 1      owns tensor memory and issues the products: S_j = Q K_j^T (M 128, N 64, K = head size) into one of
+//               two S buffers, and O += P_j V_j (M 128, N = head size, K 64) with V as an MN-major operand.  S_{j+1}
+//               is issued before P_j is waited for, so the tensor cores work while the softmax warps do;
+//   warps 2-5   softmax: thread r owns row r (tensor-memory lane r).  It reads S_j with tcgen05.ld, masks and scales
+//               into the exp2 domain, keeps a running maximum and sum in float, writes P_j as bfloat16 into shared
+//               memory in the swizzled K-major layout the product wants, and rescales O in tensor memory only when
+//               the maximum has grown by more than 2^8 (until then the stale maximum is kept, which changes no
+//               result: the final division uses the same maximum for numerator and denominator).
+// Every mbarrier wait is bounded; a wait that runs out sets HB_STATUS_WAIT_EXPIRED, all roles leave their loops, tensor
+// memory is freed and the block returns.
+//
+// Counterpart in the reference: attention_mma_paged_*_bf16 (mma.sync m16n8k16, 64 x 64 tiles;
+// helios/crates/helios-hal/kernels/elementwise.cu:576-729,749); mask: key position <= query position (:660-663).
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef HB_HEAD_DIM
+#define HB_HEAD_DIM 128
+#endif
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int D = HB_HEAD_DIM;
+static_assert(D == 64 || D == 128, "the tcgen05 attention takes head sizes 64 and 128");
+constexpr int BM = 128;                       // virtual rows per block = tensor-memory lanes
+constexpr int BN = 64;                        // keys per tile
+constexpr int HALVES = D / 64;
+constexpr int PANEL = BN * 64;                // elements of a 64-key x 64-column panel (8 KB)
+constexpr int QPANEL = BM * 64;               // elements of a 128-row x 64-column panel of Q (16 KB)
+constexpr int TILE_ELEMS = HALVES * PANEL;
+constexpr int STAGE_BYTES = 2 * TILE_ELEMS * 2;
+constexpr int STAGES = 3;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 256;                // S0 [0,64) S1 [64,128) O [128,128+D)
+constexpr int O_COL = 128;
+constexpr unsigned WAIT_LIMIT = 1u << 24;
+constexpr float RESCALE_THRESHOLD = 8.0f;     // in the exp2 domain
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* failed) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned spin = 0; spin < WAIT_LIMIT; ++spin) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spin & 1023) == 1023 && *failed) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// K-major operand: rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ unsigned long long desc_k_major(const void* tile) {
+    return (unsigned long long)((smem_u32(tile) & 0x3FFFFu) >> 4) | (1ull << 16) | ((unsigned long long)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand (V as [key][64 columns] panels): panels `panel_bytes` apart along N, 8-key groups 1024 bytes apart along K.
+__device__ __forceinline__ unsigned long long desc_mn_major(const void* tile, unsigned panel_bytes) {
+    return (unsigned long long)((smem_u32(tile) & 0x3FFFFu) >> 4) | ((unsigned long long)(panel_bytes >> 4) << 16) |
+           ((unsigned long long)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// float accumulator, bfloat16 operands, A K-major, M 128, N n; B MN-major when b_mn.
+__device__ __forceinline__ unsigned idesc_for(int n, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
+    unsigned r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st16(unsigned taddr, const float (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                   "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+                   "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                   "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+                 : "memory");
+}
+
+struct AttnArgs {
+    const bf16* q; int q_stride;
+    bf16* out; int out_stride;
+    const int* block_table; int table_width;
+    const int* positions;
+    int heads, kv_heads, page_size, pages, window;
+    float scale_log2;
+    int* status;
+};
+
+// tiles[3*i] = first token (flat index), tiles[3*i+1] = token count, tiles[3*i+2] = batch row; virtual row v of a tile is
+// token v / gc, head v % gc of the block's key/value group (gc = min(group, 128) heads per block).
+__global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a,
+                                                               const int* __restrict__ tiles, int gc, int head_chunks) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* ring = base;                                                     // STAGES x [K panels | V panels]
+    bf16* qs = reinterpret_cast<bf16*>(ring + (size_t)STAGES * STAGE_BYTES);        // HALVES panels of 128 rows x 64
+    bf16* ps = qs + HALVES * QPANEL;                                                // 2 buffers of 128 rows x 64 keys
+    unsigned long long* kv_full = reinterpret_cast<unsigned long long*>(ps + 2 * QPANEL);
+    unsigned long long* kv_empty = kv_full + STAGES;
+    unsigned long long* s_full = kv_empty + STAGES;   // [2]
+    unsigned long long* p_full = s_full + 2;          // [2]
+    unsigned long long* o_done = p_full + 2;          // [1]
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(o_done + 1);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tok0 = tiles[3 * blockIdx.x], ntok = tiles[3 * blockIdx.x + 1], brow = tiles[3 * blockIdx.x + 2];
+    const int kvh = blockIdx.y / head_chunks, chunk = blockIdx.y - kvh * head_chunks;
+    const int group = a.heads / a.kv_heads;
+    const int first_head = kvh * group + chunk * gc;
+    const int heads_here = min(gc, group - chunk * gc);
+    const int* table = a.block_table + (size_t)brow * a.table_width;
+    const int pos_first = a.positions[tok0], pos_last = pos_first + ntok - 1;
+    const int need_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+    const int start = (need_lo / BN) * BN;
+    const int n_tiles = (pos_last - start) / BN + 1;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 4); }
+        mbar_init(o_done, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // stages whose first tile can be fetched in part start as zeros (see attention_tma.cu)
+    for (int s = 0; s < STAGES && s < n_tiles; ++s) {
+        if (s != n_tiles - 1 && !(s == 0 && need_lo > start)) continue;
+        uint4* stage = reinterpret_cast<uint4*>(ring + (size_t)s * STAGE_BYTES);
+        for (int e = tid; e < STAGE_BYTES / 16; e += THREADS) stage[e] = make_uint4(0, 0, 0, 0);
+    }
+    // queries into the swizzled K-major panels: element (row v, column c) -> panel c / 64, row v, chunk ((c % 64) / 8) ^ (v % 8)
+    for (int e = tid; e < BM * (D / 8); e += THREADS) {
+        const int v = e / (D / 8), cc = e - v * (D / 8);
+        const int tok = v / gc, hh = v - tok * gc;
+        uint4 value = make_uint4(0, 0, 0, 0);
+        if (tok < ntok && hh < heads_here)
+            value = *reinterpret_cast<const uint4*>(a.q + (size_t)(tok0 + tok) * a.q_stride + (size_t)(first_head + hh) * D + cc * 8);
+        *reinterpret_cast<uint4*>(qs + (cc >> 3) * QPANEL + v * 64 + (((cc & 7) ^ (v & 7)) << 3)) = value;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer (whole warp)
+        const int shift = 31 - __clz(a.page_size);
+        const int pages_per_tile = BN >> shift;
+        const int ops = pages_per_tile * 2 * HALVES;
+        const unsigned page_bytes = 2u * a.page_size * D * 2u;
+        if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
+        for (int it = 0; it < n_tiles; ++it) {
+            const int s = it % STAGES, round = it / STAGES;
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(&kv_empty[s], (round & 1) ^ 1, failed) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { if (lane == 0) *failed = 1; break; }
+            const int tile_base = start + it * BN;
+            int my_page = -1;
+            const int k0 = tile_base + lane * a.page_size;
+            if (lane < pages_per_tile && k0 <= pos_last && k0 + a.page_size - 1 >= need_lo) {
+                const int block = k0 >> shift;
+                const int id = block < a.table_width ? __ldg(table + block) : -1;
+                if (id >= 0 && id < a.pages) my_page = id;
+                else atomicOr(a.status, HB_STATUS_BAD_PAGE);
+            }
+            const unsigned valid = __popc(__ballot_sync(0xffffffffu, my_page >= 0));
+            if (lane == 0) {
+                if (valid) mbar_expect_tx(&kv_full[s], valid * page_bytes); else mbar_arrive(&kv_full[s]);
+            }
+            __syncwarp();
+            bf16* stage = reinterpret_cast<bf16*>(ring + (size_t)s * STAGE_BYTES);
+            for (int op0 = 0; op0 < ops; op0 += 32) {
+                const int op = op0 + lane;
+                const int p = min(op, ops - 1) / (2 * HALVES), rest = op % (2 * HALVES);
+                const int which = rest / HALVES, h = rest - which * HALVES;
+                const int page = __shfl_sync(0xffffffffu, my_page, p);
+                if (op < ops && page >= 0)
+                    tma_load_2d(stage + which * TILE_ELEMS + h * PANEL + p * a.page_size * 64, &kv_map, &kv_full[s], h * 64,
+                                ((page * 2 + which) * a.kv_heads + kvh) * a.page_size);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ tensor-core issuer (one lane)
+        if (lane == 0) {
+            const unsigned idesc_s = idesc_for(BN, false), idesc_o = idesc_for(D, true);
+            bool ok = true;
+            auto issue_s = [&](int j) {
+                const bf16* ks = reinterpret_cast<const bf16*>(ring + (size_t)(j % STAGES) * STAGE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk)
+                    umma(tmem + (j & 1) * BN, desc_k_major(qs + (kk >> 2) * QPANEL) + (unsigned long long)((kk & 3) * 2),
+                         desc_k_major(ks + (kk >> 2) * PANEL) + (unsigned long long)((kk & 3) * 2), idesc_s, kk > 0 ? 1u : 0u);
+                umma_commit(&s_full[j & 1]);
+            };
+            if (!mbar_wait(&kv_full[0], 0, failed)) { *failed = 1; ok = false; }
+            if (ok) { tc_fence_after(); issue_s(0); }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) {
+                    if (!mbar_wait(&kv_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
+                    tc_fence_after();
+                    issue_s(j + 1);
+                }
+                if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1, failed)) { *failed = 1; ok = false; break; }
+                tc_fence_after();
+                const bf16* vs = reinterpret_cast<const bf16*>(ring + (size_t)(j % STAGES) * STAGE_BYTES) + TILE_ELEMS;
+                const bf16* pb = ps + (j & 1) * QPANEL;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk)
+                    umma(tmem + O_COL, desc_k_major(pb) + (unsigned long long)(kk * 2),
+                         desc_mn_major(vs, PANEL * 2) + (unsigned long long)(kk * (2048 >> 4)), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&kv_empty[j % STAGES]);
+                umma_commit(o_done);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax: thread = row = tensor-memory lane
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
+        const int tok = r / gc, hh = r - tok * gc;
+        const bool row_valid = tok < ntok && hh < heads_here;
+        const int hi = row_valid ? pos_first + tok : -1;
+        const int lo = (row_valid && a.window > 0) ? max(0, hi - a.window + 1) : 0;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int b = j & 1;
+            if (!mbar_wait(&s_full[b], (j >> 1) & 1, failed)) { *failed = 1; ok = false; break; }
+            tc_fence_after();
+            float s[BN];
+#pragma unroll
+            for (int c = 0; c < BN; c += 16) tmem_ld16(lane_addr + b * BN + c, *reinterpret_cast<float(*)[16]>(&s[c]));
+            const int tile_base = start + j * BN;
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < BN; ++i) {
+                const int pos = tile_base + i;
+                s[i] = (pos <= hi && pos >= lo) ? s[i] * a.scale_log2 : -INFINITY;
+                tmax = fmaxf(tmax, s[i]);
+            }
+            const float m_new = fmaxf(m, tmax);
+            float alpha = 1.f;
+            if (m == -INFINITY) {
+                m = m_new;  // nothing visible so far: the row of O holds zeros (or is overwritten by the first product), no rescale
+            } else if (m_new - m > RESCALE_THRESHOLD) {
+                alpha = exp2f(m - m_new);
+                m = m_new;
+            }
+            const float m_use = (m == -INFINITY) ? 0.f : m;
+            float sum = 0.f;
+            uint4* prow = reinterpret_cast<uint4*>(ps + b * QPANEL + r * 64);
+#pragma unroll
+            for (int c = 0; c < BN / 8; ++c) {
+                uint4 packed;
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = exp2f(s[c * 8 + 2 * e] - m_use), p1 = exp2f(s[c * 8 + 2 * e + 1] - m_use);
+                    h2[e] = __floats2bfloat162_rn(p0, p1);
+                    // the sum uses the rounded values the product will see
+                    sum += __bfloat162float(h2[e].x) + __bfloat162float(h2[e].y);
+                }
+                prow[c ^ (r & 7)] = packed;
+            }
+            l = l * alpha + sum;
+            if (j > 0) {
+                if (!mbar_wait(o_done, (j - 1) & 1, failed)) { *failed = 1; ok = false; break; }
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+                    for (int c = 0; c < D; c += 16) {
+                        float o[16];
+                        tmem_ld16(lane_addr + O_COL + c, o);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] *= alpha;
+                        tmem_st16(lane_addr + O_COL + c, o);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[b]);
+        }
+        if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1, failed);
+        if (!ok) *failed = 1;
+        tc_fence_after();
+        if (ok) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+            for (int c = 0; c < D; c += 16) {
+                float o[16];
+                tmem_ld16(lane_addr + O_COL + c, o);
+                if (row_valid) {
+                    uint4 w[2];
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(w);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) h2[i] = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv);
+                    uint4* dst = reinterpret_cast<uint4*>(a.out + (size_t)(tok0 + tok) * a.out_stride + (size_t)(first_head + hh) * D + c);
+                    dst[0] = w[0];
+                    dst[1] = w[1];
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && *failed) atomicOr(a.status, HB_STATUS_WAIT_EXPIRED);
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* found = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &found, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(found);
+    }
+    return fn;
+}
+
+constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)(HALVES + 2) * QPANEL * sizeof(bf16) + (2 * STAGES + 5) * 8 + 16;
+}  // namespace
+
+// Rows of a tile (tokens x heads of a group) this kernel wants: the host planner cuts rows into tiles of
+// 128 / min(group, 128) tokens.
+HB_EXPORT int hb_attention_tc_tile_rows() { return BM; }
+
+HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+                                    int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int heads,
+                                    int kv_heads, int head_dim, int page_size, int pages, float scale, int window, int* status,
+                                    cudaStream_t stream) {
+    (void)token_row;
+    if (n_tiles <= 0) return 0;
+    if (head_dim != D) return HB_UNSUPPORTED_SIZE;
+    if (kv_heads <= 0 || heads % kv_heads || q_stride % 8 || out_stride % 8) return HB_BAD_ARGUMENT;
+    if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return HB_UNSUPPORTED_SIZE;
+    if (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15) return HB_BAD_ARGUMENT;
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return HB_BAD_ARGUMENT;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)pages * 2 * kv_heads * page_size};
+    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    const cuuint32_t elem[2] = {1, 1};
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return HB_BAD_ARGUMENT;
+    AttnArgs a{(const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_width, positions,
+               heads, kv_heads, page_size, pages, window, scale * 1.4426950408889634f, status};
+    const int group = heads / kv_heads, gc = group < BM ? group : BM, head_chunks = (group + gc - 1) / gc;
+    if ((long long)kv_heads * head_chunks > 65535) return HB_UNSUPPORTED_SIZE;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    attention_tc_kernel<<<dim3(n_tiles, kv_heads * head_chunks), THREADS, SMEM_BYTES, stream>>>(map, a, tiles, gc, head_chunks);
+    return launch_status();
+}

@@ -97,7 +97,7 @@ class ModelRunner:
                 flat.extend(table)
                 flat.extend([NO_PAGE] * (width - len(table)))
             packer.add(f"table{group}", flat, (len(rows), width))
-        host = {"positions": positions, "token_row": token_row, "want": want}
+        host = {"positions": positions, "token_row": token_row, "want": want, "page_size": self.cache.page_size}
         if pad_tables:
             host["context_cap"] = width * self.cache.page_size if self.cache.paged else 0
         for key, plan in self.planners.items():

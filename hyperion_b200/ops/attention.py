@@ -33,8 +33,18 @@ def _entry(head_dim: int, page_size: int, shape: str):
     return getattr(library("attention_bf16", HB_HEAD_DIM=head_dim), f"hb_attention_{shape}")
 
 
-def tile_tokens(heads: int, kv_heads: int) -> int:
-    return TILE_ROWS // min(heads // kv_heads, TILE_ROWS)
+def uses_tcgen05(head_dim: int, page_size: int) -> bool:
+    """Head sizes 64 and 128 with pages of 8 to 64 tokens: prompt portions take the tcgen05 kernel (128-row tiles)."""
+    return head_dim in (64, 128) and 8 <= page_size <= 64
+
+
+def tile_rows(head_dim: int, page_size) -> int:
+    """Virtual rows (tokens x heads of a group) per tile of the kernel that will run."""
+    return 128 if page_size is not None and uses_tcgen05(head_dim, page_size) else TILE_ROWS
+
+
+def tile_tokens(heads: int, kv_heads: int, rows: int = TILE_ROWS) -> int:
+    return rows // min(heads // kv_heads, rows)
 
 
 def plan(rows, tokens_per_tile: int) -> tuple[list[int], list[int]]:
@@ -64,10 +74,15 @@ def _common(q, out, cache, block_table, token_row, positions):
         raise KernelError("attention (bfloat16): queries and cache must be dense bfloat16")
 
 
-def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n_tiles, scale, window, out):
+def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n_tiles, scale, window, out, tile_size: int = TILE_ROWS):
+    """``tile_size``: the virtual rows per tile the tiles were planned for (64, or 128 for the tcgen05 kernel)."""
     _common(q, out, cache, block_table, token_row, positions)
     pages, _, kv_heads, page_size, head_dim = cache.shape
-    check(_entry(head_dim, page_size, "tiles")(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
+    if uses_tcgen05(head_dim, page_size) and tile_size == 128:
+        entry = library("attention_tcgen05", HB_HEAD_DIM=head_dim).hb_attention_tc_tiles
+    else:
+        entry = _entry(head_dim, page_size, "tiles")
+    check(entry(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
                                  i32(block_table.shape[1]), ptr(token_row), ptr(positions), ptr(tiles), i32(n_tiles), i32(heads),
                                  i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale), i32(window or 0),
                                  ptr(status_word(q.device)), stream_ptr()), "attention_tiles")

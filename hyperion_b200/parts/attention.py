@@ -49,7 +49,6 @@ class GroupedQueryAttention(Mixer):
         self.kv_width = self.kv_heads * self.head_dim
         # the tensor-core kernels take bfloat16 and head sizes in steps of 16; other head sizes use the generic kernel
         self.fast = self.dtype == torch.bfloat16 and fast_attention.supported(self.head_dim)
-        self.tile_tokens = fast_attention.tile_tokens(self.heads, self.kv_heads)
 
     def weights(self) -> dict[str, WeightSpec]:
         names = {"q_proj.weight": WeightSpec((self.q_width, self.hidden)), "o_proj.weight": WeightSpec((self.hidden, self.q_width))}
@@ -80,6 +79,8 @@ class GroupedQueryAttention(Mixer):
             modules.append(("attention_bf16", {"HB_HEAD_DIM": self.head_dim}))
             if self.head_dim % 64 == 0:
                 modules.append(("attention_tma", {"HB_HEAD_DIM": self.head_dim}))
+            if self.head_dim in (64, 128):
+                modules.append(("attention_tcgen05", {"HB_HEAD_DIM": self.head_dim}))
         else:
             modules.append(("attention_generic", {}))
         modules.append(("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {}))
@@ -107,29 +108,35 @@ class GroupedQueryAttention(Mixer):
 
     # ------------------------------------------------------------------ the tensor-core path
     def step_plans(self):
-        """Per-step metadata: the rows cut into tiles and single tokens (shared by all layers with the same tile size)."""
+        """Per-step metadata: the rows cut into tiles and single tokens (shared by all layers with the same tiling)."""
         if not self.fast:
             return {}
-        tokens_per_tile = self.tile_tokens
+        heads, kv_heads, head_dim = self.heads, self.kv_heads, self.head_dim
 
         def plan(rows, packer, host):
+            size = fast_attention.tile_rows(head_dim, host.get("page_size"))
+            tokens_per_tile = fast_attention.tile_tokens(heads, kv_heads, size)
+            key = f"attn_tiles_{tokens_per_tile}"
+            if key in host:
+                return
             tiles, items = fast_attention.plan(rows, tokens_per_tile)
-            host[f"attn_tiles_{tokens_per_tile}"] = len(tiles) // 3
+            host[key] = len(tiles) // 3
             host["attn_items"] = len(items)
             if tiles:
-                packer.add(f"attn_tiles_{tokens_per_tile}", tiles)
+                packer.add(key, tiles)
             if items and "attn_items" not in [name for name, *_ in packer._items]:
                 packer.add("attn_items", items)
 
-        return {("attention_plan", tokens_per_tile): plan}
+        return {("attention_plan", heads // kv_heads, head_dim): plan}
 
     def _attend_fast(self, qkv, step, cache):
         out = torch.empty((step.n_tokens, self.q_width), dtype=self.dtype, device=qkv.device)
-        key = f"attn_tiles_{self.tile_tokens}"
+        size = fast_attention.tile_rows(self.head_dim, step.host.get("page_size"))
+        key = f"attn_tiles_{fast_attention.tile_tokens(self.heads, self.kv_heads, size)}"
         n_tiles, n_items = step.host.get(key, 0), step.host.get("attn_items", 0)
         if n_tiles:
             fast_attention.attention_tiles(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions,
-                                           step.extra[key], n_tiles, self.scale, self.window, out)
+                                           step.extra[key], n_tiles, self.scale, self.window, out, tile_size=size)
         if n_items:
             # a step replayed from a CUDA graph fixes its launch shape for every context its tables can hold
             longest = step.host.get("context_cap") or max(row.position + row.count for row in step.rows
