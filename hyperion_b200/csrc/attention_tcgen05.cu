@@ -11,7 +11,8 @@
 //               is issued before P_j is waited for, so the tensor cores work while the softmax warps do;
 //   warps 2-5   softmax: thread r owns row r (tensor-memory lane r).  It reads S_j with tcgen05.ld, masks and scales
 //               into the exp2 domain, keeps a running maximum and sum in float, writes P_j as bfloat16 into shared
-//               memory in the swizzled K-major layout the product wants, and rescales O in tensor memory only when
+//               memory in the swizzled K-major layout the product wants (after the previous product has finished
+//               with that buffer), and rescales O in tensor memory only when
 //               the maximum has grown by more than 2^8 (until then the stale maximum is kept, which changes no
 //               result: the final division uses the same maximum for numerator and denominator).
 // Every mbarrier wait is bounded; a wait that runs out sets HB_STATUS_WAIT_EXPIRED, all roles leave their loops, tensor
@@ -37,8 +38,9 @@ constexpr int HALVES = D / 64;
 constexpr int PANEL = BN * 64;                // elements of a 64-key x 64-column panel (8 KB)
 constexpr int QPANEL = BM * 64;               // elements of a 128-row x 64-column panel of Q (16 KB)
 constexpr int TILE_ELEMS = HALVES * PANEL;
-constexpr int STAGE_BYTES = 2 * TILE_ELEMS * 2;
-constexpr int STAGES = 3;
+constexpr int TILE_BYTES = TILE_ELEMS * 2;      // one K or one V tile
+constexpr int STAGES = 2;                     // K tiles and V tiles have rings of their own: a K slot is free as soon as S is done,
+                                              // so K is fetched two tiles ahead; with one P buffer two blocks fit an SM (2 x 112 KB)
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 256;                // S0 [0,64) S1 [64,128) O [128,128+D)
 constexpr int O_COL = 128;
@@ -108,6 +110,31 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 64 consecutive float columns of this thread's lane in one instruction.
+__device__ __forceinline__ void tmem_ld64(unsigned taddr, float (&v)[64]) {
+    unsigned r[64];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
+        "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]),
+          "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]),
+          "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]),
+          "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 2^x by the hardware approximation (inputs are <= 8 here; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tmem_st16(unsigned taddr, const float (&v)[16]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
                  ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
@@ -131,16 +158,26 @@ struct AttnArgs {
 // token v / gc, head v % gc of the block's key/value group (gc = min(group, 128) heads per block).
 __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a,
                                                                const int* __restrict__ tiles, int gc, int head_chunks) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char* ring = base;                                                     // STAGES x [K panels | V panels]
-    bf16* qs = reinterpret_cast<bf16*>(ring + (size_t)STAGES * STAGE_BYTES);        // HALVES panels of 128 rows x 64
-    bf16* ps = qs + HALVES * QPANEL;                                                // 2 buffers of 128 rows x 64 keys
-    unsigned long long* kv_full = reinterpret_cast<unsigned long long*>(ps + 2 * QPANEL);
-    unsigned long long* kv_empty = kv_full + STAGES;
-    unsigned long long* s_full = kv_empty + STAGES;   // [2]
-    unsigned long long* p_full = s_full + 2;          // [2]
-    unsigned long long* o_done = p_full + 2;          // [1]
+    // The swizzled tiles need a 1024-byte aligned base.  Dynamic shared memory of a kernel without static shared memory
+    // starts at such an address; the block checks it and leaves with an error status otherwise, rather than spending
+    // the kilobyte of slack that would keep a second block from fitting on the SM.
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* base = smem_raw;
+    if (smem_u32(base) & 1023u) {
+        if (threadIdx.x == 0) atomicOr(a.status, HB_STATUS_WAIT_EXPIRED);
+        return;
+    }
+    unsigned char* k_ring = base;                                                   // STAGES K tiles
+    unsigned char* v_ring = base + (size_t)STAGES * TILE_BYTES;                     // STAGES V tiles
+    bf16* qs = reinterpret_cast<bf16*>(base + (size_t)2 * STAGES * TILE_BYTES);     // HALVES panels of 128 rows x 64
+    bf16* ps = qs + HALVES * QPANEL;                                                // 128 rows x 64 keys
+    unsigned long long* k_full = reinterpret_cast<unsigned long long*>(ps + QPANEL);
+    unsigned long long* k_empty = k_full + STAGES;
+    unsigned long long* v_full = k_empty + STAGES;
+    unsigned long long* v_empty = v_full + STAGES;
+    unsigned long long* s_full = v_empty + STAGES;    // [2]
+    unsigned long long* p_full = s_full + 2;          // [1]
+    unsigned long long* o_done = p_full + 1;          // [1]
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(o_done + 1);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -157,8 +194,9 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
     const int n_tiles = (pos_last - start) / BN + 1;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 4); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+        for (int b = 0; b < 2; ++b) mbar_init(&s_full[b], 1);
+        mbar_init(p_full, 4);
         mbar_init(o_done, 1);
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -170,8 +208,9 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
     // stages whose first tile can be fetched in part start as zeros (see attention_tma.cu)
     for (int s = 0; s < STAGES && s < n_tiles; ++s) {
         if (s != n_tiles - 1 && !(s == 0 && need_lo > start)) continue;
-        uint4* stage = reinterpret_cast<uint4*>(ring + (size_t)s * STAGE_BYTES);
-        for (int e = tid; e < STAGE_BYTES / 16; e += THREADS) stage[e] = make_uint4(0, 0, 0, 0);
+        uint4* k_stage = reinterpret_cast<uint4*>(k_ring + (size_t)s * TILE_BYTES);
+        uint4* v_stage = reinterpret_cast<uint4*>(v_ring + (size_t)s * TILE_BYTES);
+        for (int e = tid; e < TILE_BYTES / 16; e += THREADS) { k_stage[e] = make_uint4(0, 0, 0, 0); v_stage[e] = make_uint4(0, 0, 0, 0); }
     }
     // queries into the swizzled K-major panels: element (row v, column c) -> panel c / 64, row v, chunk ((c % 64) / 8) ^ (v % 8)
     for (int e = tid; e < BM * (D / 8); e += THREADS) {
@@ -192,15 +231,12 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
         // ------------------------------------------------------------------ producer (whole warp)
         const int shift = 31 - __clz(a.page_size);
         const int pages_per_tile = BN >> shift;
-        const int ops = pages_per_tile * 2 * HALVES;
-        const unsigned page_bytes = 2u * a.page_size * D * 2u;
+        const int ops = pages_per_tile * HALVES;
+        const unsigned page_bytes = (unsigned)a.page_size * D * 2u;  // of one page of K, or of V
         if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
-        for (int it = 0; it < n_tiles; ++it) {
+        bool alive = true;
+        for (int it = 0; it < n_tiles && alive; ++it) {
             const int s = it % STAGES, round = it / STAGES;
-            int ok = 1;
-            if (lane == 0) ok = mbar_wait(&kv_empty[s], (round & 1) ^ 1, failed) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) { if (lane == 0) *failed = 1; break; }
             const int tile_base = start + it * BN;
             int my_page = -1;
             const int k0 = tile_base + lane * a.page_size;
@@ -211,19 +247,25 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
                 else atomicOr(a.status, HB_STATUS_BAD_PAGE);
             }
             const unsigned valid = __popc(__ballot_sync(0xffffffffu, my_page >= 0));
-            if (lane == 0) {
-                if (valid) mbar_expect_tx(&kv_full[s], valid * page_bytes); else mbar_arrive(&kv_full[s]);
-            }
-            __syncwarp();
-            bf16* stage = reinterpret_cast<bf16*>(ring + (size_t)s * STAGE_BYTES);
-            for (int op0 = 0; op0 < ops; op0 += 32) {
-                const int op = op0 + lane;
-                const int p = min(op, ops - 1) / (2 * HALVES), rest = op % (2 * HALVES);
-                const int which = rest / HALVES, h = rest - which * HALVES;
-                const int page = __shfl_sync(0xffffffffu, my_page, p);
-                if (op < ops && page >= 0)
-                    tma_load_2d(stage + which * TILE_ELEMS + h * PANEL + p * a.page_size * 64, &kv_map, &kv_full[s], h * 64,
-                                ((page * 2 + which) * a.kv_heads + kvh) * a.page_size);
+            for (int which = 0; which < 2 && alive; ++which) {  // the K tile, then the V tile
+                unsigned long long* full = which ? &v_full[s] : &k_full[s];
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(which ? &v_empty[s] : &k_empty[s], (round & 1) ^ 1, failed) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { if (lane == 0) *failed = 1; alive = false; break; }
+                if (lane == 0) {
+                    if (valid) mbar_expect_tx(full, valid * page_bytes); else mbar_arrive(full);
+                }
+                __syncwarp();
+                bf16* tile = reinterpret_cast<bf16*>((which ? v_ring : k_ring) + (size_t)s * TILE_BYTES);
+                for (int op0 = 0; op0 < ops; op0 += 32) {
+                    const int op = op0 + lane;
+                    const int p = min(op, ops - 1) / HALVES, h = op % HALVES;
+                    const int page = __shfl_sync(0xffffffffu, my_page, p);
+                    if (op < ops && page >= 0)
+                        tma_load_2d(tile + h * PANEL + p * a.page_size * 64, &kv_map, full, h * 64,
+                                    ((page * 2 + which) * a.kv_heads + kvh) * a.page_size);
+                }
             }
         }
     } else if (warp == 1) {
@@ -232,30 +274,32 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
             const unsigned idesc_s = idesc_for(BN, false), idesc_o = idesc_for(D, true);
             bool ok = true;
             auto issue_s = [&](int j) {
-                const bf16* ks = reinterpret_cast<const bf16*>(ring + (size_t)(j % STAGES) * STAGE_BYTES);
+                const bf16* ks = reinterpret_cast<const bf16*>(k_ring + (size_t)(j % STAGES) * TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk)
                     umma(tmem + (j & 1) * BN, desc_k_major(qs + (kk >> 2) * QPANEL) + (unsigned long long)((kk & 3) * 2),
                          desc_k_major(ks + (kk >> 2) * PANEL) + (unsigned long long)((kk & 3) * 2), idesc_s, kk > 0 ? 1u : 0u);
+                umma_commit(&k_empty[j % STAGES]);  // the K slot is free once this product has read it
                 umma_commit(&s_full[j & 1]);
             };
-            if (!mbar_wait(&kv_full[0], 0, failed)) { *failed = 1; ok = false; }
+            if (!mbar_wait(&k_full[0], 0, failed)) { *failed = 1; ok = false; }
             if (ok) { tc_fence_after(); issue_s(0); }
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) {
-                    if (!mbar_wait(&kv_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
+                    if (!mbar_wait(&k_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
                     tc_fence_after();
                     issue_s(j + 1);
                 }
-                if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1, failed)) { *failed = 1; ok = false; break; }
+                if (!mbar_wait(p_full, j & 1, failed)) { *failed = 1; ok = false; break; }
+                if (!mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
                 tc_fence_after();
-                const bf16* vs = reinterpret_cast<const bf16*>(ring + (size_t)(j % STAGES) * STAGE_BYTES) + TILE_ELEMS;
-                const bf16* pb = ps + (j & 1) * QPANEL;
+                const bf16* vs = reinterpret_cast<const bf16*>(v_ring + (size_t)(j % STAGES) * TILE_BYTES);
+                const bf16* pb = ps;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk)
                     umma(tmem + O_COL, desc_k_major(pb) + (unsigned long long)(kk * 2),
                          desc_mn_major(vs, PANEL * 2) + (unsigned long long)(kk * (2048 >> 4)), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&kv_empty[j % STAGES]);
+                umma_commit(&v_empty[j % STAGES]);
                 umma_commit(o_done);
             }
         }
@@ -275,15 +319,22 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
             if (!mbar_wait(&s_full[b], (j >> 1) & 1, failed)) { *failed = 1; ok = false; break; }
             tc_fence_after();
             float s[BN];
-#pragma unroll
-            for (int c = 0; c < BN; c += 16) tmem_ld16(lane_addr + b * BN + c, *reinterpret_cast<float(*)[16]>(&s[c]));
+            tmem_ld64(lane_addr + b * BN, s);
             const int tile_base = start + j * BN;
             float tmax = -INFINITY;
+            if (tile_base + BN - 1 <= hi && tile_base >= lo) {  // every key of the tile is visible to this row
 #pragma unroll
-            for (int i = 0; i < BN; ++i) {
-                const int pos = tile_base + i;
-                s[i] = (pos <= hi && pos >= lo) ? s[i] * a.scale_log2 : -INFINITY;
-                tmax = fmaxf(tmax, s[i]);
+                for (int i = 0; i < BN; ++i) {
+                    s[i] *= a.scale_log2;
+                    tmax = fmaxf(tmax, s[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < BN; ++i) {
+                    const int pos = tile_base + i;
+                    s[i] = (pos <= hi && pos >= lo) ? s[i] * a.scale_log2 : -INFINITY;
+                    tmax = fmaxf(tmax, s[i]);
+                }
             }
             const float m_new = fmaxf(m, tmax);
             float alpha = 1.f;
@@ -295,40 +346,40 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
             }
             const float m_use = (m == -INFINITY) ? 0.f : m;
             float sum = 0.f;
-            uint4* prow = reinterpret_cast<uint4*>(ps + b * QPANEL + r * 64);
+            uint4 packed[BN / 8];
 #pragma unroll
             for (int c = 0; c < BN / 8; ++c) {
-                uint4 packed;
-                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed[c]);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float p0 = exp2f(s[c * 8 + 2 * e] - m_use), p1 = exp2f(s[c * 8 + 2 * e + 1] - m_use);
+                    const float p0 = fast_exp2(s[c * 8 + 2 * e] - m_use), p1 = fast_exp2(s[c * 8 + 2 * e + 1] - m_use);
+                    sum += p0 + p1;
                     h2[e] = __floats2bfloat162_rn(p0, p1);
-                    // the sum uses the rounded values the product will see
-                    sum += __bfloat162float(h2[e].x) + __bfloat162float(h2[e].y);
                 }
-                prow[c ^ (r & 7)] = packed;
             }
             l = l * alpha + sum;
-            if (j > 0) {
+            if (j > 0) {  // the previous product must be done before P is overwritten and before O may be rescaled
                 if (!mbar_wait(o_done, (j - 1) & 1, failed)) { *failed = 1; ok = false; break; }
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            }
+            uint4* prow = reinterpret_cast<uint4*>(ps + r * 64);
 #pragma unroll
-                    for (int c = 0; c < D; c += 16) {
-                        float o[16];
-                        tmem_ld16(lane_addr + O_COL + c, o);
+            for (int c = 0; c < BN / 8; ++c) prow[c ^ (r & 7)] = packed[c];
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i] *= alpha;
-                        tmem_st16(lane_addr + O_COL + c, o);
-                    }
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                for (int c = 0; c < D; c += 16) {
+                    float o[16];
+                    tmem_ld16(lane_addr + O_COL + c, o);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] *= alpha;
+                    tmem_st16(lane_addr + O_COL + c, o);
                 }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[b]);
+            if (lane == 0) mbar_arrive(p_full);
         }
         if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1, failed);
         if (!ok) *failed = 1;
@@ -375,7 +426,7 @@ EncodeTiled encode_tiled() {
     return fn;
 }
 
-constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)(HALVES + 2) * QPANEL * sizeof(bf16) + (2 * STAGES + 5) * 8 + 16;
+constexpr size_t SMEM_BYTES = (size_t)2 * STAGES * TILE_BYTES + (size_t)(HALVES + 1) * QPANEL * sizeof(bf16) + (4 * STAGES + 4) * 8 + 16;
 }  // namespace
 
 // Rows of a tile (tokens x heads of a group) this kernel wants: the host planner cuts rows into tiles of
