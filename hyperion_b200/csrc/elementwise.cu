@@ -285,11 +285,76 @@ __global__ void rope_kv_store_kernel(T* __restrict__ x, int stride, int q_heads,
     }
 }
 
+// bfloat16 with head sizes that are multiples of 16: every thread rotates 8 consecutive pairs (two 16-byte loads, two
+// 16-byte stores) or copies 8 values; same arithmetic per element as the scalar kernel.
+__global__ void rope_kv_store_bf16x8_kernel(__nv_bfloat16* __restrict__ x, int stride, int q_heads, int kv_heads, int head_dim,
+                                            const int* __restrict__ positions, const float2* __restrict__ table, int max_positions,
+                                            __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table, int table_width,
+                                            const int* __restrict__ token_row, int page_size, int pages, int* status) {
+    const int t = blockIdx.x;
+    const int half = head_dim >> 1, chunks = half >> 3;  // 8-pair chunks per head
+    const int pos = positions[t];
+    if (pos < 0 || pos >= max_positions) {
+        if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, HB_STATUS_BAD_POSITION);
+        return;
+    }
+    const int block = pos / page_size;
+    const int page = block < table_width ? block_table[(size_t)token_row[t] * table_width + block] : -1;
+    const bool page_ok = page >= 0 && page < pages;
+    if (!page_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, HB_STATUS_BAD_PAGE);
+    const int slot = pos - block * page_size;
+    __nv_bfloat16* row = x + (size_t)t * stride;
+    const float2* cs = table + (size_t)pos * half;
+    const size_t page_base = (size_t)(page_ok ? page : 0) * 2 * kv_heads * page_size * head_dim;
+    const int rotated = (q_heads + kv_heads) * chunks;
+    const int total = rotated + kv_heads * 2 * chunks;  // values: head_dim / 8 chunks per head
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < total; e += gridDim.y * blockDim.x) {
+        if (e < rotated) {
+            const int head = e / chunks, i = (e - head * chunks) * 8;
+            __nv_bfloat16* p = row + head * head_dim + i;
+            const uint4 lo4 = *reinterpret_cast<const uint4*>(p), hi4 = *reinterpret_cast<const uint4*>(p + half);
+            const __nv_bfloat16* lo = reinterpret_cast<const __nv_bfloat16*>(&lo4);
+            const __nv_bfloat16* hi = reinterpret_cast<const __nv_bfloat16*>(&hi4);
+            uint4 out_lo, out_hi;
+            __nv_bfloat16* y1 = reinterpret_cast<__nv_bfloat16*>(&out_lo);
+            __nv_bfloat16* y2 = reinterpret_cast<__nv_bfloat16*>(&out_hi);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float2 c = cs[i + j];
+                const float x1 = __bfloat162float(lo[j]), x2 = __bfloat162float(hi[j]);
+                y1[j] = __float2bfloat16_rn(x1 * c.x - x2 * c.y);
+                y2[j] = __float2bfloat16_rn(x2 * c.x + x1 * c.y);
+            }
+            if (head < q_heads) {
+                *reinterpret_cast<uint4*>(p) = out_lo;
+                *reinterpret_cast<uint4*>(p + half) = out_hi;
+            } else if (page_ok) {
+                __nv_bfloat16* dst = cache + page_base + (((size_t)(head - q_heads)) * page_size + slot) * head_dim + i;
+                *reinterpret_cast<uint4*>(dst) = out_lo;
+                *reinterpret_cast<uint4*>(dst + half) = out_hi;
+            }
+        } else if (page_ok) {
+            const int f = e - rotated, head = f / (2 * chunks), i = (f - head * 2 * chunks) * 8;
+            const uint4 v = *reinterpret_cast<const uint4*>(row + (q_heads + kv_heads + head) * head_dim + i);
+            *reinterpret_cast<uint4*>(cache + page_base + (((size_t)(kv_heads + head)) * page_size + slot) * head_dim + i) = v;
+        }
+    }
+}
+
 HB_EXPORT int hb_rope_kv_store(void* x, int is_bf16, int tokens, int stride, int q_heads, int kv_heads, int head_dim,
                                const int* positions, const float* table, int max_positions, void* cache, const int* block_table,
                                int table_width, const int* token_row, int page_size, int pages, int* status, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (head_dim & 1) return HB_UNSUPPORTED_SIZE;
+    if (is_bf16 && head_dim % 16 == 0 && stride % 8 == 0 && (((uintptr_t)x | (uintptr_t)cache) & 15) == 0) {
+        const int items = (q_heads + 2 * kv_heads) * (head_dim / 16);
+        const int threads = items >= 256 ? 256 : 128;
+        const dim3 grid8(tokens, tokens >= 512 ? 1 : min(8, (items + threads - 1) / threads));
+        rope_kv_store_bf16x8_kernel<<<grid8, threads, 0, stream>>>((__nv_bfloat16*)x, stride, q_heads, kv_heads, head_dim, positions,
+                                                                   (const float2*)table, max_positions, (__nv_bfloat16*)cache, block_table,
+                                                                   table_width, token_row, page_size, pages, status);
+        return launch_status();
+    }
     const int pairs = (q_heads + 2 * kv_heads) * (head_dim / 2);
     const int slices = tokens >= 512 ? 1 : min(16, (pairs + 255) / 256);
     const dim3 grid(tokens, slices);

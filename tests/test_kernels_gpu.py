@@ -165,10 +165,11 @@ def test_kv_store_writes_where_the_table_says_and_nowhere_else():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_fused_rope_and_cache_write_equals_the_two_steps(dtype):
+@pytest.mark.parametrize("head_dim", [24, 32, 128])  # 32 and 128 take the 16-byte variant in bfloat16
+def test_fused_rope_and_cache_write_equals_the_two_steps(dtype, head_dim):
     from hyperion_b200.parts.rope import rotary_table
 
-    q_heads, kv_heads, head_dim, page_size = 5, 3, 24, 4
+    q_heads, kv_heads, page_size = 5, 3, 4
     table = torch.tensor([[2, 0, 5, -1], [1, 3, 4, 6]], dtype=torch.int32).to(DEV)
     token_row = torch.tensor([0, 0, 0, 1, 1], dtype=torch.int32).to(DEV)
     positions = torch.tensor([3, 4, 11, 0, 15], dtype=torch.int32).to(DEV)
