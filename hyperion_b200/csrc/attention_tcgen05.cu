@@ -249,9 +249,6 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
                 if (id >= 0 && id < a.pages) my_page = id;
                 else atomicOr(a.status, HB_STATUS_BAD_PAGE);
             }
-#if defined(HB_EXPERIMENT) && (HB_EXPERIMENT & 8)
-            my_page = -1;  // timing experiment: nothing is fetched
-#endif
             const unsigned valid = __popc(__ballot_sync(0xffffffffu, my_page >= 0));
             for (int which = 0; which < 2 && alive; ++which) {  // the K tile, then the V tile
                 unsigned long long* full = which ? &v_full[s] : &k_full[s];
@@ -325,12 +322,7 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
             if (!mbar_wait(&s_full[b], (j >> 1) & 1, failed)) { *failed = 1; ok = false; break; }
             tc_fence_after();
             float s[BN];
-#if defined(HB_EXPERIMENT) && (HB_EXPERIMENT & 1)
-#pragma unroll
-            for (int i = 0; i < BN; ++i) s[i] = 0.f;  // timing experiment: no load of S
-#else
             tmem_ld64(lane_addr + b * BN, s);
-#endif
             const int tile_base = start + j * BN;
             float tmax = -INFINITY;
             if (tile_base + BN - 1 <= hi && tile_base >= lo) {  // every key of the tile is visible to this row
@@ -363,11 +355,7 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
                 __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed[c]);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-#if defined(HB_EXPERIMENT) && (HB_EXPERIMENT & 2)
-                    const float p0 = s[c * 8 + 2 * e] - m_use, p1 = s[c * 8 + 2 * e + 1] - m_use;  // timing experiment: no exponential
-#else
                     const float p0 = fast_exp2(s[c * 8 + 2 * e] - m_use), p1 = fast_exp2(s[c * 8 + 2 * e + 1] - m_use);
-#endif
                     sum += p0 + p1;
                     h2[e] = __floats2bfloat162_rn(p0, p1);
                 }
@@ -391,9 +379,7 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-#if !(defined(HB_EXPERIMENT) && (HB_EXPERIMENT & 4))
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);

@@ -276,9 +276,6 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
                 if (id >= 0 && id < a.pages) my_page = id;
                 else atomicOr(a.status, HB_STATUS_BAD_PAGE);
             }
-#if defined(HB_EXPERIMENT) && HB_EXPERIMENT == 2
-            my_page = -1;  // timing experiment: nothing is fetched
-#endif
             const unsigned valid = __popc(__ballot_sync(0xffffffffu, my_page >= 0));
             if (lane == 0) {
                 if (valid) mbar_expect_tx(&full[s], valid * page_bytes); else mbar_arrive(&full[s]);
@@ -319,11 +316,7 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
         if (!mbar_wait(&full[s], round & 1, failed)) { *failed = 1; atomicOr(a.status, HB_STATUS_WAIT_EXPIRED); ok = false; break; }
         const bf16* ks = reinterpret_cast<const bf16*>(ring + (size_t)s * STAGE_BYTES);
         const int base = start + it * BN;
-#if defined(HB_EXPERIMENT) && HB_EXPERIMENT == 1
-        if (base < 0) {  // timing experiment: consumers only hand the stages back
-#else
         if (TOKENS) {
-#endif
             if (base + warp * 16 <= pos_last) process_keys<2>(st, qs, ks, ks + TILE_ELEMS, warp * 16, base, hi, lo, a.scale_log2);
         } else if (!TOKENS) {
             if (warp_has_rows && base <= warp_hi && base + BN - 1 >= warp_lo)

@@ -13,6 +13,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Callable, Hashable, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -83,19 +84,20 @@ class MetadataPacker:
     def begin(self) -> None:
         self._items: list[tuple[str, int, int, tuple[int, ...]]] = []
         self._cursor = 0
-        self._flat: list[int] = []
+        self._chunks: list[np.ndarray] = []
 
     def add(self, name: str, values: Any, shape: Optional[tuple[int, ...]] = None) -> None:
-        """Append an int32 array (a list of ints, or a tensor); every array starts on a 16-byte boundary."""
+        """Append an int32 array (a list of ints, a numpy array or a tensor); every array starts on a 16-byte boundary."""
         if isinstance(values, torch.Tensor):
-            values = values.reshape(-1).tolist()
-        count = len(values)
+            values = values.detach().cpu().numpy()
+        array = np.asarray(values, dtype=np.int32).reshape(-1)
+        count = array.size
         shape = shape or (count,)
         self._items.append((name, self._cursor, count, shape))
-        self._flat.extend(values)
+        self._chunks.append(array)
         padding = -count % 4
         if padding:
-            self._flat.extend((0,) * padding)
+            self._chunks.append(np.zeros(padding, dtype=np.int32))
         self._cursor += count + padding
 
     def finish(self) -> dict[str, torch.Tensor]:
@@ -106,7 +108,7 @@ class MetadataPacker:
             self.events[self._index].synchronize()
         host = self.hosts[self._index]
         if self._cursor:
-            host[: self._cursor] = torch.tensor(self._flat, dtype=torch.int32)  # one conversion for the whole step
+            np.concatenate(self._chunks, out=host.numpy()[: self._cursor])  # straight into the pinned buffer
             self.dev[: self._cursor].copy_(host[: self._cursor], non_blocking=True)
             if self.device.type == "cuda":
                 event = torch.cuda.Event()

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from typing import Hashable, Optional, Sequence
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -54,9 +55,9 @@ class ModelRunner:
             count = len(entry.tokens)
             if count == 0:
                 raise BadStep(f"request {entry.request!r} brings no tokens")
-            for token in entry.tokens:
-                if isinstance(token, bool) or not isinstance(token, int) or not 0 <= token < vocab:
-                    raise BadStep(f"request {entry.request!r}: token {token!r} is outside the vocabulary of {vocab}")
+            tokens = np.asarray(entry.tokens)
+            if tokens.ndim != 1 or tokens.dtype.kind not in "iu" or int(tokens.min()) < 0 or int(tokens.max()) >= vocab:
+                raise BadStep(f"request {entry.request!r}: its tokens must be integers in 0..{vocab - 1}")
             for index in entry.want:
                 if isinstance(index, bool) or not isinstance(index, int) or not 0 <= index < count:
                     raise BadStep(f"request {entry.request!r}: wanted index {index!r} is outside its {count} tokens")
@@ -67,23 +68,24 @@ class ModelRunner:
     # ------------------------------------------------------------------ the batch on the device
     def _context(self, entries: Sequence[StepEntry], extra_arrays=None, pad_tables: bool = False) -> StepContext:
         rows: list[Row] = []
-        token_ids: list[int] = []
-        positions: list[int] = []
-        token_row: list[int] = []
+        token_chunks, position_chunks, row_chunks = [], [], []
         want: list[int] = []
+        start = 0
         for index, entry in enumerate(entries):
-            start, position = len(token_ids), self.cache.length(entry.request)
-            rows.append(Row(entry.request, start, len(entry.tokens), position, self.cache.slot(entry.request)))
-            token_ids.extend(entry.tokens)
-            positions.extend(range(position, position + len(entry.tokens)))
-            token_row.extend([index] * len(entry.tokens))
+            position, count = self.cache.length(entry.request), len(entry.tokens)
+            rows.append(Row(entry.request, start, count, position, self.cache.slot(entry.request)))
+            token_chunks.append(np.asarray(entry.tokens, dtype=np.int32))
+            position_chunks.append(np.arange(position, position + count, dtype=np.int32))
+            row_chunks.append(np.full(count, index, dtype=np.int32))
             want.extend(start + i for i in entry.want)
+            start += count
+        token_ids, positions, token_row = np.concatenate(token_chunks), np.concatenate(position_chunks), np.concatenate(row_chunks)
         packer = self.packer
         packer.begin()
         packer.add("token_ids", token_ids)
         packer.add("positions", positions)
         packer.add("token_row", token_row)
-        packer.add("row_start", [row.start for row in rows] + [len(token_ids)])
+        packer.add("row_start", [row.start for row in rows] + [int(token_ids.size)])
         packer.add("slots", [row.slot for row in rows])
         if want:
             packer.add("want", want)
@@ -107,7 +109,7 @@ class ModelRunner:
         arrays = packer.finish()
         extra = {k: v for k, v in arrays.items() if k not in ("token_ids", "positions", "token_row", "row_start", "slots", "want")
                  and not k.startswith("table")}
-        return StepContext(rows=rows, n_tokens=len(token_ids), token_ids=arrays["token_ids"], positions=arrays["positions"],
+        return StepContext(rows=rows, n_tokens=int(token_ids.size), token_ids=arrays["token_ids"], positions=arrays["positions"],
                            token_row=arrays["token_row"], row_start=arrays["row_start"], want_rows=arrays.get("want"),
                            n_want=len(want), paged_tables=[arrays[f"table{g}"] for g in range(len(self.cache.paged))],
                            slots=arrays["slots"], extra=extra, host=host)
