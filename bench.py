@@ -183,8 +183,9 @@ def time_prefill(engine, reps: int = 5, warmup: int = 3) -> dict:
 
 
 def time_e2e(engine, batch: int, steps: int, warmup: int) -> dict:
-    """Decode throughput through ``Engine.generate``: prompts go in from the host, every step's
-    sampled ids come back to the host before the next step is planned."""
+    """Decode throughput through ``Engine.generate``: prompts go in from the host; every step copies its
+    metadata from pinned memory and its sampled ids back to pinned memory, where the callback reads them
+    (one step behind the device, which takes each token from the step before on the device)."""
     from hyperion_b200.sampling import SamplingParams
 
     vocab = engine.model.spec.vocab_size

@@ -7,6 +7,7 @@ and its direct ``generate`` (helios/crates/helios-hal/src/backends/hopper_sm90/f
 """
 from __future__ import annotations
 
+from collections import deque
 from pathlib import Path
 from typing import Any, Optional, Sequence
 
@@ -57,7 +58,8 @@ class Engine:
         self.cache = CacheManager(users, page_size, num_pages, max_requests, dtype=model.dtype, device=model.device)
         self.runner = ModelRunner(model, self.cache)
         self.sampler = Sampler(vocab, model.device, seen=self.cache.state_storage(SAMPLER_STATE))
-        self._token_staging = torch.empty(max(1, max_requests), dtype=torch.int32, pin_memory=True)
+        self._token_staging = torch.empty((2, max(1, max_requests)), dtype=torch.int32, pin_memory=True)
+        self._token_ring = torch.empty((2, max(1, max_requests)), dtype=torch.int32, device=model.device)
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -99,13 +101,16 @@ class Engine:
     # ------------------------------------------------------------------ generation
     def generate(self, prompts: Sequence[Sequence[int]], sampling=None, *, max_batch: Optional[int] = None,
                  max_batch_tokens: int = 2048, prefill_chunk_busy: int = 512, max_seq_len: Optional[int] = None,
-                 on_token=None, return_reasons: bool = False):
+                 on_token=None, return_reasons: bool = False, lookahead: bool = True):
         """Generate a continuation for every prompt (lists of token ids) with continuous batching.
 
         ``sampling`` is one :class:`SamplingParams` for all prompts or one per prompt; missing fields
         take the model folder's ``generation_config.json`` defaults.  Returns the generated ids per
         prompt (with ``return_reasons`` also why each ended: ``stop``, ``length`` or a failure text).
-        ``on_token(index, token)`` is called as tokens appear.
+        ``on_token(index, token)`` is called as tokens appear.  With ``lookahead`` the next step is
+        launched before the last one's ids have reached the host (it takes them on the device), so
+        the device never waits for the host; ids then appear one step late, and a request that
+        ends on an end-of-sequence token has run one row in vain.
         """
         from .engine.scheduler import Request, Scheduler, SchedulerConfig
 
@@ -124,7 +129,7 @@ class Engine:
         scheduler = Scheduler(SchedulerConfig(
             num_pages=self.cache.num_pages, page_size=self.page_size, max_seq_len=limit,
             max_batch=min(max_batch or self.cache.max_requests, self.cache.max_requests), max_batch_tokens=max_batch_tokens,
-            prefill_chunk_busy=prefill_chunk_busy, eos_token_ids=tuple(self.defaults.eos_token_ids)))
+            prefill_chunk_busy=prefill_chunk_busy, eos_token_ids=tuple(self.defaults.eos_token_ids), max_in_flight=2 if lookahead else 1))
         for index, (prompt, params) in enumerate(zip(prompts, per_prompt)):
             scheduler.enqueue(Request(index, prompt, params.validated()))
         outputs: list[list[int]] = [[] for _ in prompts]
@@ -140,39 +145,67 @@ class Engine:
                 else:
                     reasons[event.request] = event.reason
 
+        depth = 2 if lookahead else 1
+        in_flight: deque = deque()  # (plan, requests of its sampled rows, pinned ids, event), oldest first
+        newest: Optional[tuple[int, torch.Tensor]] = None  # (plan step, its sampled ids on the device)
+
+        def launch(plan):
+            nonlocal newest
+            entries, options, places, sampled_rows = [], [], {}, []
+            for index, row in enumerate(plan.rows):
+                if not self.cache.has(row.request):
+                    self.cache.add_request(row.request)
+                tokens = row.tokens
+                if row.token_from is not None:  # sampled by the plan before, still on the device
+                    step, place = row.token_from
+                    if newest is None or newest[0] != step:
+                        raise RuntimeError(f"plan {plan.step} wants a token of plan {step}, which is not the one before it")
+                    places[index], tokens = place, [0]
+                entries.append(StepEntry(row.request, tokens, [len(tokens) - 1] if row.sample else []))
+                if row.sample:
+                    sampled_rows.append(row.request)
+                    options.extend(pack_options(params_of[row.request], row.sampled_before, self.cache.slot(row.request)))
+            logits = self.runner.step(entries, {"sampling_options": (options, (len(options) // 8, 8))} if options else None,
+                                      device_tokens=(newest[1], places) if places else None)
+            if logits is None:
+                return plan, sampled_rows, None, None
+            ring = plan.step % depth
+            tokens = self.sampler.sample(logits, self.runner.last_context.extra["sampling_options"],
+                                         out=self._token_ring[ring, : len(sampled_rows)],
+                                         all_greedy=all(params_of[request].greedy for request in sampled_rows))
+            newest = (plan.step, tokens)
+            host = self._token_staging[ring, : len(sampled_rows)]
+            host.copy_(tokens, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+            return plan, sampled_rows, host, event
+
+        def retire(plan, sampled_rows, host, event):
+            sampled = {}
+            if event is not None:
+                event.synchronize()
+                sampled = dict(zip(sampled_rows, host.tolist()))
+            handle(scheduler.complete(plan, sampled))
+            self._free_released(scheduler)
+
         while True:
-            plan = scheduler.next_plan()
+            plan = scheduler.next_plan() if len(in_flight) < depth else None
             handle(scheduler.take_events())
-            if plan is None:
+            if plan is not None:
+                try:
+                    in_flight.append(launch(plan))
+                except Exception as error:  # the step's requests fail, the others go on
+                    handle(scheduler.fail(plan, f"{type(error).__name__}: {error}"))
+                    self._free_released(scheduler)
+                    if not isinstance(error, (OutOfPages, BadStep)):
+                        raise
+                    continue
+            if in_flight and (plan is None or len(in_flight) >= depth):
+                retire(*in_flight.popleft())
+            elif plan is None:
                 if scheduler.idle:
                     break
                 raise RuntimeError("the scheduler has requests but plans nothing")
-            entries, options = [], []
-            for row in plan.rows:
-                if not self.cache.has(row.request):
-                    self.cache.add_request(row.request)
-                entries.append(StepEntry(row.request, row.tokens, [len(row.tokens) - 1] if row.sample else []))
-                if row.sample:
-                    options.extend(pack_options(params_of[row.request], row.sampled_before, self.cache.slot(row.request)))
-            try:
-                logits = self.runner.step(entries, {"sampling_options": (options, (len(options) // 8, 8))} if options else None)
-            except Exception as error:  # the step's requests fail, the others go on
-                handle(scheduler.fail(plan, f"{type(error).__name__}: {error}"))
-                self._free_released(scheduler)
-                if not isinstance(error, (OutOfPages, BadStep)):
-                    raise
-                continue
-            sampled = {}
-            if logits is not None:
-                tokens = self.sampler.sample(logits, self.runner.last_context.extra["sampling_options"],
-                                             all_greedy=all(params_of[row.request].greedy for row in plan.rows if row.sample))
-                host = self._token_staging[: tokens.numel()]
-                host.copy_(tokens, non_blocking=True)
-                torch.cuda.current_stream().synchronize()
-                chosen = host.tolist()
-                sampled = {row.request: chosen[i] for i, row in enumerate(r for r in plan.rows if r.sample)}
-            handle(scheduler.complete(plan, sampled))
-            self._free_released(scheduler)
         self.check()
         return (outputs, reasons) if return_reasons else outputs
 

@@ -32,6 +32,19 @@ HB_EXPORT int hb_embedding(const void* table, int table_is_bf16, const int* ids,
     return launch_status();
 }
 
+// Tokens that were sampled by the step before and never left the device: ids[pairs[2i]] = source[pairs[2i+1]].
+__global__ void place_tokens_kernel(int* __restrict__ ids, const int* __restrict__ source, const int* __restrict__ pairs, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) ids[pairs[2 * i]] = source[pairs[2 * i + 1]];
+}
+
+// The caller has checked the pairs against the sizes of ids and source.
+HB_EXPORT int hb_place_tokens(int* ids, const int* source, const int* pairs, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    place_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, source, pairs, n);
+    return launch_status();
+}
+
 // ---------------------------------------------------------------- residual add + RMSNorm
 // Output row r normalises source row s = rows ? rows[r] : r of h (+ delta). With `write_h` the sum
 // is stored back into h[s] (the residual stream); it is skipped when rows are gathered for the

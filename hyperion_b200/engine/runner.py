@@ -66,7 +66,7 @@ class ModelRunner:
                 raise BadStep(f"request {entry.request!r} would reach position {length + count}, the model's limit is {limit}")
 
     # ------------------------------------------------------------------ the batch on the device
-    def _context(self, entries: Sequence[StepEntry], extra_arrays=None, pad_tables: bool = False) -> StepContext:
+    def _context(self, entries: Sequence[StepEntry], extra_arrays=None, pad_tables: bool = False, device_places=None) -> StepContext:
         rows: list[Row] = []
         token_chunks, position_chunks, row_chunks = [], [], []
         want: list[int] = []
@@ -106,6 +106,8 @@ class ModelRunner:
             plan(rows, packer, host)
         for name, (values, shape) in (extra_arrays or {}).items():
             packer.add(name, values, shape)
+        if device_places:  # last, so that the other arrays lie where a captured graph expects them
+            packer.add("device_token_pairs", [v for index, place in device_places.items() for v in (rows[index].start, place)])
         arrays = packer.finish()
         extra = {k: v for k, v in arrays.items() if k not in ("token_ids", "positions", "token_row", "row_start", "slots", "want")
                  and not k.startswith("table")}
@@ -115,13 +117,24 @@ class ModelRunner:
                            slots=arrays["slots"], extra=extra, host=host)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], extra_arrays=None) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], extra_arrays=None, device_tokens=None) -> Optional[torch.Tensor]:
         """Run the entries as one batch.  Returns float logits [wanted, vocab] on the device, in the
         order of the entries and of each entry's ``want``, or None when nothing was wanted.
         ``extra_arrays`` ({name: (int32 values, shape)}) ride along in the step's one host-to-device
-        copy and are found in ``self.last_context.extra`` afterwards."""
+        copy and are found in ``self.last_context.extra`` afterwards.
+        ``device_tokens`` = (int32 tensor on the device, {index of an entry: index into the tensor}):
+        the named entries, of one token each, take that token from the tensor instead of from their
+        ``tokens`` (whose value is ignored), so a token sampled by the step before need not pass
+        through the host."""
         entries = list(entries)
         self._validate(entries)
+        if device_tokens is not None:
+            source, places = device_tokens
+            if source.dtype != torch.int32 or source.device != self.device or not source.is_contiguous():
+                raise BadStep("device tokens must be a contiguous int32 tensor on the engine's device")
+            for index, place in places.items():
+                if not 0 <= index < len(entries) or len(entries[index].tokens) != 1 or not 0 <= place < source.numel():
+                    raise BadStep(f"device token {place} for entry {index}: only a single-token entry can take a token of the tensor")
         added = []
         try:
             for entry in entries:
@@ -134,8 +147,11 @@ class ModelRunner:
                 self.cache.free(request)
             raise
         key = self._graph_key(entries, extra_arrays)
-        context = self._context(entries, extra_arrays, pad_tables=key is not None)
+        context = self._context(entries, extra_arrays, pad_tables=key is not None,
+                                device_places=device_tokens[1] if device_tokens is not None else None)
         self.last_context = context
+        if device_tokens is not None and device_tokens[1]:
+            ops.place_tokens(context.token_ids, device_tokens[0], context.extra.pop("device_token_pairs"))
         logits = self.model.forward(context, self.cache) if key is None else self._replay(key, context)
         for entry in entries:
             self.cache.advance(entry.request, len(entry.tokens))

@@ -18,14 +18,24 @@ yields the same plans, like the reference's step scheduler
 Unlike the reference, whose step is either one prompt chunk or a bucket of decode rows, a step here
 mixes both: every decoding request contributes its one token, and prompt portions fill what is
 left of the step's token budget, so portion sizes change from step to step.
+
+Plans may run ahead of their results (``max_in_flight`` > 1): everything a plan needs except the
+value of the token sampled by the plan before it is known when that plan was made (how many tokens
+a request has, whether ``max_tokens`` or the context limit ends it).  A row whose token is still
+on the device carries ``PENDING_TOKEN`` and names the plan and sampled row it comes from; the
+engine feeds it from the device.  Only an end-of-sequence token is learnt late: the request then
+has one row too many in flight, whose result is dropped.
 """
 from __future__ import annotations
 
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Hashable, Optional, Sequence
+from typing import Hashable, Optional, Sequence, Union
 
 from ..sampling.params import SamplingParams
+
+
+PENDING_TOKEN = -1  # stands in a plan row for a sampled token that has not reached the host yet
 
 
 class QueueFull(RuntimeError):
@@ -49,6 +59,7 @@ class SchedulerConfig:
     prefill_chunk_busy: int = 512  # largest prompt portion while requests are decoding
     max_queue: int = 1 << 16
     eos_token_ids: tuple[int, ...] = ()
+    max_in_flight: int = 1  # plans that may be made before the oldest one's results are in
 
 
 @dataclass
@@ -57,6 +68,7 @@ class PlanRow:
     tokens: list[int]
     sample: bool  # the row's last token ends the prompt or is a decode token: a token is chosen after it
     sampled_before: int  # how many tokens the request has sampled so far (the draw counter)
+    token_from: Optional[tuple[int, int]] = None  # tokens == [PENDING_TOKEN]: (plan step, index among its sampled rows)
 
 
 @dataclass
@@ -78,8 +90,9 @@ class _Sequence:
     request: Request
     reserved_pages: int
     fed: int = 0  # prompt tokens already planned
+    planned_samples: int = 0  # sampled rows planned so far, results in or not
     generated: list[int] = field(default_factory=list)
-    pending: Optional[int] = None  # the sampled token not yet fed back
+    feed: Union[None, int, tuple[int, int]] = None  # what the next decode row feeds: a token, or where a plan in flight will put it
 
     @property
     def prefilling(self) -> bool:
@@ -96,7 +109,7 @@ class Scheduler:
         self.events: list[Event] = []
         self.released: list[Hashable] = []  # requests whose cache the engine must free
         self._step = 0
-        self._in_flight: Optional[Plan] = None
+        self._in_flight: deque[Plan] = deque()  # oldest first
 
     # ------------------------------------------------------------------ intake
     def enqueue(self, request: Request) -> None:
@@ -134,18 +147,22 @@ class Scheduler:
 
     # ------------------------------------------------------------------ planning
     def next_plan(self) -> Optional[Plan]:
-        """The next step, or None when nothing is running or waiting."""
-        if self._in_flight is not None:
+        """The next step, or None when there is nothing to run now (nothing is running or waiting,
+        or every running request has its last row in flight)."""
+        if len(self._in_flight) >= self.config.max_in_flight:
             raise RuntimeError("the previous plan has not been completed")
         self._admit()
         c = self.config
         rows: list[PlanRow] = []
         budget = c.max_batch_tokens
-        decoding = [s for s in self.running.values() if not s.prefilling and s.pending is not None]
+        decoding = [s for s in self.running.values() if s.feed is not None]
         for s in decoding:
             if budget == 0:
                 break
-            rows.append(PlanRow(s.request.id, [s.pending], True, len(s.generated)))
+            if isinstance(s.feed, tuple):
+                rows.append(PlanRow(s.request.id, [PENDING_TOKEN], True, s.planned_samples, token_from=s.feed))
+            else:
+                rows.append(PlanRow(s.request.id, [s.feed], True, s.planned_samples))
             budget -= 1
         limit = c.prefill_chunk_busy if decoding else c.max_batch_tokens
         for s in self.running.values():
@@ -156,30 +173,38 @@ class Scheduler:
             prompt = s.request.prompt
             count = min(len(prompt) - s.fed, budget, limit)
             rows.append(PlanRow(s.request.id, list(prompt[s.fed : s.fed + count]), s.fed + count == len(prompt), 0))
+            s.fed += count
             budget -= count
         if not rows:
             return None
+        sampled = 0
+        for row in rows:  # what each request feeds next is known now, but for the token's value
+            if not row.sample:
+                continue
+            s = self.running[row.request]
+            s.planned_samples += 1
+            more = s.planned_samples < s.request.params.max_tokens and len(s.request.prompt) + s.planned_samples < c.max_seq_len
+            s.feed = (self._step, sampled) if more else None
+            sampled += 1
         plan = Plan(self._step, rows)
         self._step += 1
-        self._in_flight = plan
+        self._in_flight.append(plan)
         return plan
 
     # ------------------------------------------------------------------ results
     def complete(self, plan: Plan, sampled: dict[Hashable, int]) -> list[Event]:
-        """The step ran: ``sampled`` holds the token chosen for every row with ``sample``."""
-        if plan is not self._in_flight:
-            raise RuntimeError("complete() must get the plan in flight")
-        self._in_flight = None
+        """The oldest plan in flight ran: ``sampled`` holds the token chosen for every row with ``sample``."""
+        if not self._in_flight or plan is not self._in_flight[0]:
+            raise RuntimeError("complete() must get the oldest plan in flight")
+        self._in_flight.popleft()
         c = self.config
+        index = -1
         for row in plan.rows:
-            s = self.running.get(row.request)
-            if s is None:  # cancelled while in flight
-                continue
-            if s.prefilling:
-                s.fed += len(row.tokens)
-            else:
-                s.pending = None
             if not row.sample:
+                continue
+            index += 1
+            s = self.running.get(row.request)
+            if s is None:  # cancelled, or ended by an end-of-sequence token, while this row was in flight
                 continue
             token = int(sampled[row.request])
             params = s.request.params
@@ -190,15 +215,15 @@ class Scheduler:
             self.events.append(Event(row.request, "token", token=token))
             if len(s.generated) >= params.max_tokens or len(s.request.prompt) + len(s.generated) >= c.max_seq_len:
                 self._finish(s, "length")
-            else:
-                s.pending = token
+            elif s.feed == (plan.step, index):
+                s.feed = token  # no later plan has taken it from the device
         return self.take_events()
 
     def fail(self, plan: Plan, reason: str) -> list[Event]:
         """The step failed: only the requests it carried fail, and they are released."""
-        if plan is not self._in_flight:
-            raise RuntimeError("fail() must get the plan in flight")
-        self._in_flight = None
+        if plan not in self._in_flight:
+            raise RuntimeError("fail() must get a plan in flight")
+        self._in_flight.remove(plan)
         for row in plan.rows:
             s = self.running.pop(row.request, None)
             if s is not None:

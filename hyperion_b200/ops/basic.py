@@ -40,6 +40,12 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None =
     return out
 
 
+def place_tokens(ids: torch.Tensor, source: torch.Tensor, pairs: torch.Tensor) -> None:
+    """ids[pairs[i, 0]] = source[pairs[i, 1]] on the device (all int32); the caller has checked the pairs."""
+    require_cuda(ids, source, pairs)
+    check(library("elementwise").hb_place_tokens(ptr(ids), ptr(source), ptr(pairs), i32(pairs.numel() // 2), stream_ptr()), "place_tokens")
+
+
 def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
                 rows: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """RMSNorm of ``h (+ delta)`` times ``weight``.

@@ -6,7 +6,7 @@ import random
 import pytest
 
 from hyperion_b200.cache import NO_PAGE, CacheError, CacheManager, OutOfPages, PagePool
-from hyperion_b200.engine.scheduler import Request, Scheduler, SchedulerConfig
+from hyperion_b200.engine.scheduler import PENDING_TOKEN, Request, Scheduler, SchedulerConfig
 from hyperion_b200.parts.base import PagedKV, RequestState
 from hyperion_b200.sampling import SamplingParams
 
@@ -282,3 +282,103 @@ def test_same_trace_gives_the_same_plans():
         return [[(r.request, tuple(r.tokens), r.sample, r.sampled_before) for r in p.rows] for p in plans]
 
     assert run() == run()
+
+
+# ---------------------------------------------------------------------- plans that run ahead of their results
+def drive_ahead(scheduler, token_of, limit=1000):
+    """Like ``drive`` but each plan is made before the one before it is completed, as a pipelined
+    engine does; a pending token is resolved from the plan it names, which must be the one before."""
+    events, in_flight, tokens_of_plan = [], [], {}
+    fed: dict = {}  # request -> the tokens its rows carried, pending ones resolved
+    counts: dict = {}
+    for _ in range(limit):
+        plan = scheduler.next_plan() if len(in_flight) < 2 else None
+        events += scheduler.take_events()
+        if plan is not None:
+            sampled = {}
+            for row in plan.rows:
+                tokens = row.tokens
+                if row.token_from is not None:
+                    step, index = row.token_from
+                    assert tokens == [PENDING_TOKEN] and step == plan.step - 1
+                    tokens = [tokens_of_plan[step][index]]
+                else:
+                    assert PENDING_TOKEN not in tokens
+                fed.setdefault(row.request, []).extend(tokens)
+                if row.sample:
+                    counts[row.request] = counts.get(row.request, 0) + 1
+                    assert row.sampled_before == counts[row.request] - 1
+                    sampled[row.request] = token_of(row.request, counts[row.request])
+            tokens_of_plan[plan.step] = [sampled[row.request] for row in plan.rows if row.sample]
+            in_flight.append((plan, sampled))
+        if in_flight and (plan is None or len(in_flight) >= 2):
+            events += scheduler.complete(*in_flight.pop(0))
+        elif plan is None:
+            assert scheduler.idle
+            return events, fed
+    raise AssertionError("the scheduler did not finish")
+
+
+def outcome(events):
+    tokens, reasons = {}, {}
+    for e in events:
+        if e.kind == "token":
+            tokens.setdefault(e.request, []).append(e.token)
+        else:
+            reasons[e.request] = (e.kind, e.reason)
+    return tokens, reasons
+
+
+def test_plans_ahead_of_results_give_the_same_tokens_and_reasons():
+    eos = 7
+
+    def token_of(request, n):  # request 2 and 5 meet the end-of-sequence token, the others end by length
+        return eos if request in (2, 5) and n == request else 100 + 10 * request + n
+
+    def scheduler(depth):
+        s = Scheduler(SchedulerConfig(num_pages=40, page_size=4, max_seq_len=48, max_batch=3, max_batch_tokens=12, prefill_chunk_busy=5,
+                                      eos_token_ids=(eos,), max_in_flight=depth))
+        r = random.Random(6)
+        for i in range(8):
+            s.enqueue(Request(i, [r.randrange(50) for _ in range(r.randrange(1, 30))], params(2 + (5 * i) % 9)))
+        return s
+
+    _, events = drive(scheduler(1), token_of)
+    ahead_events, fed = drive_ahead(scheduler(2), token_of)
+    assert outcome(ahead_events) == outcome(events)
+    tokens, reasons = outcome(events)
+    assert reasons[2] == ("finished", "stop") and reasons[5] == ("finished", "stop") and reasons[0] == ("finished", "length")
+    reference = scheduler(1)
+    for request in list(reference.waiting):  # every request was fed its prompt, then its own tokens, nothing else
+        generated = tokens.get(request.id, [])
+        carried = fed[request.id]
+        assert carried[: len(request.prompt)] == list(request.prompt)
+        extra = carried[len(request.prompt):]
+        assert extra[: len(generated)] == generated[: len(extra)] and len(extra) <= len(generated) + 1
+
+
+def test_no_row_is_planned_past_max_tokens_or_the_context_limit_when_running_ahead():
+    s = Scheduler(SchedulerConfig(num_pages=100, page_size=4, max_seq_len=10, max_batch_tokens=64, max_in_flight=2))
+    s.enqueue(Request("a", list(range(4)), params(2)))
+    s.enqueue(Request("b", list(range(7)), params(50)))
+    first = s.next_plan()
+    second = s.next_plan()  # both decode from the device
+    assert [(r.request, r.tokens, r.token_from) for r in second.rows] == [("a", [PENDING_TOKEN], (0, 0)), ("b", [PENDING_TOKEN], (0, 1))]
+    with pytest.raises(RuntimeError):
+        s.next_plan()
+    s.complete(first, {"a": 11, "b": 21})
+    third = s.next_plan()  # a has its two rows; b may take one more (7 + 3 = 10 is the limit)
+    assert [(r.request, r.token_from) for r in third.rows] == [("b", (1, 1))]
+    s.complete(second, {"a": 12, "b": 22})
+    assert s.next_plan() is None and not s.idle  # b's last row is in flight: nothing to plan, not idle
+    events = s.complete(third, {"b": 23})
+    assert [e.token for e in events if e.kind == "token"] == [23] and events[-1].reason == "length"
+    assert s.idle
+
+
+def test_a_known_token_is_fed_from_the_host_even_with_room_to_run_ahead():
+    s = Scheduler(SchedulerConfig(num_pages=100, page_size=4, max_seq_len=64, max_in_flight=2))
+    s.enqueue(Request("a", [1, 2, 3], params(4)))
+    first = s.next_plan()
+    s.complete(first, {"a": 9})
+    assert s.next_plan().rows[0].tokens == [9]

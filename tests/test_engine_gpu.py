@@ -166,6 +166,38 @@ def test_eos_stops_and_is_not_emitted(folders, tmp_path):
     assert tokens[0] == free_run[:first] and reasons == ["stop"]
 
 
+def test_running_ahead_of_the_host_changes_nothing(folders, tmp_path):
+    """Six requests, two of which meet an end-of-sequence token, greedy and at temperature 0.9, in a pool
+    so small that requests wait: with the next step launched before the last ids reach the host, tokens
+    and reasons are those of the step-by-step loop, and every page comes back."""
+    import json
+    import shutil
+
+    from hyperion_b200.sampling import SamplingParams
+
+    config, _ = TINY["A"]
+    prompts = [random_ids(500 + i, n, config.vocab_size) for i, n in enumerate([5, 33, 18, 47, 2, 26])]
+    params = [SamplingParams(temperature=0.0 if i % 2 else 0.9, seed=70 + i, max_tokens=4 + 3 * i, ignore_eos=True) for i in range(6)]
+    free_run = engine_for(folders["A"], "float32").generate(prompts, params, lookahead=False)
+    folder = tmp_path / "with_eos"
+    shutil.copytree(folders["A"], folder)
+    document = json.loads((folder / "config.json").read_text())
+    document["eos_token_id"] = [free_run[3][5], free_run[5][2]]
+    (folder / "config.json").write_text(json.dumps(document))
+    params = [SamplingParams(temperature=p.temperature, seed=p.seed, max_tokens=p.max_tokens) for p in params]
+    results = []
+    for lookahead in (False, True):
+        engine = engine_for(folder, "float32", max_tokens=160, max_requests=3)  # 10 pages
+        seen = []
+        results.append(engine.generate(prompts, params, max_batch_tokens=24, prefill_chunk_busy=8, return_reasons=True, lookahead=lookahead,
+                                       on_token=lambda index, token: seen.append((index, token))))
+        assert sorted(seen) == sorted((i, t) for i, tokens in enumerate(results[-1][0]) for t in tokens)
+        engine.cache.check()
+        assert engine.cache.free_pages() == 10 and not engine.cache.live_requests
+    assert results[0] == results[1]
+    assert "stop" in results[0][1] and "length" in results[0][1]
+
+
 def test_small_pool_makes_requests_wait_and_a_hopeless_one_fail(folders):
     from hyperion_b200.sampling import SamplingParams
 
