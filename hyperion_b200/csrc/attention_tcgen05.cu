@@ -163,7 +163,9 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
     // the kilobyte of slack that would keep a second block from fitting on the SM.
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = smem_raw;
+    let_next_kernel_start();
     if (smem_u32(base) & 1023u) {
+        wait_for_previous_kernels();
         if (threadIdx.x == 0) atomicOr(a.status, HB_STATUS_WAIT_EXPIRED);
         return;
     }
@@ -215,6 +217,7 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
         uint4* v_stage = reinterpret_cast<uint4*>(v_ring + (size_t)s * TILE_BYTES);
         for (int e = tid; e < TILE_BYTES / 16; e += THREADS) { k_stage[e] = make_uint4(0, 0, 0, 0); v_stage[e] = make_uint4(0, 0, 0, 0); }
     }
+    wait_for_previous_kernels();  // the queries and the newest keys and values come from the kernel before
     // queries into the swizzled K-major panels: element (row v, column c) -> panel c / 64, row v, chunk ((c % 64) / 8) ^ (v % 8)
     for (int e = tid; e < BM * (D / 8); e += THREADS) {
         const int v = e / (D / 8), cc = e - v * (D / 8);
@@ -466,6 +469,5 @@ HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attention_tc_kernel<<<dim3(n_tiles, kv_heads * head_chunks), THREADS, SMEM_BYTES, stream>>>(map, a, tiles, gc, head_chunks);
-    return launch_status();
+    return launch_after_previous(attention_tc_kernel, dim3(n_tiles, kv_heads * head_chunks), THREADS, SMEM_BYTES, stream, map, a, tiles, gc, head_chunks);
 }

@@ -201,6 +201,7 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
     volatile int* failed = reinterpret_cast<volatile int*>(empty + STAGES);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    let_next_kernel_start();
     int tok0, ntok, brow, split = 0;
     if (TOKENS) {
         tok0 = work[blockIdx.x]; ntok = 1; brow = a.token_row[tok0]; split = blockIdx.z;
@@ -237,6 +238,7 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
         uint4* stage = reinterpret_cast<uint4*>(ring + (size_t)s * STAGE_BYTES);
         for (int e = tid; e < STAGE_BYTES / 16; e += THREADS) stage[e] = make_uint4(0, 0, 0, 0);
     }
+    wait_for_previous_kernels();  // the queries and the newest keys and values come from the kernel before
     // queries: virtual row v = token * gc + head
     for (int e = tid; e < ROWS * (D / 8); e += THREADS) {
         const int v = e / (D / 8), c = e - v * (D / 8);
@@ -384,6 +386,8 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
 __global__ void attention_merge_kernel(const int* __restrict__ items, const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                        bf16* __restrict__ out, int out_stride, int heads, int splits) {
     const int item = blockIdx.x, head = blockIdx.y, t = items[item];
+    let_next_kernel_start();
+    wait_for_previous_kernels();
     const size_t slot0 = ((size_t)item * heads + head) * splits;
     float m = -INFINITY;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, ws_ml[(slot0 + s) * 2]);
@@ -459,9 +463,8 @@ HB_EXPORT int hb_attention_tma_tiles(const void* q, int q_stride, void* out, int
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attention_tma_kernel<false><<<dim3(n_tiles, kv_heads * head_chunks), THREADS, smem_bytes<false>(), stream>>>(map, a, tiles, gc, head_chunks, 1,
-                                                                                                               nullptr, nullptr);
-    return launch_status();
+    return launch_after_previous(attention_tma_kernel<false>, dim3(n_tiles, kv_heads * head_chunks), THREADS, smem_bytes<false>(), stream, map, a, tiles,
+                                 gc, head_chunks, 1, nullptr, nullptr);
 }
 
 HB_EXPORT int hb_attention_tma_tokens(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
@@ -483,10 +486,9 @@ HB_EXPORT int hb_attention_tma_tokens(const void* q, int q_stride, void* out, in
     }
     float* ws_o = workspace;
     float* ws_ml = workspace ? workspace + (size_t)n_items * heads * splits * D : nullptr;
-    attention_tma_kernel<true><<<dim3(n_items, kv_heads * head_chunks, splits), THREADS, smem_bytes<true>(), stream>>>(map, a, items, 16, head_chunks,
-                                                                                                                     splits, ws_o, ws_ml);
-    int code = launch_status();
+    int code = launch_after_previous(attention_tma_kernel<true>, dim3(n_items, kv_heads * head_chunks, splits), THREADS, smem_bytes<true>(), stream, map, a,
+                                     items, 16, head_chunks, splits, ws_o, ws_ml);
     if (code || splits == 1) return code;
-    attention_merge_kernel<<<dim3(n_items, heads), D < 128 ? 64 : 128, 0, stream>>>(items, ws_o, ws_ml, (bf16*)out, out_stride, heads, splits);
-    return launch_status();
+    return launch_after_previous(attention_merge_kernel, dim3(n_items, heads), D < 128 ? 64 : 128, 0, stream, items, (const float*)ws_o,
+                                 (const float*)ws_ml, (bf16*)out, out_stride, heads, splits);
 }

@@ -6,6 +6,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define HB_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -73,3 +74,40 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched through launch_after_previous() may start while the kernel before it in the
+// stream is still running. It must call wait_for_previous_kernels() before it reads anything an
+// earlier kernel wrote and before it writes global memory at all; what stands before that call
+// (barrier set-up, tensor-memory allocation, loads of weights, which no kernel writes) overlaps
+// the earlier kernel's tail. let_next_kernel_start() allows the kernel after this one to be
+// scheduled as soon as every block of this one has called it; that kernel still waits in its own
+// wait_for_previous_kernels() until this one has finished and its writes are visible. Both calls
+// do nothing in a kernel that was launched the ordinary way. HYPERION_B200_PDL=0 turns the
+// overlap off (every launch is then serialised as usual).
+__device__ __forceinline__ void wait_for_previous_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool overlap_launches() {
+    static const bool enabled = [] {
+        const char* value = getenv("HYPERION_B200_PDL");
+        return !(value && value[0] == '0');
+    }();
+    return enabled;
+}
+
+template <typename... Params, typename... Args>
+static inline int launch_after_previous(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
+                                        Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = overlap_launches() ? 1 : 0;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}

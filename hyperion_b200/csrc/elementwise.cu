@@ -58,6 +58,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     float* hrow = h + (size_t)s * hidden;
     const TD* drow = delta ? delta + (size_t)s * hidden : nullptr;
     float sum = 0.f;
+    let_next_kernel_start();
+    wait_for_previous_kernels();
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = hrow[i];
         if (drow) {
@@ -88,14 +90,19 @@ __global__ void add_rmsnorm_cached_kernel(float* __restrict__ h, const TD* __res
     const TD* drow = delta ? delta + (size_t)s * hidden : nullptr;
     float v[8], w[8];
     float sum = 0.f;
+    let_next_kernel_start();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {  // the norm's weight is nobody's output: it is fetched while the kernel before still runs
+        const int i = threadIdx.x + j * blockDim.x;
+        w[j] = i < hidden ? weight[i] : 0.f;
+    }
+    wait_for_previous_kernels();
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         v[j] = 0.f;
-        w[j] = 0.f;
         if (i < hidden) {
             v[j] = hrow[i];
-            w[j] = weight[i];
             if (drow) v[j] += to_float(drow[i]);
         }
     }
@@ -122,17 +129,18 @@ HB_EXPORT int hb_add_rmsnorm(float* h, const void* delta, int delta_is_bf16, con
                              cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const int threads = hidden >= 4096 ? 1024 : (hidden >= 1024 ? 512 : 256);
+    int status = 0;
     const bool cached = hidden <= 8 * threads;  // both kernels add a thread's squares in the same order, so they agree bit for bit
 #define HB_NORM(TD, TO)                                                                                                                    \
-    if (cached) add_rmsnorm_cached_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, write_h); \
-    else add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, write_h)
+    if (cached) status = launch_after_previous(add_rmsnorm_cached_kernel<TD, TO>, n_rows, threads, 0, stream, h, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, write_h); \
+    else status = launch_after_previous(add_rmsnorm_kernel<TD, TO>, n_rows, threads, 0, stream, h, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, write_h)
     if (delta_is_bf16) {
         if (out_is_bf16) { HB_NORM(__nv_bfloat16, __nv_bfloat16); } else { HB_NORM(__nv_bfloat16, float); }
     } else {
         if (out_is_bf16) { HB_NORM(float, __nv_bfloat16); } else { HB_NORM(float, float); }
     }
 #undef HB_NORM
-    return launch_status();
+    return status;
 }
 
 // ---------------------------------------------------------------- SwiGLU
@@ -152,6 +160,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter) {
     const int t = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    let_next_kernel_start();
+    wait_for_previous_kernels();
     if (i >= inter) return;
     const uint4 g4 = *reinterpret_cast<const uint4*>(gate_up + (size_t)t * 2 * inter + i);
     const uint4 u4 = *reinterpret_cast<const uint4*>(gate_up + (size_t)t * 2 * inter + inter + i);
@@ -172,8 +182,7 @@ HB_EXPORT int hb_swiglu(const void* gate_up, void* out, int is_bf16, int tokens,
     if (tokens > 65535) return HB_UNSUPPORTED_SIZE;
     if (is_bf16 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
         dim3 grid8((inter / 8 + 255) / 256, tokens);
-        swiglu_bf16x8_kernel<<<grid8, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
-        return launch_status();
+        return launch_after_previous(swiglu_bf16x8_kernel, grid8, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
     }
     dim3 grid((inter + 255) / 256, tokens);
     if (is_bf16)
@@ -306,13 +315,16 @@ __global__ void rope_kv_store_bf16x8_kernel(__nv_bfloat16* __restrict__ x, int s
                                             const int* __restrict__ token_row, int page_size, int pages, int* status) {
     const int t = blockIdx.x;
     const int half = head_dim >> 1, chunks = half >> 3;  // 8-pair chunks per head
-    const int pos = positions[t];
-    if (pos < 0 || pos >= max_positions) {
+    let_next_kernel_start();
+    const int pos = positions[t];  // positions and tables come with the step's one copy from the host, not from a kernel
+    const bool pos_ok = pos >= 0 && pos < max_positions;
+    const int block = pos_ok ? pos / page_size : 0;
+    const int page = pos_ok && block < table_width ? block_table[(size_t)token_row[t] * table_width + block] : -1;
+    wait_for_previous_kernels();
+    if (!pos_ok) {
         if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, HB_STATUS_BAD_POSITION);
         return;
     }
-    const int block = pos / page_size;
-    const int page = block < table_width ? block_table[(size_t)token_row[t] * table_width + block] : -1;
     const bool page_ok = page >= 0 && page < pages;
     if (!page_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, HB_STATUS_BAD_PAGE);
     const int slot = pos - block * page_size;
@@ -363,10 +375,9 @@ HB_EXPORT int hb_rope_kv_store(void* x, int is_bf16, int tokens, int stride, int
         const int items = (q_heads + 2 * kv_heads) * (head_dim / 16);
         const int threads = items >= 256 ? 256 : 128;
         const dim3 grid8(tokens, tokens >= 512 ? 1 : min(8, (items + threads - 1) / threads));
-        rope_kv_store_bf16x8_kernel<<<grid8, threads, 0, stream>>>((__nv_bfloat16*)x, stride, q_heads, kv_heads, head_dim, positions,
-                                                                   (const float2*)table, max_positions, (__nv_bfloat16*)cache, block_table,
-                                                                   table_width, token_row, page_size, pages, status);
-        return launch_status();
+        return launch_after_previous(rope_kv_store_bf16x8_kernel, grid8, threads, 0, stream, (__nv_bfloat16*)x, stride, q_heads, kv_heads, head_dim,
+                                     positions, (const float2*)table, max_positions, (__nv_bfloat16*)cache, block_table, table_width, token_row,
+                                     page_size, pages, status);
     }
     const int pairs = (q_heads + 2 * kv_heads) * (head_dim / 2);
     const int slices = tokens >= 512 ? 1 : min(16, (pairs + 255) / 256);

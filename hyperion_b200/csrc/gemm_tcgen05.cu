@@ -138,6 +138,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ C
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    let_next_kernel_start();
     // blockIdx.x runs fastest over the tiles of map_a's rows, so blocks that are resident together share map_b's tile in L2
     const int row0 = blockIdx.x * BM;  // first row of map_a's operand
     const int col0 = blockIdx.y * BN;  // first row of map_b's operand
@@ -163,7 +164,22 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ C
 
     if (warp == 0) {
         if (lane == 0) {  // producer
-            for (int i = 0; i < n_kb; ++i) {
+            // The first ring of weight tiles is fetched before the kernels ahead in the stream have finished
+            // (no kernel writes weights); the activations, which they produce, follow after the wait.
+            const int ahead = min(n_kb, L::STAGES);
+            for (int i = 0; i < ahead; ++i) {
+                unsigned char* a_tile = tiles + (size_t)i * L::STAGE_BYTES;
+                mbar_expect_tx(&full[i], L::STAGE_BYTES);
+                if (SWAP) tma_load_2d(a_tile, &map_a, &full[i], (kb_begin + i) * BK, row0);
+                else tma_load_2d(a_tile + L::A_BYTES, &map_b, &full[i], (kb_begin + i) * BK, col0);
+            }
+            wait_for_previous_kernels();
+            for (int i = 0; i < ahead; ++i) {
+                unsigned char* a_tile = tiles + (size_t)i * L::STAGE_BYTES;
+                if (SWAP) tma_load_2d(a_tile + L::A_BYTES, &map_b, &full[i], (kb_begin + i) * BK, col0);
+                else tma_load_2d(a_tile, &map_a, &full[i], (kb_begin + i) * BK, row0);
+            }
+            for (int i = ahead; i < n_kb; ++i) {
                 const int s = i % L::STAGES;
                 if (!mbar_wait(&empty[s], ((i / L::STAGES) & 1) ^ 1, failed)) { *failed = 1; break; }
                 unsigned char* a_tile = tiles + (size_t)s * L::STAGE_BYTES;
@@ -193,6 +209,7 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ C
     } else {  // epilogue: warps 2..5 read TMEM lane quarters 2, 3, 0, 1
         const int quarter = warp & 3;
         const int r = row0 + quarter * 32 + lane;  // row of map_a's operand this thread holds
+        wait_for_previous_kernels();  // before this thread writes anything
         bool ok = n_kb > 0 ? mbar_wait(acc_full, 0, failed) : true;
         if (!ok) *failed = 1;
         tc_fence_after();
@@ -284,6 +301,8 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ C
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int m, int n, void* c, int ldc, int out_is_f32,
                                      const float* bias_f, const bf16* bias_h) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    let_next_kernel_start();
+    wait_for_previous_kernels();
     if (i >= (size_t)m * n) return;
     const int row = (int)(i / n), col = (int)(i - (size_t)row * n);
     float sum = 0.f;
@@ -332,8 +351,7 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams&
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_kernel<BN, EPI, SWAP><<<grid, THREADS, Layout<BN>::SMEM, stream>>>(map_a, map_b, p);
-    return launch_status();
+    return launch_after_previous(gemm_kernel<BN, EPI, SWAP>, grid, THREADS, Layout<BN>::SMEM, stream, map_a, map_b, p);
 }
 
 template <int BN>
@@ -387,7 +405,6 @@ HB_EXPORT int hb_gemm_bf16(const void* a, int lda, const void* w, int ldw, void*
                                 : launch_swap<64>(epi, map_w, map_x, p, grid, stream);
     if (code || splits == 1) return code;
     const size_t total = (size_t)m * n;
-    splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(workspace, splits, m, n, c, ldc, epilogue == EPI_F32, bias_f,
-                                                                             (const bf16*)bias_h);
-    return launch_status();
+    return launch_after_previous(splitk_reduce_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, (const float*)workspace, splits, m, n, c, ldc,
+                                 (int)(epilogue == EPI_F32), bias_f, (const bf16*)bias_h);
 }

@@ -267,6 +267,8 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, int row_
     const float* z = logits + (size_t)row * row_stride;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
+    let_next_kernel_start();
+    wait_for_previous_kernels();
     for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
         const float v = z[i];
         if (v > bv || (bi == 0x7fffffff && v == v)) { bv = v; bi = i; }
@@ -292,6 +294,7 @@ __global__ void argmax_final_kernel(const float* __restrict__ best_value, const 
     const int row = blockIdx.x;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
+    wait_for_previous_kernels();
     for (int c = threadIdx.x; c < chunks; c += 32) {
         const float ov = best_value[row * chunks + c];
         const int oi = best_index[row * chunks + c];
@@ -319,11 +322,9 @@ HB_EXPORT int hb_argmax(const float* logits, int row_stride, int rows, int vocab
     if (vocab <= 0 || chunks < 1 || chunks > 1024 || !workspace) return HB_BAD_ARGUMENT;
     float* values = reinterpret_cast<float*>(workspace);
     int* indices = reinterpret_cast<int*>(workspace) + (size_t)rows * chunks;
-    argmax_partial_kernel<<<dim3(rows, chunks), 256, 0, stream>>>(logits, row_stride, vocab, chunks, values, indices);
-    int code = launch_status();
+    int code = launch_after_previous(argmax_partial_kernel, dim3(rows, chunks), 256, 0, stream, logits, row_stride, vocab, chunks, values, indices);
     if (code) return code;
-    argmax_final_kernel<<<rows, 32, 0, stream>>>(values, indices, chunks, options, seen, seen_words, tokens);
-    return launch_status();
+    return launch_after_previous(argmax_final_kernel, rows, 32, 0, stream, (const float*)values, (const int*)indices, chunks, options, seen, seen_words, tokens);
 }
 
 namespace {
