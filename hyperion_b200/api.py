@@ -11,8 +11,10 @@ from collections import deque
 from pathlib import Path
 from typing import Any, Optional, Sequence
 
+import numpy as np
 import torch
 
+from . import host as host_runtime
 from .cache.manager import CacheManager, OutOfPages
 from .config.generation import GenerationDefaults, read_generation_defaults
 from .engine.batch import BadStep, StepEntry
@@ -130,73 +132,94 @@ class Engine:
             num_pages=self.cache.num_pages, page_size=self.page_size, max_seq_len=limit,
             max_batch=min(max_batch or self.cache.max_requests, self.cache.max_requests), max_batch_tokens=max_batch_tokens,
             prefill_chunk_busy=prefill_chunk_busy, eos_token_ids=tuple(self.defaults.eos_token_ids), max_in_flight=2 if lookahead else 1))
-        for index, (prompt, params) in enumerate(zip(prompts, per_prompt)):
-            scheduler.enqueue(Request(index, prompt, params.validated()))
+        # Requests are known to the scheduler by keys 0..n-1 (their order here) and to the cache by keys of its own.
+        sched_keys = [scheduler.enqueue(Request(index, prompt, params.validated())) for index, (prompt, params) in enumerate(zip(prompts, per_prompt))]
+        assert sched_keys == list(range(len(prompts)))
+        per_prompt = [p.validated() for p in per_prompt]
+        base_options = np.asarray([pack_options(p, 0, 0) for p in per_prompt], dtype=np.int32).reshape(len(prompts), 8)
+        greedy = np.asarray([p.greedy for p in per_prompt], dtype=bool)
+        cache_key = np.full(len(prompts), -1, dtype=np.int64)  # the cache's key of each request once it is live
         outputs: list[list[int]] = [[] for _ in prompts]
         reasons: list[Optional[str]] = [None] * len(prompts)
-        params_of = {index: request.params for index, request in enumerate(scheduler.waiting)}
 
-        def handle(events):
-            for event in events:
-                if event.kind == "token":
-                    outputs[event.request].append(event.token)
+        def take_events():
+            keys, kinds, tokens, texts = scheduler.take_event_arrays()
+            for key, kind, token, text in zip(keys.tolist(), kinds.tolist(), tokens.tolist(), texts):
+                if kind == 0:
+                    outputs[key].append(token)
                     if on_token is not None:
-                        on_token(event.request, event.token)
+                        on_token(key, token)
                 else:
-                    reasons[event.request] = event.reason
+                    reasons[key] = text
+
+        def free_released():
+            for key in scheduler.take_released_keys().tolist():
+                if cache_key[key] >= 0 and self.cache.has(key):
+                    self.cache.free(key)
+                cache_key[key] = -1
 
         depth = 2 if lookahead else 1
-        in_flight: deque = deque()  # (plan, requests of its sampled rows, pinned ids, event), oldest first
+        in_flight: deque = deque()  # (plan, pinned ids or None, event), oldest first
         newest: Optional[tuple[int, torch.Tensor]] = None  # (plan step, its sampled ids on the device)
 
         def launch(plan):
             nonlocal newest
-            entries, options, places, sampled_rows = [], [], {}, []
-            for index, row in enumerate(plan.rows):
-                if not self.cache.has(row.request):
-                    self.cache.add_request(row.request)
-                tokens = row.tokens
-                if row.token_from is not None:  # sampled by the plan before, still on the device
-                    step, place = row.token_from
-                    if newest is None or newest[0] != step:
-                        raise RuntimeError(f"plan {plan.step} wants a token of plan {step}, which is not the one before it")
-                    places[index], tokens = place, [0]
-                entries.append(StepEntry(row.request, tokens, [len(tokens) - 1] if row.sample else []))
-                if row.sample:
-                    sampled_rows.append(row.request)
-                    options.extend(pack_options(params_of[row.request], row.sampled_before, self.cache.slot(row.request)))
-            logits = self.runner.step(entries, {"sampling_options": (options, (len(options) // 8, 8))} if options else None,
-                                      device_tokens=(newest[1], places) if places else None)
+            for key in plan.keys[cache_key[plan.keys] < 0].tolist():  # first portion of a prompt: the request becomes live
+                self.cache.add_request(key)
+                cache_key[key] = self.cache.keys.known(key)
+            tokens, places = plan.tokens, None
+            pending = np.flatnonzero(plan.from_step >= 0)
+            if len(pending):  # sampled by the plan before, still on the device
+                if newest is None or np.any(plan.from_step[pending] != newest[0]):
+                    raise RuntimeError(f"plan {plan.step} wants tokens of a plan that is not the one before it")
+                starts = np.cumsum(plan.counts) - plan.counts
+                tokens = tokens.copy()
+                tokens[starts[pending]] = 0
+                places = dict(zip(pending.tolist(), plan.from_index[pending].tolist()))
+            sampled_rows = np.flatnonzero(plan.sample)
+            want = (np.cumsum(plan.counts)[sampled_rows] - 1).astype(np.int32)
+            extra = None
+            if len(sampled_rows):
+                options = base_options[plan.keys[sampled_rows]]
+                options[:, 6] = plan.sampled_before[sampled_rows]
+                slots = np.empty(len(plan.keys), np.int32)
+                lengths = np.empty(len(plan.keys), np.int32)
+                keys = np.ascontiguousarray(cache_key[plan.keys])
+                host_runtime.check(host_runtime.library().hb_cache_lengths(self.cache.native, len(keys), host_runtime.address(keys),
+                                                                           host_runtime.address(lengths), host_runtime.address(slots)))
+                options[:, 7] = slots[sampled_rows]
+                extra = {"sampling_options": (options, (len(sampled_rows), 8))}
+            logits = self.runner.step_arrays(plan.keys.tolist(), np.ascontiguousarray(cache_key[plan.keys]), plan.counts, tokens, want, extra,
+                                             device_tokens=(newest[1], places) if places else None)
             if logits is None:
-                return plan, sampled_rows, None, None
+                return plan, None, None
             ring = plan.step % depth
-            tokens = self.sampler.sample(logits, self.runner.last_context.extra["sampling_options"],
-                                         out=self._token_ring[ring, : len(sampled_rows)],
-                                         all_greedy=all(params_of[request].greedy for request in sampled_rows))
-            newest = (plan.step, tokens)
-            host = self._token_staging[ring, : len(sampled_rows)]
-            host.copy_(tokens, non_blocking=True)
+            chosen = self.sampler.sample(logits, self.runner.last_context.extra["sampling_options"],
+                                         out=self._token_ring[ring, : len(sampled_rows)], all_greedy=bool(greedy[plan.keys[sampled_rows]].all()))
+            newest = (plan.step, chosen)
+            pinned = self._token_staging[ring, : len(sampled_rows)]
+            pinned.copy_(chosen, non_blocking=True)
             event = torch.cuda.Event()
             event.record()
-            return plan, sampled_rows, host, event
+            return plan, pinned, event
 
-        def retire(plan, sampled_rows, host, event):
-            sampled = {}
+        def retire(plan, pinned, event):
             if event is not None:
                 event.synchronize()
-                sampled = dict(zip(sampled_rows, host.tolist()))
-            handle(scheduler.complete(plan, sampled))
-            self._free_released(scheduler)
+            scheduler.complete_arrays(plan.step, pinned.numpy() if pinned is not None else np.empty(0, np.int32))
+            take_events()
+            free_released()
 
         while True:
-            plan = scheduler.next_plan() if len(in_flight) < depth else None
-            handle(scheduler.take_events())
+            plan = scheduler.next_plan_arrays() if len(in_flight) < depth else None
+            take_events()
             if plan is not None:
                 try:
                     in_flight.append(launch(plan))
                 except Exception as error:  # the step's requests fail, the others go on
-                    handle(scheduler.fail(plan, f"{type(error).__name__}: {error}"))
-                    self._free_released(scheduler)
+                    scheduler.fail_step(plan.step, f"{type(error).__name__}: {error}")
+                    take_events()
+                    free_released()
                     if not isinstance(error, (OutOfPages, BadStep)):
                         raise
                     continue
@@ -208,11 +231,6 @@ class Engine:
                 raise RuntimeError("the scheduler has requests but plans nothing")
         self.check()
         return (outputs, reasons) if return_reasons else outputs
-
-    def _free_released(self, scheduler) -> None:
-        for request in scheduler.take_released():
-            if self.cache.has(request):
-                self.cache.free(request)
 
     def check(self) -> None:
         """Wait for the device and raise if a kernel flagged a problem."""

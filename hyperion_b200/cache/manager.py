@@ -19,65 +19,55 @@ bookkeeping can be exercised without one.
 """
 from __future__ import annotations
 
-from collections import deque
-from dataclasses import dataclass, field
+import ctypes
+from dataclasses import dataclass
 from typing import Hashable, Optional, Sequence
 
+import numpy as np
 import torch
 
+from .. import host
+from ..host import CacheError, OutOfPages
 from ..parts.base import PagedKV, RequestState
 
 NO_PAGE = -1
 
 
-class OutOfPages(RuntimeError):
-    """A request asked for more pages than its group's pool has free; nothing was taken."""
-
-
-class CacheError(RuntimeError):
-    """The manager was used inconsistently (unknown request, page freed twice, ...)."""
-
-
 class PagePool:
-    """Free list of page ids with first-in first-out reuse and double-use detection."""
+    """Free list of page ids with first-in first-out reuse and double-use detection (``hb::PagePool``)."""
 
     def __init__(self, num_pages: int):
-        if num_pages <= 0:
-            raise ValueError("a page pool needs at least one page")
+        self._lib = host.library()
+        self._handle = ctypes.c_void_p()
+        host.check(self._lib.hb_pool_new(num_pages, ctypes.byref(self._handle)))
         self.num_pages = num_pages
-        self._free: deque[int] = deque(range(num_pages))
-        self._held: set[int] = set()
+
+    def __del__(self):
+        if getattr(self, "_handle", None):
+            self._lib.hb_pool_delete(self._handle)
+            self._handle = None
 
     @property
     def available(self) -> int:
-        return len(self._free)
+        return self._lib.hb_pool_available(self._handle)
 
     def take(self) -> int:
-        if not self._free:
-            raise OutOfPages("no free page")
-        page = self._free.popleft()
-        self._held.add(page)
-        return page
+        page = ctypes.c_int()
+        host.check(self._lib.hb_pool_take(self._handle, ctypes.byref(page)))
+        return page.value
 
     def give_back(self, page: int) -> None:
-        if page not in self._held:
-            raise CacheError(f"page {page} given back but not held")
-        self._held.remove(page)
-        self._free.append(page)
+        host.check(self._lib.hb_pool_give_back(self._handle, page))
 
     def check(self) -> None:
         """Every page is either free or held, exactly once."""
-        free = list(self._free)
-        if len(set(free)) != len(free) or set(free) & self._held or len(free) + len(self._held) != self.num_pages:
-            raise CacheError("page accounting broken")
+        host.check(self._lib.hb_pool_check(self._handle))
 
 
 @dataclass
 class PagedGroup:
     spec: PagedKV
     users: list[int]  # schedule entries whose mixers own a cache in this group, in order
-    pool: PagePool
-    tables: dict[Hashable, list[int]] = field(default_factory=dict)
     storage: Optional[torch.Tensor] = None  # [users, pages, 2, kv_heads, page_size, head_dim]
 
 
@@ -88,13 +78,10 @@ class StateGroup:
     storage: Optional[torch.Tensor] = None  # [users, slots, *shape]
 
 
-@dataclass
-class _Request:
-    slot: int
-    length: int = 0  # tokens whose cache entries are written
-
-
 class CacheManager:
+    """Groups cache users by need, owns the tensors, and keeps pages, tables, slots and lengths in
+    the host runtime's ``hb::CacheIndex`` (``csrc/host/cache_index.cpp``)."""
+
     def __init__(self, users: Sequence[tuple[int, PagedKV | RequestState]], page_size: int, num_pages: int, max_requests: int,
                  dtype: torch.dtype = torch.float32, device: Optional[torch.device] = None):
         if page_size <= 0 or page_size & (page_size - 1):
@@ -109,7 +96,7 @@ class CacheManager:
             if isinstance(need, PagedKV):
                 group = next((i for i, g in enumerate(self.paged) if g.spec == need), None)
                 if group is None:
-                    self.paged.append(PagedGroup(need, [], PagePool(num_pages)))
+                    self.paged.append(PagedGroup(need, []))
                     group = len(self.paged) - 1
                 self.paged[group].users.append(entry)
                 self._where[entry] = ("paged", group, len(self.paged[group].users) - 1)
@@ -122,8 +109,11 @@ class CacheManager:
                 self._where[entry] = ("state", group, len(self.states[group].users) - 1)
             else:
                 raise TypeError(f"unknown cache request {need!r}")
-        self._requests: dict[Hashable, _Request] = {}
-        self._free_slots: deque[int] = deque(range(max_requests))
+        self._lib = host.library()
+        self._handle = ctypes.c_void_p()
+        windows = host.ints([g.spec.window for g in self.paged])
+        host.check(self._lib.hb_cache_new(page_size, num_pages, max_requests, len(self.paged), host.address(windows), ctypes.byref(self._handle)))
+        self.keys = host.KeyMap()
         self.device = device
         if device is not None:
             for g in self.paged:
@@ -131,28 +121,60 @@ class CacheManager:
             for s in self.states:
                 s.storage = torch.zeros((len(s.users), max_requests, *s.spec.shape), dtype=s.spec.dtype, device=device)
 
+    def __del__(self):
+        if getattr(self, "_handle", None):
+            self._lib.hb_cache_delete(self._handle)
+            self._handle = None
+
+    @property
+    def native(self) -> ctypes.c_void_p:
+        """The ``HbCache*`` for calls that take the index itself (the step assembler)."""
+        return self._handle
+
     # ------------------------------------------------------------------ lookups
     def where(self, entry: int) -> tuple[str, int, int]:
         return self._where[entry]
 
+    def _key(self, request: Hashable) -> int:
+        key = self.keys.known(request)
+        if key is None or not self._lib.hb_cache_has(self._handle, key):
+            raise CacheError(f"unknown request {request!r}")
+        return key
+
     def has(self, request: Hashable) -> bool:
-        return request in self._requests
+        key = self.keys.known(request)
+        return key is not None and bool(self._lib.hb_cache_has(self._handle, key))
 
     def length(self, request: Hashable) -> int:
-        return self._requests[request].length
+        value = ctypes.c_int()
+        host.check(self._lib.hb_cache_length(self._handle, self._key(request), ctypes.byref(value)))
+        return value.value
 
     def slot(self, request: Hashable) -> int:
-        return self._requests[request].slot
+        value = ctypes.c_int()
+        host.check(self._lib.hb_cache_slot(self._handle, self._key(request), ctypes.byref(value)))
+        return value.value
 
     def table(self, group: int, request: Hashable) -> list[int]:
-        return self.paged[group].tables[request]
+        """A copy of the request's block table in ``group`` (``NO_PAGE`` where a window has passed)."""
+        key, size = self._key(request), ctypes.c_int()
+        host.check(self._lib.hb_cache_table_size(self._handle, group, key, ctypes.byref(size)))
+        pages = np.empty(size.value, dtype=np.int32)
+        host.check(self._lib.hb_cache_table(self._handle, group, key, host.address(pages), size.value))
+        return pages.tolist()
 
     @property
     def live_requests(self) -> list[Hashable]:
-        return list(self._requests)
+        keys, count = np.empty(self.max_requests, dtype=np.int64), ctypes.c_int()
+        host.check(self._lib.hb_cache_live(self._handle, host.address(keys), self.max_requests, ctypes.byref(count)))
+        return [self.keys.name(int(k)) for k in keys[: count.value]]
 
     def free_pages(self, group: int = 0) -> int:
-        return self.paged[group].pool.available if self.paged else 0
+        if not self.paged:
+            return 0
+        value = ctypes.c_int()
+        host.check(self._lib.hb_cache_free_pages(self._handle, group, ctypes.byref(value)))
+        return value.value
 
     def bytes_per_token(self) -> int:
         total = 0
@@ -163,98 +185,58 @@ class CacheManager:
 
     # ------------------------------------------------------------------ requests
     def add_request(self, request: Hashable) -> int:
-        if request in self._requests:
+        if self.has(request):
             raise CacheError(f"request {request!r} is already live")
-        if not self._free_slots:
-            raise OutOfPages(f"all {self.max_requests} request slots are taken")
-        slot = self._free_slots.popleft()
-        self._requests[request] = _Request(slot)
-        for g in self.paged:
-            g.tables[request] = []
+        slot = ctypes.c_int()
+        host.check(self._lib.hb_cache_add(self._handle, self.keys.key(request), ctypes.byref(slot)))
         for s in self.states:
             if s.storage is not None:
-                s.storage[:, slot].zero_()
-        return slot
-
-    def _first_needed_block(self, group: PagedGroup, length: int) -> int:
-        """The first block a query at position ``length`` (the next one) can still read."""
-        if group.spec.window <= 0:
-            return 0
-        return max(0, length - group.spec.window + 1) // self.page_size
+                s.storage[:, slot.value].zero_()
+        return slot.value
 
     def pages_needed(self, request: Hashable, new_tokens: int) -> list[int]:
         """Pages each paged group must add so positions up to length + new_tokens - 1 have one."""
-        length = self._requests[request].length
-        blocks = -(-(length + new_tokens) // self.page_size)
-        return [max(0, blocks - len(g.tables[request])) for g in self.paged]
+        need = np.zeros(max(1, len(self.paged)), dtype=np.int32)
+        host.check(self._lib.hb_cache_pages_needed(self._handle, self._key(request), new_tokens, host.address(need)))
+        return need[: len(self.paged)].tolist()
 
     def extend(self, request: Hashable, new_tokens: int) -> None:
         """Give every position of the next ``new_tokens`` tokens a page in every group, or take nothing."""
-        need = self.pages_needed(request, new_tokens)
-        for g, n in zip(self.paged, need):
-            if n > g.pool.available:
-                raise OutOfPages(f"request {request!r} needs {n} more pages, {g.pool.available} free")
-        for g, n in zip(self.paged, need):
-            g.tables[request].extend(g.pool.take() for _ in range(n))
+        self.extend_all([(request, new_tokens)])
 
     def extend_all(self, work: Sequence[tuple[Hashable, int]]) -> None:
         """``extend`` for several requests at once: all of them or none."""
-        totals = [0] * len(self.paged)
-        for request, n in work:
-            if request not in self._requests:
-                raise CacheError(f"unknown request {request!r}")
-            for i, pages in enumerate(self.pages_needed(request, n)):
-                totals[i] += pages
-        for g, n in zip(self.paged, totals):
-            if n > g.pool.available:
-                raise OutOfPages(f"the step needs {n} more pages, {g.pool.available} free")
-        for request, n in work:
-            self.extend(request, n)
+        keys = host.ints([self._key(request) for request, _ in work], np.int64)
+        counts = host.ints([n for _, n in work])
+        self.extend_keys(keys, counts)
+
+    def extend_keys(self, keys: np.ndarray, counts: np.ndarray) -> None:
+        """``extend_all`` by runtime keys (int64) and token counts (int32)."""
+        host.check(self._lib.hb_cache_extend_all(self._handle, len(keys), host.address(keys), host.address(counts)))
 
     def advance(self, request: Hashable, new_tokens: int) -> list[tuple[int, int]]:
         """The tokens are written: move the length and give back pages a window has passed.
         Returns the (group, page) pairs released."""
-        record = self._requests[request]
-        record.length += new_tokens
-        released = []
-        for index, g in enumerate(self.paged):
-            table = g.tables[request]
-            if len(table) * self.page_size < record.length:
-                raise CacheError(f"request {request!r} advanced past its pages")
-            for block in range(min(self._first_needed_block(g, record.length), len(table))):
-                if table[block] != NO_PAGE:
-                    g.pool.give_back(table[block])
-                    released.append((index, table[block]))
-                    table[block] = NO_PAGE
-        return released
+        key, count = self._key(request), ctypes.c_int()
+        length = self.length(request)
+        capacity = (length + new_tokens) // self.page_size * max(1, len(self.paged)) + 1  # no more blocks than that exist
+        pairs = np.empty(2 * capacity, dtype=np.int32)
+        host.check(self._lib.hb_cache_advance(self._handle, key, new_tokens, host.address(pairs), capacity, ctypes.byref(count)))
+        return [(int(pairs[2 * i]), int(pairs[2 * i + 1])) for i in range(count.value)]
+
+    def advance_keys(self, keys: np.ndarray, counts: np.ndarray) -> None:
+        host.check(self._lib.hb_cache_advance_all(self._handle, len(keys), host.address(keys), host.address(counts)))
 
     def free(self, request: Hashable) -> None:
-        record = self._requests.pop(request, None)
-        if record is None:
+        key = self.keys.known(request)
+        if key is None or not self._lib.hb_cache_has(self._handle, key):
             raise CacheError(f"request {request!r} is not live")
-        for g in self.paged:
-            for page in g.tables.pop(request):
-                if page != NO_PAGE:
-                    g.pool.give_back(page)
-        self._free_slots.append(record.slot)
+        host.check(self._lib.hb_cache_free(self._handle, key))
+        self.keys.forget(request)
 
     def check(self) -> None:
         """Accounting invariants: no page lost or held twice; every held page is in exactly one table."""
-        for g in self.paged:
-            g.pool.check()
-            seen: set[int] = set()
-            for table in g.tables.values():
-                for page in table:
-                    if page == NO_PAGE:
-                        continue
-                    if page in seen:
-                        raise CacheError(f"page {page} is in two tables")
-                    seen.add(page)
-            if seen != g.pool._held:
-                raise CacheError("held pages and tables disagree")
-        slots = [r.slot for r in self._requests.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots) or len(slots) + len(self._free_slots) != self.max_requests:
-            raise CacheError("slot accounting broken")
+        host.check(self._lib.hb_cache_check(self._handle))
 
     # ------------------------------------------------------------------ views for the parts
     def paged_storage(self, entry: int) -> torch.Tensor:

@@ -1,4 +1,5 @@
-"""Compiles the CUDA sources of this folder for sm_100a and loads them with ctypes.
+"""Compiles the CUDA sources of this folder for sm_100a, and the C++ host runtime of ``host/``, and
+loads them with ctypes.
 
 Each ``.cu`` file becomes one shared library, built on first use with ``nvcc`` and kept beside the
 package under ``_build/`` (or in a per-user temporary folder when the package folder cannot be
@@ -141,6 +142,57 @@ def build_many(requests: Iterable[tuple[str, Mapping[str, object]]], workers: in
         futures = [pool.submit(_compile, *item) for item in pending]
         for future in futures:
             future.result()
+
+
+# ---------------------------------------------------------------------- the host runtime (C++, no CUDA)
+HOST_DIR = SOURCE_DIR / "host"
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall"]
+
+
+def _host_compiler() -> str:
+    for candidate in (os.environ.get("HYPERION_B200_CXX"), os.environ.get("CXX"), "g++", "c++", "clang++"):
+        found = shutil.which(candidate) if candidate else None
+        if found:
+            return found
+    raise BuildError("no C++ compiler found (looked at HYPERION_B200_CXX, CXX, g++, c++, clang++): the host runtime cannot be built")
+
+
+def host_library_path() -> Path:
+    digest = hashlib.sha256()
+    for path in sorted(HOST_DIR.iterdir()):
+        if path.suffix in (".cpp", ".hpp", ".h"):
+            digest.update(path.name.encode())
+            digest.update(path.read_bytes())
+    digest.update(" ".join(HOST_FLAGS).encode())
+    return _build_dir() / f"hb_host_runtime-{digest.hexdigest()[:16]}.so"
+
+
+def load_host() -> ctypes.CDLL:
+    """The host runtime (cache index, scheduler, step assembly) of ``csrc/host``, compiled on first use."""
+    with _lock:
+        if "host_runtime" in _loaded:
+            return _loaded["host_runtime"]
+    target = host_library_path()
+    if not target.is_file():
+        scratch = target.with_suffix(f".tmp{os.getpid()}.so")
+        sources = sorted(str(p) for p in HOST_DIR.glob("*.cpp"))
+        command = [_host_compiler(), *HOST_FLAGS, "-I", str(HOST_DIR), "-o", str(scratch), *sources]
+        started = time.time()
+        print("[hyperion_b200] compiling the host runtime ...", file=sys.stderr, flush=True)
+        done = subprocess.run(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if done.returncode != 0:
+            if scratch.exists():
+                scratch.unlink()
+            raise BuildError(f"the host runtime failed to compile ({' '.join(command)}):\n{done.stdout}")
+        os.replace(scratch, target)
+        print(f"[hyperion_b200] built {target.name} in {time.time() - started:.1f} s", file=sys.stderr, flush=True)
+    try:
+        library = ctypes.CDLL(str(target))
+    except OSError as error:
+        raise BuildError(f"cannot load {target}: {error}") from None
+    with _lock:
+        _loaded.setdefault("host_runtime", library)
+        return _loaded["host_runtime"]
 
 
 def all_modules() -> list[tuple[str, dict]]:

@@ -10,11 +10,15 @@ with a single transfer.
 """
 from __future__ import annotations
 
+import ctypes
+from collections.abc import Sequence
 from dataclasses import dataclass, field
-from typing import Any, Callable, Hashable, Optional, Sequence
+from typing import Any, Callable, Hashable, Optional
 
 import numpy as np
 import torch
+
+from .. import host as host_runtime
 
 
 @dataclass
@@ -37,6 +41,27 @@ class Row:
     count: int
     position: int  # position of its first token
     slot: int
+
+
+class Rows(Sequence):
+    """The rows of a step as arrays (``starts``, ``counts``, ``positions``, ``slots``: int32, one entry
+    per row); indexing or iterating gives :class:`Row` objects, made when asked for."""
+
+    def __init__(self, names: Sequence[Hashable], starts: np.ndarray, counts: np.ndarray, positions: np.ndarray, slots: np.ndarray):
+        self.names, self.starts, self.counts, self.positions, self.slots = names, starts, counts, positions, slots
+
+    def __len__(self) -> int:
+        return len(self.counts)
+
+    def __getitem__(self, index):
+        if isinstance(index, slice):
+            return [self[i] for i in range(*index.indices(len(self)))]
+        return Row(self.names[index], int(self.starts[index]), int(self.counts[index]), int(self.positions[index]), int(self.slots[index]))
+
+    @property
+    def longest_context(self) -> int:
+        """The largest position any row reaches in this step, plus one."""
+        return int((self.positions + self.counts).max())
 
 
 @dataclass
@@ -68,6 +93,7 @@ class MetadataPacker:
         self.hosts: list[torch.Tensor] = []
         self.events: list[Optional[torch.cuda.Event]] = [None] * self.RING
         self.dev: Optional[torch.Tensor] = None
+        self.generation = 0  # counts reallocations of the device buffer
         self._index = 0
         self._reserve(capacity)
 
@@ -80,11 +106,24 @@ class MetadataPacker:
         self.hosts = [torch.empty(capacity, dtype=torch.int32, pin_memory=self.device.type == "cuda") for _ in range(self.RING)]
         self.events = [None] * self.RING
         self.dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
+        self.generation += 1
 
     def begin(self) -> None:
+        """Take the next staging buffer of the ring (waiting for the copy that last read it) and start an empty layout."""
         self._items: list[tuple[str, int, int, tuple[int, ...]]] = []
         self._cursor = 0
-        self._chunks: list[np.ndarray] = []
+        self._index = (self._index + 1) % self.RING
+        if self.events[self._index] is not None:
+            self.events[self._index].synchronize()
+            self.events[self._index] = None
+        self._words = self.hosts[self._index].numpy()
+
+    def _grow(self, needed: int) -> None:
+        """More room than the buffers have: new buffers (``generation`` tells users of the device buffer), what is written so far kept."""
+        written = self._words[: self._cursor].copy()
+        self._reserve(max(needed, 2 * self.capacity))
+        self._words = self.hosts[self._index].numpy()
+        self._words[: self._cursor] = written
 
     def add(self, name: str, values: Any, shape: Optional[tuple[int, ...]] = None) -> None:
         """Append an int32 array (a list of ints, a numpy array or a tensor); every array starts on a 16-byte boundary."""
@@ -92,24 +131,47 @@ class MetadataPacker:
             values = values.detach().cpu().numpy()
         array = np.asarray(values, dtype=np.int32).reshape(-1)
         count = array.size
-        shape = shape or (count,)
-        self._items.append((name, self._cursor, count, shape))
-        self._chunks.append(array)
-        padding = -count % 4
-        if padding:
-            self._chunks.append(np.zeros(padding, dtype=np.int32))
-        self._cursor += count + padding
+        start = (self._cursor + 3) & ~3
+        if start + count > self.capacity:
+            self._grow(start + count)
+        self._words[start : start + count] = array
+        self._items.append((name, start, count, shape or (count,)))
+        self._cursor = start + count
+
+    def add_step(self, cache, keys: np.ndarray, counts: np.ndarray, tokens: np.ndarray, want: np.ndarray, table_step: int) -> None:
+        """The arrays every step carries, written by the host runtime's step assembler straight into the staging
+        buffer: token_ids, positions, token_row, row_start, slots, want and one block table per paged group."""
+        groups = len(cache.paged)
+        layout = np.zeros(4 * (6 + groups), dtype=np.int64)
+        lib = host_runtime.library()
+        for attempt in range(2):
+            cursor = ctypes.c_int64(self._cursor)
+            code = lib.hb_step_pack(cache.native, len(keys), host_runtime.address(keys), host_runtime.address(counts), host_runtime.address(tokens),
+                                    len(want), host_runtime.address(want), table_step, self._words.ctypes.data, self.capacity, ctypes.byref(cursor),
+                                    host_runtime.address(layout))
+            if code == host_runtime.BAD_ARGUMENT and attempt == 0 and b"metadata needs" in lib.hb_host_last_error():
+                self._grow(int(lib.hb_host_last_error().split()[-2]))
+                continue
+            host_runtime.check(code)
+            break
+        self._cursor = cursor.value
+        names = ["token_ids", "positions", "token_row", "row_start", "slots", "want"] + [f"table{g}" for g in range(groups)]
+        for index, name in enumerate(names):
+            offset, count, rows, columns = (int(v) for v in layout[4 * index : 4 * index + 4])
+            if name == "want" and count == 0:
+                continue
+            self._items.append((name, offset, count, (rows, columns) if name.startswith("table") else (count,)))
+
+    def view(self, name: str) -> np.ndarray:
+        """What was written under ``name`` in the staging buffer of this step (host side)."""
+        for item, start, count, shape in self._items:
+            if item == name:
+                return self._words[start : start + count].reshape(shape)
+        raise KeyError(name)
 
     def finish(self) -> dict[str, torch.Tensor]:
-        if self._cursor > self.capacity:
-            self._reserve(max(self._cursor, 2 * self.capacity))
-        self._index = (self._index + 1) % self.RING
-        if self.events[self._index] is not None:
-            self.events[self._index].synchronize()
-        host = self.hosts[self._index]
         if self._cursor:
-            np.concatenate(self._chunks, out=host.numpy()[: self._cursor])  # straight into the pinned buffer
-            self.dev[: self._cursor].copy_(host[: self._cursor], non_blocking=True)
+            self.dev[: self._cursor].copy_(self.hosts[self._index][: self._cursor], non_blocking=True)
             if self.device.type == "cuda":
                 event = torch.cuda.Event()
                 event.record()
@@ -119,7 +181,7 @@ class MetadataPacker:
 
 @dataclass
 class StepContext:
-    rows: list[Row]
+    rows: Rows
     n_tokens: int
     token_ids: torch.Tensor  # [T] int32
     positions: torch.Tensor  # [T] int32

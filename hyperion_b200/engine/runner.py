@@ -15,10 +15,11 @@ import numpy as np
 import torch
 
 from .. import ops
-from ..cache.manager import NO_PAGE, CacheManager, OutOfPages
+from .. import host as host_runtime
+from ..cache.manager import CacheManager, OutOfPages
 from ..csrc import build
 from ..models.model import DecoderModel
-from .batch import BadStep, MetadataPacker, Row, StepContext, StepEntry
+from .batch import BadStep, MetadataPacker, Rows, StepContext, StepEntry
 
 
 GRAPH_TABLE_STEP = 64  # block-table widths of graphed steps are multiples of this many pages
@@ -33,6 +34,7 @@ class ModelRunner:
         self.cache = cache
         self.device = model.device
         self.packer = MetadataPacker(self.device, capacity=1 << 20)  # never reallocated below this: graphs keep its address
+        self._packer_generation = self.packer.generation
         self.planners = model.step_planners()
         build.build_many(model.kernel_modules())
         self.steps_run = 0
@@ -66,52 +68,32 @@ class ModelRunner:
                 raise BadStep(f"request {entry.request!r} would reach position {length + count}, the model's limit is {limit}")
 
     # ------------------------------------------------------------------ the batch on the device
-    def _context(self, entries: Sequence[StepEntry], extra_arrays=None, pad_tables: bool = False, device_places=None) -> StepContext:
-        rows: list[Row] = []
-        token_chunks, position_chunks, row_chunks = [], [], []
-        want: list[int] = []
-        start = 0
-        for index, entry in enumerate(entries):
-            position, count = self.cache.length(entry.request), len(entry.tokens)
-            rows.append(Row(entry.request, start, count, position, self.cache.slot(entry.request)))
-            token_chunks.append(np.asarray(entry.tokens, dtype=np.int32))
-            position_chunks.append(np.arange(position, position + count, dtype=np.int32))
-            row_chunks.append(np.full(count, index, dtype=np.int32))
-            want.extend(start + i for i in entry.want)
-            start += count
-        token_ids, positions, token_row = np.concatenate(token_chunks), np.concatenate(position_chunks), np.concatenate(row_chunks)
+    def _context(self, names, keys: np.ndarray, counts: np.ndarray, tokens: np.ndarray, want: np.ndarray, extra_arrays=None,
+                 pad_tables: bool = False, device_places=None) -> StepContext:
         packer = self.packer
         packer.begin()
-        packer.add("token_ids", token_ids)
-        packer.add("positions", positions)
-        packer.add("token_row", token_row)
-        packer.add("row_start", [row.start for row in rows] + [int(token_ids.size)])
-        packer.add("slots", [row.slot for row in rows])
-        if want:
-            packer.add("want", want)
-        for group in range(len(self.cache.paged)):
-            tables = [self.cache.table(group, row.request) for row in rows]
-            width = max(1, max(len(t) for t in tables))
-            if pad_tables:  # a replayed graph needs the same layout for many steps: widths in steps of GRAPH_TABLE_STEP
-                width = -(-width // GRAPH_TABLE_STEP) * GRAPH_TABLE_STEP
-            flat: list[int] = []
-            for table in tables:
-                flat.extend(table)
-                flat.extend([NO_PAGE] * (width - len(table)))
-            packer.add(f"table{group}", flat, (len(rows), width))
-        host = {"positions": positions, "token_row": token_row, "want": want, "page_size": self.cache.page_size}
+        # a replayed graph needs the same layout for many steps: its table widths are multiples of GRAPH_TABLE_STEP
+        packer.add_step(self.cache, keys, counts, tokens, want, GRAPH_TABLE_STEP if pad_tables else 0)
+        starts = packer.view("row_start")
+        starts = starts[:-1].copy()
+        rows = Rows(names, starts, counts, packer.view("positions")[starts], packer.view("slots").copy())
+        host = {"page_size": self.cache.page_size}
         if pad_tables:
-            host["context_cap"] = width * self.cache.page_size if self.cache.paged else 0
+            widest = max((packer.view(f"table{g}").shape[1] for g in range(len(self.cache.paged))), default=0)
+            host["context_cap"] = widest * self.cache.page_size
         for key, plan in self.planners.items():
             plan(rows, packer, host)
         for name, (values, shape) in (extra_arrays or {}).items():
             packer.add(name, values, shape)
         if device_places:  # last, so that the other arrays lie where a captured graph expects them
-            packer.add("device_token_pairs", [v for index, place in device_places.items() for v in (rows[index].start, place)])
+            packer.add("device_token_pairs", [v for index, place in device_places.items() for v in (int(starts[index]), place)])
         arrays = packer.finish()
+        if packer.generation != self._packer_generation:  # the device buffer moved: captured graphs point at the old one
+            self.graphs.clear()
+            self._packer_generation = packer.generation
         extra = {k: v for k, v in arrays.items() if k not in ("token_ids", "positions", "token_row", "row_start", "slots", "want")
                  and not k.startswith("table")}
-        return StepContext(rows=rows, n_tokens=int(token_ids.size), token_ids=arrays["token_ids"], positions=arrays["positions"],
+        return StepContext(rows=rows, n_tokens=len(tokens), token_ids=arrays["token_ids"], positions=arrays["positions"],
                            token_row=arrays["token_row"], row_start=arrays["row_start"], want_rows=arrays.get("want"),
                            n_want=len(want), paged_tables=[arrays[f"table{g}"] for g in range(len(self.cache.paged))],
                            slots=arrays["slots"], extra=extra, host=host)
@@ -128,51 +110,87 @@ class ModelRunner:
         through the host."""
         entries = list(entries)
         self._validate(entries)
-        if device_tokens is not None:
-            source, places = device_tokens
-            if source.dtype != torch.int32 or source.device != self.device or not source.is_contiguous():
-                raise BadStep("device tokens must be a contiguous int32 tensor on the engine's device")
-            for index, place in places.items():
-                if not 0 <= index < len(entries) or len(entries[index].tokens) != 1 or not 0 <= place < source.numel():
-                    raise BadStep(f"device token {place} for entry {index}: only a single-token entry can take a token of the tensor")
+        self._check_device_tokens(device_tokens, [len(e.tokens) for e in entries])
         added = []
         try:
             for entry in entries:
                 if not self.cache.has(entry.request):
                     self.cache.add_request(entry.request)
                     added.append(entry.request)
-            self.cache.extend_all([(entry.request, len(entry.tokens)) for entry in entries])
+            keys = np.asarray([self.cache.keys.known(entry.request) for entry in entries], dtype=np.int64)
+            counts = np.asarray([len(entry.tokens) for entry in entries], dtype=np.int32)
+            self.cache.extend_keys(keys, counts)
         except OutOfPages:
             for request in added:
                 self.cache.free(request)
             raise
-        key = self._graph_key(entries, extra_arrays)
-        context = self._context(entries, extra_arrays, pad_tables=key is not None,
+        tokens = np.concatenate([np.asarray(entry.tokens, dtype=np.int32) for entry in entries])
+        starts = np.concatenate(([0], np.cumsum(counts)[:-1]))
+        want = np.asarray([int(starts[i]) + w for i, entry in enumerate(entries) for w in entry.want], dtype=np.int32)
+        return self._run([entry.request for entry in entries], keys, counts, tokens, want, extra_arrays, device_tokens)
+
+    def step_arrays(self, names, keys: np.ndarray, counts: np.ndarray, tokens: np.ndarray, want: np.ndarray, extra_arrays=None,
+                    device_tokens=None) -> Optional[torch.Tensor]:
+        """:meth:`step` for callers that hold the batch as arrays already (the generation loop): ``keys`` are the cache
+        manager's keys of live requests (int64), ``counts`` the tokens per row, ``tokens`` all rows' tokens back to back,
+        ``want`` flat indices among them (all int32).  The same checks, done on whole arrays."""
+        vocab, limit = self.model.spec.vocab_size, self.model.spec.max_positions
+        if len(keys) == 0 or len(counts) != len(keys) or int(counts.sum()) != len(tokens):
+            raise BadStep("a step needs at least one row, and as many tokens as its rows count")
+        if len(np.unique(keys)) != len(keys):
+            raise BadStep("a request appears twice in one step")
+        if int(counts.min()) < 1:
+            raise BadStep("a row brings no tokens")
+        if int(tokens.min()) < 0 or int(tokens.max()) >= vocab:
+            raise BadStep(f"tokens must be integers in 0..{vocab - 1}")
+        if len(want) and (int(want.min()) < 0 or int(want.max()) >= len(tokens)):
+            raise BadStep("a wanted place is outside the step's tokens")
+        lengths, slots = np.empty(len(keys), np.int32), np.empty(len(keys), np.int32)
+        host_runtime.check(host_runtime.library().hb_cache_lengths(self.cache.native, len(keys), host_runtime.address(keys), host_runtime.address(lengths),
+                                                                   host_runtime.address(slots)))
+        if int(lengths.min()) < 0:
+            raise BadStep("a row names a request the cache does not know")
+        if int((lengths + counts).max()) > limit:
+            raise BadStep(f"a request would pass the model's limit of {limit} positions")
+        self._check_device_tokens(device_tokens, counts)
+        self.cache.extend_keys(keys, counts)
+        return self._run(names, keys, counts, tokens, want, extra_arrays, device_tokens)
+
+    def _check_device_tokens(self, device_tokens, counts) -> None:
+        if device_tokens is None:
+            return
+        source, places = device_tokens
+        if source.dtype != torch.int32 or source.device != self.device or not source.is_contiguous():
+            raise BadStep("device tokens must be a contiguous int32 tensor on the engine's device")
+        for index, place in places.items():
+            if not 0 <= index < len(counts) or counts[index] != 1 or not 0 <= place < source.numel():
+                raise BadStep(f"device token {place} for entry {index}: only a single-token entry can take a token of the tensor")
+
+    def _run(self, names, keys, counts, tokens, want, extra_arrays, device_tokens) -> Optional[torch.Tensor]:
+        key = self._graph_key(keys, counts, want, extra_arrays)
+        context = self._context(names, keys, counts, tokens, want, extra_arrays, pad_tables=key is not None,
                                 device_places=device_tokens[1] if device_tokens is not None else None)
         self.last_context = context
         if device_tokens is not None and device_tokens[1]:
             ops.place_tokens(context.token_ids, device_tokens[0], context.extra.pop("device_token_pairs"))
         logits = self.model.forward(context, self.cache) if key is None else self._replay(key, context)
-        for entry in entries:
-            self.cache.advance(entry.request, len(entry.tokens))
+        self.cache.advance_keys(keys, counts)
         self.steps_run += 1
         return logits
 
     # ------------------------------------------------------------------ CUDA graphs for decode steps
-    def _graph_key(self, entries: Sequence[StepEntry], extra_arrays):
+    def _graph_key(self, keys: np.ndarray, counts: np.ndarray, want: np.ndarray, extra_arrays):
         """Steps of single decoded tokens whose logits are all wanted repeat with the same shape: their
         launches are captured once per (rows, table width, extra arrays) and replayed, which removes
         the host's launch cost (the reference captures a graph per decode bucket for the same reason:
         helios/crates/helios-hal/src/backends/hopper_sm90/session.rs:510-551)."""
-        if not self.use_graphs or any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+        if not self.use_graphs or len(want) != len(counts) or int(counts.max()) != 1 or not np.array_equal(want, np.arange(len(counts))):
             return None
-        widths = []
-        for group in range(len(self.cache.paged)):
-            blocks = max(-(-(self.cache.length(e.request) + 1) // self.cache.page_size) for e in entries)
-            blocks = max(blocks, max(len(self.cache.table(group, e.request)) for e in entries))
-            widths.append(-(-blocks // GRAPH_TABLE_STEP) * GRAPH_TABLE_STEP)
+        widths = np.zeros(max(1, len(self.cache.paged)), dtype=np.int32)
+        host_runtime.check(host_runtime.library().hb_step_decode_widths(self.cache.native, len(keys), host_runtime.address(keys), GRAPH_TABLE_STEP,
+                                                                        host_runtime.address(widths)))
         extras = tuple((name, len(values)) for name, (values, _) in (extra_arrays or {}).items())
-        return (len(entries), tuple(widths), extras)
+        return (len(keys), tuple(widths[: len(self.cache.paged)].tolist()), extras)
 
     def _replay(self, key, context: StepContext):
         entry = self.graphs.get(key)

@@ -1,4 +1,4 @@
-"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
+"""The scheduler's Python face: admits requests, cuts prompts into portions under a token budget, decodes,
 finishes and frees.
 
 It is a state machine without clock, thread or device, so that the same trace of requests always
@@ -25,21 +25,24 @@ a request has, whether ``max_tokens`` or the context limit ends it).  A row whos
 on the device carries ``PENDING_TOKEN`` and names the plan and sampled row it comes from; the
 engine feeds it from the device.  Only an end-of-sequence token is learnt late: the request then
 has one row too many in flight, whose result is dropped.
+
+The state machine itself is ``hb::Scheduler`` of the host runtime (``csrc/host/scheduler.cpp``); this
+module keeps request names and sampling parameters and turns its arrays into the objects below.
 """
 from __future__ import annotations
 
-from collections import deque
-from dataclasses import dataclass, field
-from typing import Hashable, Optional, Sequence, Union
+import ctypes
+from dataclasses import dataclass
+from typing import Hashable, Optional, Sequence
 
+import numpy as np
+
+from .. import host
+from ..host import QueueFull
 from ..sampling.params import SamplingParams
 
-
 PENDING_TOKEN = -1  # stands in a plan row for a sampled token that has not reached the host yet
-
-
-class QueueFull(RuntimeError):
-    pass
+EVENT_KINDS = ("token", "finished", "failed")
 
 
 @dataclass
@@ -78,6 +81,20 @@ class Plan:
 
 
 @dataclass
+class PlanArrays:
+    """A plan as the runtime hands it out: one entry per row, tokens of all rows back to back."""
+
+    step: int
+    keys: np.ndarray  # int64 runtime keys of the rows' requests
+    counts: np.ndarray
+    sample: np.ndarray
+    sampled_before: np.ndarray
+    from_step: np.ndarray  # -1 unless the row's token is still on the device
+    from_index: np.ndarray
+    tokens: np.ndarray
+
+
+@dataclass
 class Event:
     request: Hashable
     kind: str  # "token" | "finished" | "failed"
@@ -85,178 +102,155 @@ class Event:
     reason: Optional[str] = None  # "stop" | "length" | "cancelled" | message of a failure
 
 
-@dataclass
-class _Sequence:
-    request: Request
-    reserved_pages: int
-    fed: int = 0  # prompt tokens already planned
-    planned_samples: int = 0  # sampled rows planned so far, results in or not
-    generated: list[int] = field(default_factory=list)
-    feed: Union[None, int, tuple[int, int]] = None  # what the next decode row feeds: a token, or where a plan in flight will put it
-
-    @property
-    def prefilling(self) -> bool:
-        return self.fed < len(self.request.prompt)
-
-
 class Scheduler:
     def __init__(self, config: SchedulerConfig):
-        if config.max_batch_tokens < 1 or config.prefill_chunk_busy < 1 or config.max_batch < 1:
-            raise ValueError("max_batch_tokens, prefill_chunk_busy and max_batch must be at least 1")
         self.config = config
-        self.waiting: deque[Request] = deque()
-        self.running: dict[Hashable, _Sequence] = {}  # insertion order = admission order
-        self.events: list[Event] = []
-        self.released: list[Hashable] = []  # requests whose cache the engine must free
-        self._step = 0
-        self._in_flight: deque[Plan] = deque()  # oldest first
+        self._lib = host.library()
+        self._handle = ctypes.c_void_p()
+        eos = host.ints(list(config.eos_token_ids))
+        host.check(self._lib.hb_sched_new(config.num_pages, config.page_size, config.max_seq_len, config.max_batch, config.max_batch_tokens,
+                                          config.prefill_chunk_busy, config.max_queue, config.max_in_flight, len(eos), host.address(eos),
+                                          ctypes.byref(self._handle)))
+        self.keys = host.KeyMap()
+        self.requests: dict[int, Request] = {}  # by runtime key, until the request's last event has been taken
+        self._released: list[Hashable] = []
+
+    def __del__(self):
+        if getattr(self, "_handle", None):
+            self._lib.hb_sched_delete(self._handle)
+            self._handle = None
 
     # ------------------------------------------------------------------ intake
-    def enqueue(self, request: Request) -> None:
-        if len(self.waiting) >= self.config.max_queue:
-            raise QueueFull(f"{len(self.waiting)} requests are waiting")
-        if request.id in self.running or any(r.id == request.id for r in self.waiting):
+    def enqueue(self, request: Request) -> int:
+        """Queue a request; returns the key the runtime knows it by."""
+        if self.keys.known(request.id) is not None:
             raise ValueError(f"request id {request.id!r} is already known")
-        self.waiting.append(request)
+        key = self.keys.key(request.id)
+        prompt = host.ints(list(request.prompt))
+        try:
+            host.check(self._lib.hb_sched_enqueue(self._handle, key, len(prompt), host.address(prompt), request.params.max_tokens,
+                                                  int(request.params.ignore_eos)))
+        except Exception:
+            self.keys.forget(request.id)
+            raise
+        self.requests[key] = request
+        return key
 
-    def _pages(self, tokens: int) -> int:
-        return -(-tokens // self.config.page_size)
-
-    @property
-    def reserved_pages(self) -> int:
-        return sum(s.reserved_pages for s in self.running.values())
-
-    def _admit(self) -> None:
-        c = self.config
-        while self.waiting and len(self.running) < c.max_batch:
-            request = self.waiting[0]
-            prompt = len(request.prompt)
-            if prompt == 0 or prompt >= c.max_seq_len:
-                self.waiting.popleft()
-                self.events.append(Event(request.id, "failed", reason=f"prompt of {prompt} tokens is outside 1..{c.max_seq_len - 1}"))
-                continue
-            need = self._pages(min(prompt + request.params.max_tokens, c.max_seq_len))
-            if need > c.num_pages:
-                self.waiting.popleft()
-                self.events.append(Event(request.id, "failed", reason=f"needs {need} pages, the pool has {c.num_pages}"))
-                continue
-            if self.reserved_pages + need > c.num_pages:
-                return  # waits for running requests to finish; order is kept
-            self.waiting.popleft()
-            self.running[request.id] = _Sequence(request, need)
-
-    # ------------------------------------------------------------------ planning
-    def next_plan(self) -> Optional[Plan]:
-        """The next step, or None when there is nothing to run now (nothing is running or waiting,
-        or every running request has its last row in flight)."""
-        if len(self._in_flight) >= self.config.max_in_flight:
-            raise RuntimeError("the previous plan has not been completed")
-        self._admit()
-        c = self.config
-        rows: list[PlanRow] = []
-        budget = c.max_batch_tokens
-        decoding = [s for s in self.running.values() if s.feed is not None]
-        for s in decoding:
-            if budget == 0:
-                break
-            if isinstance(s.feed, tuple):
-                rows.append(PlanRow(s.request.id, [PENDING_TOKEN], True, s.planned_samples, token_from=s.feed))
-            else:
-                rows.append(PlanRow(s.request.id, [s.feed], True, s.planned_samples))
-            budget -= 1
-        limit = c.prefill_chunk_busy if decoding else c.max_batch_tokens
-        for s in self.running.values():
-            if budget == 0:
-                break
-            if not s.prefilling:
-                continue
-            prompt = s.request.prompt
-            count = min(len(prompt) - s.fed, budget, limit)
-            rows.append(PlanRow(s.request.id, list(prompt[s.fed : s.fed + count]), s.fed + count == len(prompt), 0))
-            s.fed += count
-            budget -= count
-        if not rows:
-            return None
-        sampled = 0
-        for row in rows:  # what each request feeds next is known now, but for the token's value
-            if not row.sample:
-                continue
-            s = self.running[row.request]
-            s.planned_samples += 1
-            more = s.planned_samples < s.request.params.max_tokens and len(s.request.prompt) + s.planned_samples < c.max_seq_len
-            s.feed = (self._step, sampled) if more else None
-            sampled += 1
-        plan = Plan(self._step, rows)
-        self._step += 1
-        self._in_flight.append(plan)
-        return plan
-
-    # ------------------------------------------------------------------ results
-    def complete(self, plan: Plan, sampled: dict[Hashable, int]) -> list[Event]:
-        """The oldest plan in flight ran: ``sampled`` holds the token chosen for every row with ``sample``."""
-        if not self._in_flight or plan is not self._in_flight[0]:
-            raise RuntimeError("complete() must get the oldest plan in flight")
-        self._in_flight.popleft()
-        c = self.config
-        index = -1
-        for row in plan.rows:
-            if not row.sample:
-                continue
-            index += 1
-            s = self.running.get(row.request)
-            if s is None:  # cancelled, or ended by an end-of-sequence token, while this row was in flight
-                continue
-            token = int(sampled[row.request])
-            params = s.request.params
-            if token in c.eos_token_ids and not params.ignore_eos:
-                self._finish(s, "stop")
-                continue
-            s.generated.append(token)
-            self.events.append(Event(row.request, "token", token=token))
-            if len(s.generated) >= params.max_tokens or len(s.request.prompt) + len(s.generated) >= c.max_seq_len:
-                self._finish(s, "length")
-            elif s.feed == (plan.step, index):
-                s.feed = token  # no later plan has taken it from the device
-        return self.take_events()
-
-    def fail(self, plan: Plan, reason: str) -> list[Event]:
-        """The step failed: only the requests it carried fail, and they are released."""
-        if plan not in self._in_flight:
-            raise RuntimeError("fail() must get a plan in flight")
-        self._in_flight.remove(plan)
-        for row in plan.rows:
-            s = self.running.pop(row.request, None)
-            if s is not None:
-                self.released.append(row.request)
-                self.events.append(Event(row.request, "failed", reason=reason))
-        return self.take_events()
-
-    def cancel(self, request: Hashable) -> bool:
-        for index, waiting in enumerate(self.waiting):
-            if waiting.id == request:
-                del self.waiting[index]
-                self.events.append(Event(request, "finished", reason="cancelled"))
-                return True
-        s = self.running.pop(request, None)
-        if s is None:
-            return False
-        self.released.append(request)
-        self.events.append(Event(request, "finished", reason="cancelled"))
-        return True
-
-    def _finish(self, s: _Sequence, reason: str) -> None:
-        del self.running[s.request.id]
-        self.released.append(s.request.id)
-        self.events.append(Event(s.request.id, "finished", reason=reason))
-
-    def take_events(self) -> list[Event]:
-        events, self.events = self.events, []
-        return events
-
-    def take_released(self) -> list[Hashable]:
-        released, self.released = self.released, []
-        return released
+    def _state(self) -> tuple[int, int, int, int, int]:
+        values = [ctypes.c_int() for _ in range(5)]
+        host.check(self._lib.hb_sched_state(self._handle, *[ctypes.byref(v) for v in values]))
+        return tuple(v.value for v in values)
 
     @property
     def idle(self) -> bool:
-        return not self.waiting and not self.running
+        return bool(self._state()[0])
+
+    @property
+    def reserved_pages(self) -> int:
+        return self._state()[3]
+
+    @property
+    def waiting(self) -> list[Request]:
+        count = self._state()[1]
+        keys = np.empty(max(1, count), dtype=np.int64)
+        host.check(self._lib.hb_sched_waiting_keys(self._handle, host.address(keys), len(keys)))
+        return [self.requests[int(k)] for k in keys[:count]]
+
+    # ------------------------------------------------------------------ planning
+    def next_plan_arrays(self) -> Optional[PlanArrays]:
+        """The next step as arrays, or None when there is nothing to run now (nothing is running or
+        waiting, or every running request has its last row in flight)."""
+        step, rows, tokens = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        host.check(self._lib.hb_sched_next_plan(self._handle, ctypes.byref(step), ctypes.byref(rows), ctypes.byref(tokens)))
+        if step.value < 0:
+            return None
+        n = rows.value
+        plan = PlanArrays(step.value, np.empty(n, np.int64), *[np.empty(n, np.int32) for _ in range(5)], np.empty(tokens.value, np.int32))
+        host.check(self._lib.hb_sched_plan(self._handle, plan.step, *[host.address(a) for a in (plan.keys, plan.counts, plan.sample, plan.sampled_before,
+                                                                                              plan.from_step, plan.from_index, plan.tokens)]))
+        return plan
+
+    def next_plan(self) -> Optional[Plan]:
+        arrays = self.next_plan_arrays()
+        if arrays is None:
+            return None
+        rows, at = [], 0
+        for i, key in enumerate(arrays.keys.tolist()):
+            count = int(arrays.counts[i])
+            pending = arrays.from_step[i] >= 0
+            rows.append(PlanRow(self.keys.name(key), arrays.tokens[at : at + count].tolist(), bool(arrays.sample[i]), int(arrays.sampled_before[i]),
+                                (int(arrays.from_step[i]), int(arrays.from_index[i])) if pending else None))
+            at += count
+        return Plan(arrays.step, rows)
+
+    # ------------------------------------------------------------------ results
+    def complete_arrays(self, step: int, sampled: np.ndarray) -> None:
+        """The oldest plan in flight ran: ``sampled`` (int32) holds the token of every sampled row, in row order."""
+        sampled = host.ints(sampled)
+        host.check(self._lib.hb_sched_complete(self._handle, step, len(sampled), host.address(sampled)))
+
+    def complete(self, plan: Plan, sampled: dict[Hashable, int]) -> list[Event]:
+        """The oldest plan in flight ran: ``sampled`` holds the token chosen for every row with ``sample``."""
+        self.complete_arrays(plan.step, np.asarray([int(sampled[row.request]) for row in plan.rows if row.sample], dtype=np.int32))
+        return self.take_events()
+
+    def fail_step(self, step: int, reason: str) -> None:
+        """The step of a plan in flight failed: only the requests it carried fail, and they are released."""
+        host.check(self._lib.hb_sched_fail(self._handle, step, reason.encode("utf-8", "replace")))
+
+    def fail(self, plan, reason: str) -> list[Event]:
+        self.fail_step(plan.step, reason)
+        return self.take_events()
+
+    def cancel(self, request: Hashable) -> bool:
+        key = self.keys.known(request)
+        if key is None:
+            return False
+        found = ctypes.c_int()
+        host.check(self._lib.hb_sched_cancel(self._handle, key, ctypes.byref(found)))
+        return bool(found.value)
+
+    def take_event_arrays(self):
+        """(keys, kinds, tokens, reasons) of the events since the last call; kinds index ``EVENT_KINDS``."""
+        count, size = ctypes.c_int(), ctypes.c_int()
+        host.check(self._lib.hb_sched_take_events(self._handle, 0, None, None, None, None, 0, ctypes.byref(count), ctypes.byref(size)))
+        n = count.value
+        if n == 0:
+            return np.empty(0, np.int64), np.empty(0, np.int32), np.empty(0, np.int32), []
+        keys, kinds, tokens = np.empty(n, np.int64), np.empty(n, np.int32), np.empty(n, np.int32)
+        text = ctypes.create_string_buffer(max(1, size.value))
+        host.check(self._lib.hb_sched_take_events(self._handle, n, host.address(keys), host.address(kinds), host.address(tokens), text, size.value,
+                                                  ctypes.byref(count), ctypes.byref(size)))
+        reasons = text.raw[: size.value].split(b"\0")[:n]
+        return keys, kinds, tokens, [r.decode("utf-8", "replace") for r in reasons]
+
+    def take_events(self) -> list[Event]:
+        self._drain_released()  # while the names of requests that just ended are still known
+        keys, kinds, tokens, reasons = self.take_event_arrays()
+        events = []
+        for key, kind, token, reason in zip(keys.tolist(), kinds.tolist(), tokens.tolist(), reasons):
+            name = self.keys.name(key)
+            if kind == 0:
+                events.append(Event(name, "token", token=token))
+            else:  # the request's last event: its name and parameters are dropped
+                events.append(Event(name, EVENT_KINDS[kind], reason=reason))
+                self.requests.pop(key, None)
+                self.keys.forget(name)
+        return events
+
+    def take_released_keys(self) -> np.ndarray:
+        keys, count = np.empty(self.config.max_batch + 1, dtype=np.int64), ctypes.c_int()
+        host.check(self._lib.hb_sched_take_released(self._handle, len(keys), host.address(keys), ctypes.byref(count)))
+        if count.value > len(keys):  # they stayed queued: again with room
+            keys = np.empty(count.value, dtype=np.int64)
+            host.check(self._lib.hb_sched_take_released(self._handle, len(keys), host.address(keys), ctypes.byref(count)))
+        return keys[: count.value]
+
+    def _drain_released(self) -> None:
+        self._released += [self.keys.name(key) for key in self.take_released_keys().tolist()]
+
+    def take_released(self) -> list[Hashable]:
+        """Requests whose cache the engine must free (finished, failed or cancelled while running)."""
+        self._drain_released()
+        released, self._released = self._released, []
+        return released

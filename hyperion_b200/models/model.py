@@ -113,4 +113,4 @@ class DecoderModel:
         kind, group, _ = cache.where(entry)
         if kind == "paged":
             return PagedView(cache.paged_storage(entry), step.paged_tables[group], cache.page_size, group)
-        return StateView(cache.state_storage(entry), step.slots, [row.slot for row in step.rows])
+        return StateView(cache.state_storage(entry), step.slots, [int(slot) for slot in step.rows.slots])

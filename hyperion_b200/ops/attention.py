@@ -7,8 +7,12 @@ keys split over several blocks when the batch alone would not fill the GPU.
 """
 from __future__ import annotations
 
+import ctypes
+
+import numpy as np
 import torch
 
+from .. import host as host_runtime
 from .basic import status_word
 from .native import KernelError, check, f32, i32, library, ptr, require_cuda, stream_ptr
 
@@ -47,17 +51,17 @@ def tile_tokens(heads: int, kv_heads: int, rows: int = TILE_ROWS) -> int:
     return rows // min(heads // kv_heads, rows)
 
 
-def plan(rows, tokens_per_tile: int) -> tuple[list[int], list[int]]:
-    """(tiles as flat triples [first token, count, batch row], items = flat token indices)."""
-    tiles: list[int] = []
-    items: list[int] = []
-    for index, row in enumerate(rows):
-        if row.count <= TOKEN_SHAPE_MAX:
-            items.extend(range(row.start, row.start + row.count))
-            continue
-        for first in range(0, row.count, tokens_per_tile):
-            tiles.extend((row.start + first, min(tokens_per_tile, row.count - first), index))
-    return tiles, items
+def plan(rows, tokens_per_tile: int) -> tuple[np.ndarray, np.ndarray]:
+    """(tiles as flat triples [first token, count, batch row], items = flat token indices), int32 arrays, made by the
+    host runtime from the rows' token counts (rows follow one another in the flat batch)."""
+    counts = host_runtime.ints(rows.counts if hasattr(rows, "counts") else [row.count for row in rows])
+    tiles = np.empty(3 * int((-(-counts // tokens_per_tile)).sum()), dtype=np.int32)
+    items = np.empty(int(counts.sum()), dtype=np.int32)
+    n_tiles, n_items = ctypes.c_int(), ctypes.c_int()
+    host_runtime.check(host_runtime.library().hb_plan_attention(len(counts), host_runtime.address(counts), tokens_per_tile, TOKEN_SHAPE_MAX,
+                                                                host_runtime.address(tiles), ctypes.byref(n_tiles), host_runtime.address(items),
+                                                                ctypes.byref(n_items)))
+    return tiles[: 3 * n_tiles.value], items[: n_items.value]
 
 
 def choose_splits(n_items: int, heads: int, kv_heads: int, longest_context: int) -> int:

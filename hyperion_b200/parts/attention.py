@@ -122,12 +122,20 @@ class GroupedQueryAttention(Mixer):
             tiles, items = fast_attention.plan(rows, tokens_per_tile)
             host[key] = len(tiles) // 3
             host["attn_items"] = len(items)
-            if tiles:
+            if len(tiles):
                 packer.add(key, tiles)
-            if items and "attn_items" not in [name for name, *_ in packer._items]:
+            if len(items) and "attn_items" not in [name for name, *_ in packer._items]:
                 packer.add("attn_items", items)
 
         return {("attention_plan", heads // kv_heads, head_dim): plan}
+
+    @staticmethod
+    def _longest_short_row(rows) -> int:
+        """The largest context among the rows that go token by token."""
+        if hasattr(rows, "counts"):
+            short = rows.counts <= fast_attention.TOKEN_SHAPE_MAX
+            return int((rows.positions[short] + rows.counts[short]).max())
+        return max(row.position + row.count for row in rows if row.count <= fast_attention.TOKEN_SHAPE_MAX)
 
     def _attend_fast(self, qkv, step, cache):
         out = torch.empty((step.n_tokens, self.q_width), dtype=self.dtype, device=qkv.device)
@@ -139,8 +147,7 @@ class GroupedQueryAttention(Mixer):
                                            step.extra[key], n_tiles, self.scale, self.window, out, tile_size=size)
         if n_items:
             # a step replayed from a CUDA graph fixes its launch shape for every context its tables can hold
-            longest = step.host.get("context_cap") or max(row.position + row.count for row in step.rows
-                                                          if row.count <= fast_attention.TOKEN_SHAPE_MAX)
+            longest = step.host.get("context_cap") or self._longest_short_row(step.rows)
             if self.window:
                 longest = min(longest, self.window + fast_attention.KEY_TILE)
             splits = fast_attention.choose_splits(n_items, self.heads, self.kv_heads, longest)

@@ -107,7 +107,7 @@ def test_window_group_gives_pages_back_while_the_request_lives():
     # length 20: the next query (position 20) reads keys 15..20, so blocks 0..2 (positions 0..11) are gone
     assert m.table(windowed, "a")[:3] == [NO_PAGE] * 3 and all(p != NO_PAGE for p in m.table(windowed, "a")[3:])
     assert all(p != NO_PAGE for p in m.table(full, "a")) and len(m.table(full, "a")) == 5
-    assert m.paged[windowed].pool.available == 6 - 2
+    assert m.free_pages(windowed) == 6 - 2
     # a long portion needs pages for all its positions during the step and gives most back after it
     m.add_request("b")
     with pytest.raises(OutOfPages):
@@ -115,7 +115,7 @@ def test_window_group_gives_pages_back_while_the_request_lives():
     m.free("a")
     m.extend("b", 17)
     m.advance("b", 17)
-    assert m.paged[windowed].pool.available == 6 - 2
+    assert m.free_pages(windowed) == 6 - 2
     m.check()
 
 
@@ -149,7 +149,7 @@ def test_random_orders_never_lose_or_share_a_page():
     for name in list(live):
         m.free(name)
     m.check()
-    assert all(g.pool.available == 24 for g in m.paged)
+    assert all(m.free_pages(g) == 24 for g in range(len(m.paged)))
 
 
 # ---------------------------------------------------------------------------------- scheduler
@@ -382,3 +382,90 @@ def test_a_known_token_is_fed_from_the_host_even_with_room_to_run_ahead():
     first = s.next_plan()
     s.complete(first, {"a": 9})
     assert s.next_plan().rows[0].tokens == [9]
+
+
+# ---------------------------------------------------------------------- step assembly by the host runtime
+def test_step_assembly_writes_every_array_where_its_layout_says():
+    import numpy as np
+    import torch
+
+    from hyperion_b200.engine.batch import MetadataPacker
+
+    users = [(0, PagedKV(2, 16, 0)), (1, PagedKV(2, 16, 10))]
+    m = CacheManager(users, page_size=4, num_pages=32, max_requests=4)
+    for name, tokens in (("a", 9), ("b", 3), ("c", 17)):
+        m.add_request(name)
+        m.extend(name, tokens)
+        m.advance(name, tokens)
+    work = [("c", 2), ("a", 1), ("b", 6)]  # c and a decode or continue, b brings a portion
+    m.extend_all(work)
+    keys = np.asarray([m.keys.known(name) for name, _ in work], dtype=np.int64)
+    counts = np.asarray([n for _, n in work], dtype=np.int32)
+    tokens = np.arange(100, 109, dtype=np.int32)
+    want = np.asarray([1, 2, 8], dtype=np.int32)
+    packer = MetadataPacker(torch.device("cpu"), capacity=64)  # too small on purpose: it grows and keeps what was written
+    packer.begin()
+    packer.add("before", [7, 7, 7])
+    packer.add_step(m, keys, counts, tokens, want, table_step=0)
+    packer.add("after", [5])
+    arrays = {name: value.clone() for name, value in packer.finish().items()}
+    assert arrays["before"].tolist() == [7, 7, 7] and arrays["after"].tolist() == [5]
+    assert arrays["token_ids"].tolist() == tokens.tolist()
+    assert arrays["positions"].tolist() == [17, 18, 9, 3, 4, 5, 6, 7, 8]
+    assert arrays["token_row"].tolist() == [0, 0, 1, 2, 2, 2, 2, 2, 2]
+    assert arrays["row_start"].tolist() == [0, 2, 3, 9]
+    assert arrays["slots"].tolist() == [m.slot("c"), m.slot("a"), m.slot("b")]
+    assert arrays["want"].tolist() == [1, 2, 8]
+    for group in (0, 1):
+        tables = [m.table(group, name) for name, _ in work]
+        width = max(len(t) for t in tables)
+        assert arrays[f"table{group}"].tolist() == [t + [NO_PAGE] * (width - len(t)) for t in tables]
+    assert NO_PAGE in m.table(1, "c")  # the window of group 1 has passed c's first pages: they read as missing in the step too
+    assert all(start % 4 == 0 for _, start, _, _ in packer._items)
+    # widths of a graphed decode step are padded to whole steps
+    packer.begin()
+    packer.add_step(m, keys, np.ones(3, np.int32), tokens[:3], np.arange(3, dtype=np.int32), table_step=8)
+    assert packer.finish()["table0"].shape == (3, 8)
+
+
+def test_step_assembly_refuses_what_it_cannot_place():
+    import numpy as np
+    import torch
+
+    from hyperion_b200.engine.batch import MetadataPacker
+
+    m = manager()
+    m.add_request("a")
+    m.extend("a", 2)
+    packer = MetadataPacker(torch.device("cpu"), capacity=64)
+    packer.begin()
+    keys, one = np.asarray([m.keys.known("a")], np.int64), np.ones(1, np.int32)
+    with pytest.raises(ValueError):
+        packer.add_step(m, keys, one, one, np.asarray([3], np.int32), 0)  # a wanted place beyond the tokens
+    with pytest.raises(CacheError):
+        packer.add_step(m, np.asarray([12345], np.int64), one, one, np.empty(0, np.int32), 0)  # a request the cache does not know
+
+
+def test_attention_plan_cuts_long_rows_into_tiles_and_leaves_short_rows_as_items():
+    from hyperion_b200.engine.batch import Row
+    from hyperion_b200.ops import attention
+
+    rows, start = [], 0
+    for count in (1, 40, 4, 5, 16):
+        rows.append(Row("r", start, count, 0, 0))
+        start += count
+    tiles, items = attention.plan(rows, 16)
+    assert items.tolist() == [0, 41, 42, 43, 44]
+    assert tiles.reshape(-1, 3).tolist() == [[1, 16, 1], [17, 16, 1], [33, 8, 1], [45, 5, 3], [50, 16, 4]]
+
+
+def test_released_requests_are_not_lost_when_many_end_at_once():
+    s = Scheduler(SchedulerConfig(num_pages=1000, page_size=4, max_seq_len=64, max_batch=2, max_batch_tokens=64))
+    for i in range(7):
+        s.enqueue(Request(i, [1, 2], params(1)))
+    import numpy as np
+
+    while (plan := s.next_plan_arrays()) is not None:  # nobody takes events or released requests meanwhile: more pile up than run at a time
+        s.complete_arrays(plan.step, np.full(int(plan.sample.sum()), 5, np.int32))
+    assert sorted(s.take_released()) == list(range(7)) and s.take_released() == []
+    assert [e.kind for e in s.take_events()].count("finished") == 7

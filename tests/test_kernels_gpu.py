@@ -228,7 +228,7 @@ def run_fast_attention(q, heads, cache, table, rows, scale, window):
     for i, (request, first, count) in enumerate(rows):
         step_rows.append(Row(request, start, count, first, i))
         start += count
-    tiles, items = fast.plan(step_rows, fast.tile_tokens(heads, kv_heads))
+    tiles, items = (a.tolist() for a in fast.plan(step_rows, fast.tile_tokens(heads, kv_heads)))
     token_row = torch.tensor([i for i, r in enumerate(rows) for _ in range(r[2])], dtype=torch.int32, device=DEV)
     positions = torch.tensor([p for r in rows for p in range(r[1], r[1] + r[2])], dtype=torch.int32, device=DEV)
     batch_table = table[[r[0] for r in rows]].contiguous().to(DEV)
@@ -240,7 +240,7 @@ def run_fast_attention(q, heads, cache, table, rows, scale, window):
     outs = {}
     page_size, head_dim = cache.shape[3], cache.shape[4]
     if tiles and fast.uses_tcgen05(head_dim, page_size):  # the same rows again through the tcgen05 kernel (128-row tiles)
-        tiles128, _ = fast.plan(step_rows, fast.tile_tokens(heads, kv_heads, 128))
+        tiles128 = fast.plan(step_rows, fast.tile_tokens(heads, kv_heads, 128))[0].tolist()
         o = out.clone()
         fast.attention_tiles(qd, heads, cd, batch_table, token_row, positions, torch.tensor(tiles128, dtype=torch.int32, device=DEV),
                              len(tiles128) // 3, scale, window, o, tile_size=128)

@@ -256,7 +256,7 @@ def test_layers_of_different_kinds_twice_run_and_shared_cache(mixed_folder, dtyp
         cache.check()
     engine.check()
     # the windowed group held far fewer pages than the full one at the end of a long request
-    assert cache.paged[1].pool.available == cache.paged[1].pool.num_pages
+    assert cache.free_pages(1) == cache.num_pages
 
 
 # ------------------------------------------------------------------------------------------------
