@@ -142,10 +142,77 @@ __global__ void add_rmsnorm_cached_kernel(float* __restrict__ h, const TD* __res
     }
 }
 
+// The serving path's shape of it (bfloat16 delta and output, rows of a multiple of 8 values): 8 values per thread and
+// group with 16- and 32-byte accesses, each row read once. G groups per thread cover rows of up to 8 * G * 1024 values.
+template <int G>
+__global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ delta, const float* __restrict__ weight,
+                                          __nv_bfloat16* __restrict__ out, const int* __restrict__ rows, int hidden, float eps, int write_h) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* hrow = h + (size_t)s * hidden;
+    const __nv_bfloat16* drow = delta + (size_t)s * hidden;
+    float v[G][8], w[G][8];
+    let_next_kernel_start();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {  // the norm's weight is nobody's output: it is fetched while the kernel before still runs
+        const int i = (threadIdx.x + g * blockDim.x) * 8;
+        if (i < hidden) {
+            const float4 a = *reinterpret_cast<const float4*>(weight + i), b = *reinterpret_cast<const float4*>(weight + i + 4);
+            w[g][0] = a.x; w[g][1] = a.y; w[g][2] = a.z; w[g][3] = a.w; w[g][4] = b.x; w[g][5] = b.y; w[g][6] = b.z; w[g][7] = b.w;
+        }
+    }
+    wait_for_previous_kernels();
+    float sum = 0.f;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const int i = (threadIdx.x + g * blockDim.x) * 8;
+        if (i < hidden) {
+            const float4 a = *reinterpret_cast<const float4*>(hrow + i), b = *reinterpret_cast<const float4*>(hrow + i + 4);
+            const uint4 d4 = *reinterpret_cast<const uint4*>(drow + i);
+            const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d4);
+            const float2 d0 = __bfloat1622float2(d2[0]), d1 = __bfloat1622float2(d2[1]), d2f = __bfloat1622float2(d2[2]), d3 = __bfloat1622float2(d2[3]);
+            v[g][0] = a.x + d0.x; v[g][1] = a.y + d0.y; v[g][2] = a.z + d1.x; v[g][3] = a.w + d1.y;
+            v[g][4] = b.x + d2f.x; v[g][5] = b.y + d2f.y; v[g][6] = b.z + d3.x; v[g][7] = b.w + d3.y;
+            if (write_h) {
+                *reinterpret_cast<float4*>(hrow + i) = make_float4(v[g][0], v[g][1], v[g][2], v[g][3]);
+                *reinterpret_cast<float4*>(hrow + i + 4) = make_float4(v[g][4], v[g][5], v[g][6], v[g][7]);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sum = fmaf(v[g][e], v[g][e], sum);
+        }
+    }
+    const float total = block_sum(sum, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    __nv_bfloat16* orow = out + (size_t)r * hidden;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const int i = (threadIdx.x + g * blockDim.x) * 8;
+        if (i < hidden) {
+            uint4 o4;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(v[g][2 * e] * inv * w[g][2 * e], v[g][2 * e + 1] * inv * w[g][2 * e + 1]);
+            *reinterpret_cast<uint4*>(orow + i) = o4;
+        }
+    }
+}
+
 HB_EXPORT int hb_add_rmsnorm(float* h, const void* delta, int delta_is_bf16, const float* weight, void* out,
                              int out_is_bf16, const int* rows, int n_rows, int hidden, float eps, int write_h,
                              cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (delta && delta_is_bf16 && out_is_bf16 && hidden % 8 == 0 && hidden <= 16384 &&
+        (((uintptr_t)h | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0) {
+        const int groups = hidden / 8;
+        const int per_thread = groups > 1024 ? 2 : 1;
+        const int width = ((groups + per_thread - 1) / per_thread + 31) / 32 * 32;
+        if (per_thread == 1)
+            return launch_after_previous(add_rmsnorm_bf16x8_kernel<1>, n_rows, width, 0, stream, h, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows,
+                                         hidden, eps, write_h);
+        return launch_after_previous(add_rmsnorm_bf16x8_kernel<2>, n_rows, width, 0, stream, h, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows,
+                                     hidden, eps, write_h);
+    }
     const int threads = hidden >= 4096 ? 1024 : (hidden >= 1024 ? 512 : 256);
     int status = 0;
     const bool cached = hidden <= 8 * threads;  // both kernels add a thread's squares in the same order, so they agree bit for bit

@@ -42,7 +42,7 @@ def test_embedding_flags_a_bad_token_instead_of_faulting():
     raise_on_status(table.device)  # cleared
 
 
-@pytest.mark.parametrize("hidden, eps", [(72, 1e-6), (1000, 1e-5), (4104, 1e-6)])
+@pytest.mark.parametrize("hidden, eps", [(72, 1e-6), (1000, 1e-5), (4104, 1e-6), (1004, 1e-6), (9000, 1e-5), (3584, 1e-6)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(hidden, eps, out_dtype):
     h = rnd(7, hidden, seed=2, scale=3.0)
