@@ -144,9 +144,20 @@ __global__ void add_rmsnorm_cached_kernel(float* __restrict__ h, const TD* __res
 
 // The serving path's shape of it (bfloat16 delta and output, rows of a multiple of 8 values): 8 values per thread and
 // group with 16- and 32-byte accesses, each row read once. G groups per thread cover rows of up to 8 * G * 1024 values.
+// With `partials` ([splits, tokens, hidden] floats: the split-K sums of the product that made the delta) the delta is
+// their sum in split order plus the bias, rounded to bfloat16 as the product's own reduction would store it.
+struct SplitDelta {
+    const float* partials;
+    size_t split_stride;  // tokens * hidden
+    int splits;
+    const float* bias_f;
+    const __nv_bfloat16* bias_h;
+};
+
 template <int G>
-__global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ delta, const float* __restrict__ weight,
-                                          __nv_bfloat16* __restrict__ out, const int* __restrict__ rows, int hidden, float eps, int write_h) {
+__global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ delta, const SplitDelta split,
+                                          const float* __restrict__ weight, __nv_bfloat16* __restrict__ out, const int* __restrict__ rows,
+                                          int hidden, float eps, int write_h) {
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
@@ -169,7 +180,26 @@ __global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ h, const __nv_bflo
         const int i = (threadIdx.x + g * blockDim.x) * 8;
         if (i < hidden) {
             const float4 a = *reinterpret_cast<const float4*>(hrow + i), b = *reinterpret_cast<const float4*>(hrow + i + 4);
-            const uint4 d4 = *reinterpret_cast<const uint4*>(drow + i);
+            uint4 d4;
+            if (split.partials) {
+                float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                const float* first = split.partials + (size_t)s * hidden + i;
+#pragma unroll 4
+                for (int k = 0; k < split.splits; ++k) {
+                    const float4 p0 = *reinterpret_cast<const float4*>(first + k * split.split_stride);
+                    const float4 p1 = *reinterpret_cast<const float4*>(first + k * split.split_stride + 4);
+                    d[0] += p0.x; d[1] += p0.y; d[2] += p0.z; d[3] += p0.w; d[4] += p1.x; d[5] += p1.y; d[6] += p1.z; d[7] += p1.w;
+                }
+                __nv_bfloat162* packed = reinterpret_cast<__nv_bfloat162*>(&d4);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float b0 = split.bias_f ? split.bias_f[i + 2 * e] : (split.bias_h ? __bfloat162float(split.bias_h[i + 2 * e]) : 0.f);
+                    const float b1 = split.bias_f ? split.bias_f[i + 2 * e + 1] : (split.bias_h ? __bfloat162float(split.bias_h[i + 2 * e + 1]) : 0.f);
+                    packed[e] = __floats2bfloat162_rn(d[2 * e] + b0, d[2 * e + 1] + b1);
+                }
+            } else {
+                d4 = *reinterpret_cast<const uint4*>(drow + i);
+            }
             const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d4);
             const float2 d0 = __bfloat1622float2(d2[0]), d1 = __bfloat1622float2(d2[1]), d2f = __bfloat1622float2(d2[2]), d3 = __bfloat1622float2(d2[3]);
             v[g][0] = a.x + d0.x; v[g][1] = a.y + d0.y; v[g][2] = a.z + d1.x; v[g][3] = a.w + d1.y;
@@ -198,21 +228,39 @@ __global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ h, const __nv_bflo
     }
 }
 
+static bool bf16x8_norm_takes(const void* h, const void* delta, const void* weight, const void* out, int hidden) {
+    return hidden % 8 == 0 && hidden <= 16384 && (((uintptr_t)h | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
+}
+
+static int launch_bf16x8_norm(float* h, const __nv_bfloat16* delta, const SplitDelta& split, const float* weight, __nv_bfloat16* out, const int* rows,
+                              int n_rows, int hidden, float eps, int write_h, cudaStream_t stream) {
+    const int groups = hidden / 8;
+    const int per_thread = groups > 1024 ? 2 : 1;
+    const int width = ((groups + per_thread - 1) / per_thread + 31) / 32 * 32;
+    if (per_thread == 1)
+        return launch_after_previous(add_rmsnorm_bf16x8_kernel<1>, n_rows, width, 0, stream, h, delta, split, weight, out, rows, hidden, eps, write_h);
+    return launch_after_previous(add_rmsnorm_bf16x8_kernel<2>, n_rows, width, 0, stream, h, delta, split, weight, out, rows, hidden, eps, write_h);
+}
+
+// The same with the delta still in pieces: partials [splits, tokens, hidden] floats (+ a bias) are added up in split order
+// and rounded to bfloat16 before they join the residual stream. Refuses (HB_UNSUPPORTED_SIZE) what the 8-wide kernel cannot take.
+HB_EXPORT int hb_add_rmsnorm_splits(float* h, const float* partials, int splits, int tokens, const float* bias_f, const void* bias_h,
+                                    const float* weight, void* out, const int* rows, int n_rows, int hidden, float eps, int write_h,
+                                    cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (!partials || splits < 1 || tokens < 1) return HB_BAD_ARGUMENT;
+    if (!bf16x8_norm_takes(h, partials, weight, out, hidden)) return HB_UNSUPPORTED_SIZE;
+    const SplitDelta split{partials, (size_t)tokens * hidden, splits, bias_f, (const __nv_bfloat16*)bias_h};
+    return launch_bf16x8_norm(h, nullptr, split, weight, (__nv_bfloat16*)out, rows, n_rows, hidden, eps, write_h, stream);
+}
+
 HB_EXPORT int hb_add_rmsnorm(float* h, const void* delta, int delta_is_bf16, const float* weight, void* out,
                              int out_is_bf16, const int* rows, int n_rows, int hidden, float eps, int write_h,
                              cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (delta && delta_is_bf16 && out_is_bf16 && hidden % 8 == 0 && hidden <= 16384 &&
-        (((uintptr_t)h | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0) {
-        const int groups = hidden / 8;
-        const int per_thread = groups > 1024 ? 2 : 1;
-        const int width = ((groups + per_thread - 1) / per_thread + 31) / 32 * 32;
-        if (per_thread == 1)
-            return launch_after_previous(add_rmsnorm_bf16x8_kernel<1>, n_rows, width, 0, stream, h, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows,
-                                         hidden, eps, write_h);
-        return launch_after_previous(add_rmsnorm_bf16x8_kernel<2>, n_rows, width, 0, stream, h, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows,
-                                     hidden, eps, write_h);
-    }
+    if (delta && delta_is_bf16 && out_is_bf16 && bf16x8_norm_takes(h, delta, weight, out, hidden))
+        return launch_bf16x8_norm(h, (const __nv_bfloat16*)delta, SplitDelta{nullptr, 0, 0, nullptr, nullptr}, weight, (__nv_bfloat16*)out, rows, n_rows,
+                                  hidden, eps, write_h, stream);
     const int threads = hidden >= 4096 ? 1024 : (hidden >= 1024 ? 512 : 256);
     int status = 0;
     const bool cached = hidden <= 8 * threads;  // both kernels add a thread's squares in the same order, so they agree bit for bit

@@ -370,10 +370,10 @@ HB_EXPORT long long hb_gemm_bf16_workspace(int m, int n, int splits) { return sp
 //   are 128 gate rows followed by their 128 up rows (n a multiple of 256).
 //   batch_tile 0: the activations supply the 128-row side (m large).  batch_tile 16 / 32 / 64: the weights supply it
 //   and up to batch_tile rows of a form the other side (m <= batch_tile); then `splits` may divide k, with a float
-//   workspace of hb_gemm_bf16_workspace(m, n, splits) elements.
+//   workspace of hb_gemm_bf16_workspace(m, n, splits) elements; with leave_partials the sums stay there, [splits, m, n].
 HB_EXPORT int hb_gemm_bf16(const void* a, int lda, const void* w, int ldw, void* c, int ldc, const float* bias_f, const void* bias_h,
-                           int m, int n, int k, int epilogue, int batch_tile, int splits, float* workspace, int* status,
-                           cudaStream_t stream) {
+                           int m, int n, int k, int epilogue, int batch_tile, int splits, float* workspace, int leave_partials,
+                           int* status, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (k <= 0 || splits < 1) return HB_BAD_ARGUMENT;
     GemmParams p{c, bias_f, (const bf16*)bias_h, workspace, m, n, k, ldc, 0, status};
@@ -403,8 +403,19 @@ HB_EXPORT int hb_gemm_bf16(const void* a, int lda, const void* w, int ldw, void*
     int code = batch_tile == 16 ? launch_swap<16>(epi, map_w, map_x, p, grid, stream)
              : batch_tile == 32 ? launch_swap<32>(epi, map_w, map_x, p, grid, stream)
                                 : launch_swap<64>(epi, map_w, map_x, p, grid, stream);
-    if (code || splits == 1) return code;
+    if (code || splits == 1 || leave_partials) return code;  // the caller adds the partial sums up itself (hb_splitk_reduce, or a kernel that reads them)
     const size_t total = (size_t)m * n;
     return launch_after_previous(splitk_reduce_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, (const float*)workspace, splits, m, n, c, ldc,
                                  (int)(epilogue == EPI_F32), bias_f, (const bf16*)bias_h);
+}
+
+// Adds up split-K partials [splits, m, n] in split order, adds the bias and stores bfloat16 or float: the second half of
+// hb_gemm_bf16 with splits > 1, for callers that asked it to leave the partials.
+HB_EXPORT int hb_splitk_reduce(const float* workspace, int splits, int m, int n, void* c, int ldc, int out_is_f32, const float* bias_f,
+                               const void* bias_h, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (splits < 1 || !workspace) return HB_BAD_ARGUMENT;
+    const size_t total = (size_t)m * n;
+    return launch_after_previous(splitk_reduce_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, workspace, splits, m, n, c, ldc, out_is_f32, bias_f,
+                                 (const bf16*)bias_h);
 }

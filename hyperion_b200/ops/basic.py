@@ -56,25 +56,42 @@ def prefetch_l2(tensor: torch.Tensor, first_bytes: int | None = None) -> None:
     check(library("elementwise").hb_prefetch_l2(ptr(tensor), ctypes.c_size_t(count), stream_ptr()), "prefetch_l2")
 
 
-def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
                 rows: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """RMSNorm of ``h (+ delta)`` times ``weight``.
 
     Without ``rows`` the sum is written back into ``h`` (float residual stream) and every row is
     normalised; with ``rows`` (int32 indices) only those rows are read and ``h`` is left alone.
+    ``delta`` is a tensor, None, or a ``SplitSum`` (a product whose split-K pieces this kernel adds up itself).
     """
+    from .gemm import SplitSum
+
+    pieces = delta if isinstance(delta, SplitSum) else None
+    hidden = h.shape[-1]
+    if pieces is not None:
+        fits = (out_dtype == torch.bfloat16 and pieces.dtype == torch.bfloat16 and hidden % 8 == 0 and hidden <= 16384
+                and pieces.shape == tuple(h.shape) and pieces.partials.is_contiguous())
+        delta = None if fits else pieces.tensor()
+        pieces = pieces if fits else None
     require_cuda(h, delta, weight, rows)
     if h.dtype != torch.float32 or weight.dtype != torch.float32 or not h.is_contiguous():
         raise KernelError("add_rmsnorm: the residual stream and the norm weight are float32")
-    hidden = h.shape[-1]
     n_rows = rows.numel() if rows is not None else h.shape[0]
     if out is None:
         out = torch.empty((n_rows, hidden), dtype=out_dtype, device=h.device)
     if delta is not None and (delta.shape != h.shape or not delta.is_contiguous()):
         raise KernelError("add_rmsnorm: delta must have the shape of h")
     lib = library("elementwise")
+    write_h = i32(0 if rows is not None else 1)
+    if pieces is not None:
+        bias = pieces.bias
+        bias_f = bias if bias is not None and bias.dtype == torch.float32 else None
+        bias_h = bias if bias is not None and bias.dtype == torch.bfloat16 else None
+        check(lib.hb_add_rmsnorm_splits(ptr(h), ptr(pieces.partials), i32(pieces.partials.shape[0]), i32(h.shape[0]), ptr(bias_f), ptr(bias_h),
+                                        ptr(weight), ptr(out), ptr(rows), i32(n_rows), i32(hidden), f32(eps), write_h, stream_ptr()), "add_rmsnorm")
+        return out
     check(lib.hb_add_rmsnorm(ptr(h), ptr(delta), i32(is_bf16(delta) if delta is not None else 0), ptr(weight), ptr(out),
-                             i32(is_bf16(out)), ptr(rows), i32(n_rows), i32(hidden), f32(eps), i32(0 if rows is not None else 1),
+                             i32(is_bf16(out)), ptr(rows), i32(n_rows), i32(hidden), f32(eps), write_h,
                              stream_ptr()), "add_rmsnorm")
     return out
 

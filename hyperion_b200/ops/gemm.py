@@ -8,6 +8,7 @@ and SwiGLU over a block-interleaved gate/up matrix (see ``interleave_gate_up``).
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -48,8 +49,33 @@ def choose_splits(n: int, k: int) -> int:
     return max(1, min(SMS // tiles if tiles < SMS else 1, k_blocks // 4, 16))
 
 
+@dataclass
+class SplitSum:
+    """A product whose split-K partial sums have not been added up yet: ``partials`` [splits, M, N] float32, to be
+    summed in split order, plus ``bias``, rounded to ``dtype``.  A consumer that can read the pieces itself (the fused
+    residual add + norm) saves the kernel that would add them; everyone else calls :meth:`tensor`."""
+
+    partials: torch.Tensor
+    bias: Optional[torch.Tensor]
+    dtype: torch.dtype
+
+    @property
+    def shape(self) -> tuple[int, int]:
+        return tuple(self.partials.shape[1:])
+
+    def tensor(self) -> torch.Tensor:
+        splits, m, n = self.partials.shape
+        out = torch.empty((m, n), dtype=self.dtype, device=self.partials.device)
+        bias_f = self.bias if self.bias is not None and self.bias.dtype == torch.float32 else None
+        bias_h = self.bias if self.bias is not None and self.bias.dtype == torch.bfloat16 else None
+        check(library("gemm_tcgen05").hb_splitk_reduce(ptr(self.partials), i32(splits), i32(m), i32(n), ptr(out), i32(out.stride(0)),
+                                                       i32(self.dtype == torch.float32), ptr(bias_f), ptr(bias_h), stream_ptr()), "splitk_reduce")
+        return out
+
+
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, epilogue: int = EPI_BF16,
-              out: Optional[torch.Tensor] = None, splits: Optional[int] = None) -> torch.Tensor:
+              out: Optional[torch.Tensor] = None, splits: Optional[int] = None, leave_partials: bool = False):
+    """``leave_partials``: when K is split, return a :class:`SplitSum` instead of adding the pieces up."""
     require_cuda(x, w, bias)
     if not supported(x, w):
         raise KernelError("gemm_bf16: operands must be bfloat16, K-contiguous, with 16-byte aligned rows")
@@ -75,8 +101,11 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
         splits = choose_splits(n, k) if splits is None else splits
         if splits > 1:
             workspace = torch.empty(splits * m * n, dtype=torch.float32, device=x.device)
+    leave = int(leave_partials and workspace is not None and epilogue in (EPI_BF16, EPI_F32))
     lib = library("gemm_tcgen05")
     check(lib.hb_gemm_bf16(ptr(x), i32(x.stride(0)), ptr(w), i32(w.stride(0)), ptr(out), i32(out.stride(0)), ptr(bias_f), ptr(bias_h),
-                           i32(m), i32(n), i32(k), i32(epilogue), i32(tile), i32(splits), ptr(workspace), ptr(status_word(x.device)),
+                           i32(m), i32(n), i32(k), i32(epilogue), i32(tile), i32(splits), ptr(workspace), i32(leave), ptr(status_word(x.device)),
                            stream_ptr()), "gemm_bf16")
+    if leave:
+        return SplitSum(workspace.view(splits, m, n), bias, out_dtype)
     return out

@@ -46,7 +46,9 @@ def _takes_own_kernel(x: torch.Tensor, weight: torch.Tensor, bias, out_dtype) ->
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, may_leave_partials: bool = False):
+    """``may_leave_partials``: the caller's result is only ever a residual delta, so a product that was split over K may
+    come back as a :class:`hyperion_b200.ops.gemm.SplitSum` (the norm that adds the delta reads the pieces itself)."""
     require_cuda(x, weight, bias)
     out_dtype = out_dtype or x.dtype
     if weight.dtype == torch.float32:
@@ -58,7 +60,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         raise KernelError(f"linear: weights are float32 or bfloat16, got {weight.dtype}")
     xin = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
     if _takes_own_kernel(xin, weight, bias, out_dtype):
-        return gemm.gemm_bf16(xin, weight, bias, gemm.EPI_F32 if out_dtype == torch.float32 else gemm.EPI_BF16)
+        return gemm.gemm_bf16(xin, weight, bias, gemm.EPI_F32 if out_dtype == torch.float32 else gemm.EPI_BF16,
+                              leave_partials=may_leave_partials and out_dtype == torch.bfloat16)
     if not xin.is_contiguous():
         xin = xin.contiguous()
     if out_dtype == torch.bfloat16:

@@ -104,7 +104,7 @@ class GroupedQueryAttention(Mixer):
             attn = self._attend_fast(qkv, step, cache)
         else:
             attn = ops.attention_generic(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions, self.scale, self.window)
-        return ops.linear(attn, self.w_o, None, self.dtype)
+        return ops.linear(attn, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
 
     # ------------------------------------------------------------------ the tensor-core path
     def step_plans(self):

@@ -80,7 +80,9 @@ class Part:
 class Norm(Part):
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Add ``delta`` into the float residual stream ``h`` (in place, unless ``rows`` selects rows
-        to gather) and return the normalised rows in the activation type."""
+        to gather) and return the normalised rows in the activation type.  ``delta`` is what a mixer
+        or feed-forward returned: a tensor, or a product still in its split-K pieces
+        (``ops.gemm.SplitSum``; ``.tensor()`` adds them up for a norm that cannot read them itself)."""
         raise NotImplementedError
 
 

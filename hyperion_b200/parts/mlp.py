@@ -41,7 +41,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, step):
         gate_up = ops.linear(x, self.w_gate_up, None, self.dtype)
-        return ops.linear(ops.swiglu(gate_up), self.w_down, None, self.dtype)
+        return ops.linear(ops.swiglu(gate_up), self.w_down, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
 
 
 register_feed_forward("swiglu", SwiGLU)

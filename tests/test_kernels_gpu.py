@@ -414,3 +414,22 @@ def test_attention_at_the_edges_of_window_page_and_tile(kind):
             assert (got - want).abs().max() <= (1e-5 if kind == "float32" else 2 ** -7) * want.abs().max(), (spot, visible)
             distance = (got[-1, 0] - values[0][spot, 0].double()).abs().max()
             assert (distance < 0.05) == visible, (spot, visible, float(distance))
+
+
+@pytest.mark.parametrize("tokens, hidden, splits, with_rows", [(8, 3584, 5, False), (3, 72, 2, False), (33, 9000, 3, True), (64, 1000, 7, True)])
+def test_norm_that_adds_up_split_sums_itself_gives_the_bits_of_the_two_kernel_path(tokens, hidden, splits, with_rows):
+    """The delta arrives as split-K pieces: adding them up inside the norm kernel equals adding them up first."""
+    from hyperion_b200.ops.gemm import SplitSum
+
+    partials = rnd(splits, tokens, hidden, seed=40).to(DEV)
+    bias = rnd(hidden, seed=41).to(torch.bfloat16).to(DEV)
+    w = (1 + rnd(hidden, seed=42, scale=0.1)).to(DEV)
+    rows = torch.tensor([tokens - 1, 0], dtype=torch.int32, device=DEV) if with_rows else None
+    for b in (bias, bias.float(), None):
+        h1, h2 = rnd(tokens, hidden, seed=43, scale=3.0).to(DEV), rnd(tokens, hidden, seed=43, scale=3.0).to(DEV)
+        pieces = SplitSum(partials, b, torch.bfloat16)
+        fused = ops().add_rmsnorm(h1, pieces, w, 1e-6, torch.bfloat16, rows)
+        plain_way = ops().add_rmsnorm(h2, pieces.tensor(), w, 1e-6, torch.bfloat16, rows)
+        assert torch.equal(fused, plain_way) and torch.equal(h1, h2)
+    total = partials.double().sum(0) + bias.double()
+    assert (pieces.tensor().double() - partials.double().sum(0)).abs().max() <= 2 ** -8 * total.abs().max() + 1e-3
