@@ -87,6 +87,14 @@ __device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsi
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same product with the A operand in tensor memory: lane = row, two consecutive bfloat16 of K per 32-bit column.
+__device__ __forceinline__ void umma_a_in_tmem(unsigned tmem_d, unsigned tmem_a, unsigned long long b, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
 // K-major operand: rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ unsigned long long desc_k_major(const void* tile) {
     return (unsigned long long)((smem_u32(tile) & 0x3FFFFu) >> 4) | (1ull << 16) | ((unsigned long long)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
@@ -144,6 +152,13 @@ __device__ __forceinline__ void tmem_st16(unsigned taddr, const float (&v)[16]) 
                  : "memory");
 }
 
+__device__ __forceinline__ void tmem_st16_words(unsigned taddr, const unsigned* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+                   "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+                 : "memory");
+}
+
 struct AttnArgs {
     const bf16* q; int q_stride;
     bf16* out; int out_stride;
@@ -172,8 +187,7 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
     unsigned char* k_ring = base;                                                   // STAGES K tiles
     unsigned char* v_ring = base + (size_t)STAGES * TILE_BYTES;                     // STAGES V tiles
     bf16* qs = reinterpret_cast<bf16*>(base + (size_t)2 * STAGES * TILE_BYTES);     // HALVES panels of 128 rows x 64
-    bf16* ps = qs + HALVES * QPANEL;                                                // 128 rows x 64 keys
-    unsigned long long* k_full = reinterpret_cast<unsigned long long*>(ps + QPANEL);
+    unsigned long long* k_full = reinterpret_cast<unsigned long long*>(qs + HALVES * QPANEL);
     unsigned long long* k_empty = k_full + STAGES;
     unsigned long long* v_full = k_empty + STAGES;
     unsigned long long* v_empty = v_full + STAGES;
@@ -300,11 +314,11 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
                 if (!mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
                 tc_fence_after();
                 const bf16* vs = reinterpret_cast<const bf16*>(v_ring + (size_t)(j % STAGES) * TILE_BYTES);
-                const bf16* pb = ps;
+                // P(j) lies in tensor memory over the first half of S(j)'s columns: 16 keys = 8 columns per product
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk)
-                    umma(tmem + O_COL, desc_k_major(pb) + (unsigned long long)(kk * 2),
-                         desc_mn_major(vs, PANEL * 2) + (unsigned long long)(kk * (2048 >> 4)), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                    umma_a_in_tmem(tmem + O_COL, tmem + (j & 1) * BN + kk * 8, desc_mn_major(vs, PANEL * 2) + (unsigned long long)(kk * (2048 >> 4)),
+                                   idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(&v_empty[j % STAGES]);
                 umma_commit(o_done);
             }
@@ -364,14 +378,15 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
                 }
             }
             l = l * alpha + sum;
-            if (j > 0) {  // the previous product must be done before P is overwritten and before O may be rescaled
+            // P(j) goes into this thread's lane over the columns S(j) came from (the thread holds its S row in registers;
+            // the tensor core writes those columns again only with S(j + 2), issued after the product that reads P(j))
+            const unsigned* words = reinterpret_cast<const unsigned*>(packed);
+            tmem_st16_words(lane_addr + b * BN, words);
+            tmem_st16_words(lane_addr + b * BN + 16, words + 16);
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // O may be rescaled only between two products: the one before must be done (it is at most one tile behind)
                 if (!mbar_wait(o_done, (j - 1) & 1, failed)) { *failed = 1; ok = false; break; }
                 tc_fence_after();
-            }
-            uint4* prow = reinterpret_cast<uint4*>(ps + r * 64);
-#pragma unroll
-            for (int c = 0; c < BN / 8; ++c) prow[c ^ (r & 7)] = packed[c];
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
                 for (int c = 0; c < D; c += 16) {
                     float o[16];
@@ -380,9 +395,8 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
                     for (int i = 0; i < 16; ++i) o[i] *= alpha;
                     tmem_st16(lane_addr + O_COL + c, o);
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
@@ -432,7 +446,7 @@ EncodeTiled encode_tiled() {
     return fn;
 }
 
-constexpr size_t SMEM_BYTES = (size_t)2 * STAGES * TILE_BYTES + (size_t)(HALVES + 1) * QPANEL * sizeof(bf16) + (4 * STAGES + 4) * 8 + 16;
+constexpr size_t SMEM_BYTES = (size_t)2 * STAGES * TILE_BYTES + (size_t)HALVES * QPANEL * sizeof(bf16) + (4 * STAGES + 4) * 8 + 16;
 }  // namespace
 
 // Rows of a tile (tokens x heads of a group) this kernel wants: the host planner cuts rows into tiles of
