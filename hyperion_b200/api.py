@@ -210,25 +210,30 @@ class Engine:
             take_events()
             free_released()
 
-        while True:
-            plan = scheduler.next_plan_arrays() if len(in_flight) < depth else None
-            take_events()
-            if plan is not None:
-                try:
-                    in_flight.append(launch(plan))
-                except Exception as error:  # the step's requests fail, the others go on
-                    scheduler.fail_step(plan.step, f"{type(error).__name__}: {error}")
-                    take_events()
-                    free_released()
-                    if not isinstance(error, (OutOfPages, BadStep)):
-                        raise
-                    continue
-            if in_flight and (plan is None or len(in_flight) >= depth):
-                retire(*in_flight.popleft())
-            elif plan is None:
-                if scheduler.idle:
-                    break
-                raise RuntimeError("the scheduler has requests but plans nothing")
+        try:
+            while True:
+                plan = scheduler.next_plan_arrays() if len(in_flight) < depth else None
+                take_events()
+                if plan is not None:
+                    try:
+                        in_flight.append(launch(plan))
+                    except Exception as error:  # the step's requests fail, the others go on
+                        scheduler.fail_step(plan.step, f"{type(error).__name__}: {error}")
+                        take_events()
+                        free_released()
+                        if not isinstance(error, (OutOfPages, BadStep)):
+                            raise
+                        continue
+                if in_flight and (plan is None or len(in_flight) >= depth):
+                    retire(*in_flight.popleft())
+                elif plan is None:
+                    if scheduler.idle:
+                        break
+                    raise RuntimeError("the scheduler has requests but plans nothing")
+        finally:  # whatever ended the loop, this call's requests leave the cache
+            for key in np.flatnonzero(cache_key >= 0).tolist():
+                if self.cache.has(key):
+                    self.cache.free(key)
         self.check()
         return (outputs, reasons) if return_reasons else outputs
 
