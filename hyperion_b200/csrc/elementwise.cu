@@ -45,24 +45,6 @@ HB_EXPORT int hb_place_tokens(int* ids, const int* source, const int* pairs, int
     return launch_status();
 }
 
-// Asks the L2 cache to fetch [base, base + bytes) (both multiples of 16): a hint that moves no data into the SM, for
-// weights that the next kernels will stream while the ones in between leave the memory idle.
-__global__ void prefetch_l2_kernel(const unsigned char* __restrict__ base, size_t bytes, unsigned chunk) {
-    const size_t offset = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * chunk;
-    if (offset >= bytes) return;
-    const unsigned size = (unsigned)min((size_t)chunk, bytes - offset);
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + offset), "r"(size) : "memory");
-}
-
-HB_EXPORT int hb_prefetch_l2(const void* base, size_t bytes, cudaStream_t stream) {
-    if (bytes == 0) return 0;
-    if (((uintptr_t)base & 15) || (bytes & 15)) return HB_BAD_ARGUMENT;
-    const unsigned chunk = 4096;
-    const size_t threads = (bytes + chunk - 1) / chunk;
-    prefetch_l2_kernel<<<(unsigned)((threads + 127) / 128), 128, 0, stream>>>((const unsigned char*)base, bytes, chunk);
-    return launch_status();
-}
-
 // ---------------------------------------------------------------- residual add + RMSNorm
 // Output row r normalises source row s = rows ? rows[r] : r of h (+ delta). With `write_h` the sum
 // is stored back into h[s] (the residual stream); it is skipped when rows are gathered for the

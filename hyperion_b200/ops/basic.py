@@ -46,16 +46,6 @@ def place_tokens(ids: torch.Tensor, source: torch.Tensor, pairs: torch.Tensor) -
     check(library("elementwise").hb_place_tokens(ptr(ids), ptr(source), ptr(pairs), i32(pairs.numel() // 2), stream_ptr()), "place_tokens")
 
 
-def prefetch_l2(tensor: torch.Tensor, first_bytes: int | None = None) -> None:
-    """Hint: bring the tensor's first ``first_bytes`` bytes (all of it by default) into the L2 cache."""
-    require_cuda(tensor)
-    import ctypes
-
-    total = tensor.numel() * tensor.element_size()
-    count = min(total, first_bytes if first_bytes is not None else total) // 16 * 16
-    check(library("elementwise").hb_prefetch_l2(ptr(tensor), ctypes.c_size_t(count), stream_ptr()), "prefetch_l2")
-
-
 def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
                 rows: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """RMSNorm of ``h (+ delta)`` times ``weight``.
