@@ -307,6 +307,8 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) {
                     if (!mbar_wait(&k_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
+                    // S(j + 1) lands in the columns that P(j - 1) was read from: the product that read it must be over
+                    if (j > 0 && !mbar_wait(o_done, (j - 1) & 1, failed)) { *failed = 1; ok = false; break; }
                     tc_fence_after();
                     issue_s(j + 1);
                 }
@@ -401,6 +403,10 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
+        // The waits on o_done go by phase parity, so no phase may be skipped over: this thread is known to be at most one
+        // product behind (S of the last tile was seen, so every product but the last two is over); it waits for the last
+        // two in turn.
+        if (ok && n_tiles >= 2) ok = mbar_wait(o_done, (n_tiles - 2) & 1, failed);
         if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1, failed);
         if (!ok) *failed = 1;
         tc_fence_after();

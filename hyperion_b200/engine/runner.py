@@ -18,6 +18,7 @@ from .. import ops
 from .. import host as host_runtime
 from ..cache.manager import CacheManager, OutOfPages
 from ..csrc import build
+from ..ops import native
 from ..models.model import DecoderModel
 from .batch import BadStep, MetadataPacker, Rows, StepContext, StepEntry
 
@@ -173,7 +174,8 @@ class ModelRunner:
         self.last_context = context
         if device_tokens is not None and device_tokens[1]:
             ops.place_tokens(context.token_ids, device_tokens[0], context.extra.pop("device_token_pairs"))
-        logits = self.model.forward(context, self.cache) if key is None else self._replay(key, context)
+        with native.stream_bound():
+            logits = self.model.forward(context, self.cache) if key is None else self._replay(key, context)
         self.cache.advance_keys(keys, counts)
         self.steps_run += 1
         return logits
@@ -199,11 +201,9 @@ class ModelRunner:
             self._graph_seen[key] = seen
             if seen < 2 or len(self.graphs) >= MAX_GRAPHS:  # the first step of a shape runs directly (it also warms the libraries up)
                 return self.model.forward(context, self.cache)
-            from ..ops import native
-
             before = native.LAUNCHES[0]
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, pool=self._graph_pool):
+            with torch.cuda.graph(graph, pool=self._graph_pool), native.stream_bound():
                 logits = self.model.forward(context, self.cache)
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()

@@ -20,12 +20,17 @@ from .basic import sgemm_f32
 from .native import KernelError, require_cuda
 
 
+_policy: list = [None]
+
+
 def gemm_policy() -> str:
-    """``HYPERION_B200_GEMM``: ``auto`` (default), ``own`` (every bfloat16 product the tcgen05 kernel can take) or ``library``."""
-    policy = os.environ.get("HYPERION_B200_GEMM", "auto")
-    if policy not in ("auto", "own", "library"):
-        raise KernelError(f"HYPERION_B200_GEMM must be auto, own or library, got {policy!r}")
-    return policy
+    """``HYPERION_B200_GEMM`` (read once): ``auto`` (default), ``own`` (every bfloat16 product the tcgen05 kernel can take) or ``library``."""
+    if _policy[0] is None:
+        policy = os.environ.get("HYPERION_B200_GEMM", "auto")
+        if policy not in ("auto", "own", "library"):
+            raise KernelError(f"HYPERION_B200_GEMM must be auto, own or library, got {policy!r}")
+        _policy[0] = policy
+    return _policy[0]
 
 
 def _takes_own_kernel(x: torch.Tensor, weight: torch.Tensor, bias, out_dtype) -> bool:

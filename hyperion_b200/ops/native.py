@@ -27,8 +27,27 @@ def ptr(tensor: torch.Tensor | None) -> ctypes.c_void_p:
     return ctypes.c_void_p(tensor.data_ptr())
 
 
+_bound_stream: list = [None]  # the stream a step has bound for its launches, or None
+
+
 def stream_ptr() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The stream launches go to: the one bound by ``stream_bound`` if any, else torch's current stream."""
+    bound = _bound_stream[0]
+    return bound if bound is not None else ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class stream_bound:
+    """``with stream_bound():`` looks torch's current stream up once; the launches inside use it without asking again.
+    Nesting rebinds (a graph capture inside a step launches on the capture's stream)."""
+
+    def __enter__(self):
+        self.previous = _bound_stream[0]
+        _bound_stream[0] = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        _bound_stream[0] = self.previous
+        return False
 
 
 def require_cuda(*tensors: torch.Tensor | None) -> None:
@@ -57,12 +76,18 @@ def is_bf16(tensor: torch.Tensor) -> int:
     raise KernelError(f"unsupported element type {tensor.dtype} (float32 and bfloat16 only)")
 
 
+_libraries: dict = {}
+
+
 def library(module: str, **defines: Any) -> ctypes.CDLL:
-    return build.load(module, defines)
+    key = (module, tuple(sorted(defines.items()))) if defines else module
+    found = _libraries.get(key)
+    if found is None:
+        found = _libraries[key] = build.load(module, defines)
+    return found
 
 
-def i32(value: int) -> ctypes.c_int:
-    return ctypes.c_int(int(value))
+i32 = int  # a Python int is passed as a C int by ctypes itself; the name marks which arguments are 32-bit
 
 
 def f32(value: float) -> ctypes.c_float:

@@ -433,3 +433,23 @@ def test_norm_that_adds_up_split_sums_itself_gives_the_bits_of_the_two_kernel_pa
         assert torch.equal(fused, plain_way) and torch.equal(h1, h2)
     total = partials.double().sum(0) + bias.double()
     assert (pieces.tensor().double() - partials.double().sum(0)).abs().max() <= 2 ** -8 * total.abs().max() + 1e-3
+
+
+@pytest.mark.parametrize("heads, kv_heads, head_dim", [(36, 2, 64), (28, 4, 128)])
+def test_attention_gives_the_same_bits_every_time(heads, kv_heads, head_dim):
+    """Races show as results that change from run to run: the same launches 60 times over, with freed memory
+    overwritten by NaN in between so that anything read before it is written shows too."""
+    contexts = [300, 9, 130, 64, 513]
+    cache, table, keys, values = paged_case(kv_heads, head_dim, 16, contexts, torch.bfloat16, seed=5)
+    rows = [(0, 300 - 70, 70), (1, 8, 1), (2, 0, 130), (3, 62, 2), (4, 512, 1)]
+    tokens = sum(r[2] for r in rows)
+    q = rnd(tokens, (heads + 2 * kv_heads) * head_dim, seed=13, dtype=torch.bfloat16)
+    first = None
+    for _ in range(60):
+        poison = [torch.full((n,), float("nan"), device=DEV) for n in (1 << 12, 1 << 16, 1 << 20, 1 << 24)]
+        del poison
+        outs = {k: v.cpu() for k, v in run_fast_attention(q, heads, cache, table, rows, head_dim ** -0.5, 0).items()}
+        if first is None:
+            first = outs
+        for key, value in outs.items():
+            assert torch.equal(value, first[key]), f"variant {key} changed between runs"
