@@ -261,3 +261,39 @@ def test_real_layer_widths_against_the_plain_implementation(tmp_path):
         engine.check()
         del engine
         torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_bfloat16_steps_give_the_same_bits_every_time(folders, name):
+    """The same mixed steps (prompt portions, decoded tokens, graph replays among them) eight times over on one engine,
+    with freed memory overwritten by NaN in between: a race or a read of memory nobody wrote shows as logits that
+    change from run to run."""
+    from hyperion_b200.engine.batch import StepEntry
+
+    config, _ = TINY[name]
+    engine = engine_for(folders[name], "bfloat16", max_tokens=1024, max_requests=4)
+    prompts = [random_ids(600 + i, n, config.vocab_size) for i, n in enumerate([70, 33, 5])]
+
+    def run(tag):
+        logits = []
+        names = [f"{tag}{i}" for i in range(3)]
+        logits.append(engine.step([StepEntry(names[0], prompts[0][:40], [0, 39]), StepEntry(names[1], prompts[1], [32])]))
+        logits.append(engine.step([StepEntry(names[0], prompts[0][40:], [29]), StepEntry(names[2], prompts[2], [4]),
+                                   StepEntry(names[1], [7], [0])]))
+        for k in range(6):  # decoded tokens: the third such step on is a replayed graph
+            logits.append(engine.step([StepEntry(n, [11 + k], [0]) for n in names]))
+        out = [x.cpu().clone() for x in logits]
+        for n in names:
+            engine.finish(n)
+        return out
+
+    run("warm1")
+    run("warm2")  # from here on every decode step of this shape is a replay (the library's products may round differently
+    first = run("a")  # inside a captured graph than in a direct launch, so like is compared with like)
+    for repeat in range(8):
+        poison = [torch.full((n,), float("nan"), device="cuda") for n in (1 << 12, 1 << 16, 1 << 20, 1 << 22)]
+        del poison
+        again = run(f"b{repeat}_")
+        for step, (x, y) in enumerate(zip(first, again)):
+            assert torch.equal(x, y), f"repeat {repeat}, step {step}: logits changed"
+    engine.check()
