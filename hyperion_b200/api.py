@@ -57,6 +57,16 @@ class Engine:
         num_pages = max(1, -(-max_tokens // page_size))
         vocab = model.spec.vocab_size
         users = model.cache_users() + [(SAMPLER_STATE, RequestState((Sampler.seen_words(vocab),), torch.int32))]
+        # the reference checks --max-seq-len against the device's memory before it commits the pool
+        # (helios/crates/helios-hal/src/pool_plan.rs:43-60); here the pool is refused with the numbers when it cannot fit
+        itemsize = torch.empty((), dtype=model.dtype).element_size()
+        per_token = sum(2 * need.kv_heads * need.head_dim * itemsize for _, need in users if not isinstance(need, RequestState))
+        wanted = num_pages * page_size * per_token
+        free, _ = torch.cuda.mem_get_info(model.device)
+        if wanted > free:
+            raise MemoryError(f"a cache of {num_pages * page_size} tokens needs {wanted / 2**30:.1f} GiB ({per_token} bytes per token), "
+                              f"{free / 2**30:.1f} GiB are free on {model.device} beside the weights: lower max_tokens "
+                              f"(the command line's --max-seq-len, --max-batch or --cache-tokens)")
         self.cache = CacheManager(users, page_size, num_pages, max_requests, dtype=model.dtype, device=model.device)
         self.runner = ModelRunner(model, self.cache)
         self.sampler = Sampler(vocab, model.device, seen=self.cache.state_storage(SAMPLER_STATE))

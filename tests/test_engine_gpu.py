@@ -297,3 +297,8 @@ def test_bfloat16_steps_give_the_same_bits_every_time(folders, name):
         for step, (x, y) in enumerate(zip(first, again)):
             assert torch.equal(x, y), f"repeat {repeat}, step {step}: logits changed"
     engine.check()
+
+
+def test_a_cache_that_cannot_fit_is_refused_with_the_numbers(folders):
+    with pytest.raises(MemoryError, match=r"needs .* GiB .* are free"):
+        engine_for(folders["A"], "bfloat16", max_tokens=10 ** 12)
