@@ -13,7 +13,7 @@ from __future__ import annotations
 import ctypes
 from collections.abc import Sequence
 from dataclasses import dataclass, field
-from typing import Any, Callable, Hashable, Optional
+from typing import Any, Hashable, Optional
 
 import numpy as np
 import torch
