@@ -79,6 +79,14 @@ class StateView:
     row_slots: list[int]
 
 
+def _dense_strides(shape: tuple[int, ...]) -> tuple[int, ...]:
+    strides, step = [], 1
+    for extent in reversed(shape):
+        strides.append(step)
+        step *= extent
+    return tuple(reversed(strides))
+
+
 class MetadataPacker:
     """Collects int32 arrays on the host and hands back device views after one copy.
 
@@ -105,6 +113,8 @@ class MetadataPacker:
         self.capacity = capacity
         self.hosts = [torch.empty(capacity, dtype=torch.int32, pin_memory=self.device.type == "cuda") for _ in range(self.RING)]
         self.events = [None] * self.RING
+        self._recorded = [False] * self.RING  # whether the slot's event stands for a copy that may still be reading it
+        self._host_words = [host.numpy() for host in self.hosts]
         self.dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
         self.generation += 1
 
@@ -113,16 +123,16 @@ class MetadataPacker:
         self._items: list[tuple[str, int, int, tuple[int, ...]]] = []
         self._cursor = 0
         self._index = (self._index + 1) % self.RING
-        if self.events[self._index] is not None:
+        if self._recorded[self._index]:
             self.events[self._index].synchronize()
-            self.events[self._index] = None
-        self._words = self.hosts[self._index].numpy()
+            self._recorded[self._index] = False
+        self._words = self._host_words[self._index]
 
     def _grow(self, needed: int) -> None:
         """More room than the buffers have: new buffers (``generation`` tells users of the device buffer), what is written so far kept."""
         written = self._words[: self._cursor].copy()
         self._reserve(max(needed, 2 * self.capacity))
-        self._words = self.hosts[self._index].numpy()
+        self._words = self._host_words[self._index]
         self._words[: self._cursor] = written
 
     def add(self, name: str, values: Any, shape: Optional[tuple[int, ...]] = None) -> None:
@@ -173,10 +183,12 @@ class MetadataPacker:
         if self._cursor:
             self.dev[: self._cursor].copy_(self.hosts[self._index][: self._cursor], non_blocking=True)
             if self.device.type == "cuda":
-                event = torch.cuda.Event()
-                event.record()
-                self.events[self._index] = event
-        return {name: self.dev[start : start + count].view(shape) for name, start, count, shape in self._items}
+                if self.events[self._index] is None:
+                    self.events[self._index] = torch.cuda.Event()
+                self.events[self._index].record()
+                self._recorded[self._index] = True
+        dev = self.dev
+        return {name: dev.as_strided(shape, _dense_strides(shape), start) for name, start, count, shape in self._items}
 
 
 @dataclass

@@ -46,9 +46,11 @@ class ModelRunner:
         self.graph_launches = 0  # launches of this package's kernels inside replayed graphs
 
     # ------------------------------------------------------------------ validation
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    def _validate(self, entries: Sequence[StepEntry]) -> list[np.ndarray]:
+        """Refuses a malformed step; returns every entry's tokens as an array."""
         if not entries:
             raise BadStep("a step needs at least one entry")
+        arrays: list[np.ndarray] = []
         seen: set[Hashable] = set()
         vocab, limit = self.model.spec.vocab_size, self.model.spec.max_positions
         for entry in entries:
@@ -61,12 +63,14 @@ class ModelRunner:
             tokens = np.asarray(entry.tokens)
             if tokens.ndim != 1 or tokens.dtype.kind not in "iu" or int(tokens.min()) < 0 or int(tokens.max()) >= vocab:
                 raise BadStep(f"request {entry.request!r}: its tokens must be integers in 0..{vocab - 1}")
+            arrays.append(tokens)
             for index in entry.want:
                 if isinstance(index, bool) or not isinstance(index, int) or not 0 <= index < count:
                     raise BadStep(f"request {entry.request!r}: wanted index {index!r} is outside its {count} tokens")
             length = self.cache.length(entry.request) if self.cache.has(entry.request) else 0
             if length + count > limit:
                 raise BadStep(f"request {entry.request!r} would reach position {length + count}, the model's limit is {limit}")
+        return arrays
 
     # ------------------------------------------------------------------ the batch on the device
     def _context(self, names, keys: np.ndarray, counts: np.ndarray, tokens: np.ndarray, want: np.ndarray, extra_arrays=None,
@@ -110,7 +114,7 @@ class ModelRunner:
         ``tokens`` (whose value is ignored), so a token sampled by the step before need not pass
         through the host."""
         entries = list(entries)
-        self._validate(entries)
+        token_arrays = self._validate(entries)
         self._check_device_tokens(device_tokens, [len(e.tokens) for e in entries])
         added = []
         try:
@@ -125,7 +129,7 @@ class ModelRunner:
             for request in added:
                 self.cache.free(request)
             raise
-        tokens = np.concatenate([np.asarray(entry.tokens, dtype=np.int32) for entry in entries])
+        tokens = np.concatenate(token_arrays).astype(np.int32, copy=False)
         starts = np.concatenate(([0], np.cumsum(counts)[:-1]))
         want = np.asarray([int(starts[i]) + w for i, entry in enumerate(entries) for w in entry.want], dtype=np.int32)
         return self._run([entry.request for entry in entries], keys, counts, tokens, want, extra_arrays, device_tokens)
