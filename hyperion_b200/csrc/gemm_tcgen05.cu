@@ -1,16 +1,19 @@
 // bfloat16 matrix products on the 5th-generation tensor cores: C = A * W^T with A [M, K] and W [N, K],
 // both K-contiguous, accumulated in float in tensor memory.
 //
-// One block computes one tile.  Warp 0 (one lane) is the producer: it fetches 128 x 64 and BN x 64
-// operand tiles with TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a ring of
-// shared-memory stages.  Warp 1 owns tensor memory (tcgen05.alloc / dealloc) and one of its lanes
-// issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16) four times per stage, releasing the stage
-// with tcgen05.commit.  Warps 2-5 are the epilogue: each reads its quarter of the accumulator's 128
-// lanes with tcgen05.ld and writes the result.  Epilogues: bfloat16 (+ bias), float (+ bias), SwiGLU
-// over a tile whose first half are gate columns and second half the matching up columns, and a float
-// partial for split-K.  With `swap` the roles of the operands are exchanged (the weight matrix
-// supplies the 128 rows, a small batch the BN columns) and the tile is stored transposed: that is
-// the shape of decode, where M is 1..64 and the weights stream from HBM once.
+// Two kernels share the roles of their warps.  Warp 0 (one lane) is the producer: it fetches 128 x 64 and BN x 64
+// operand tiles with TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a ring of shared-memory
+// stages.  Warp 1 owns tensor memory (tcgen05.alloc / dealloc) and one of its lanes issues tcgen05.mma
+// (kind::f16, M = 128, N = BN, K = 16) four times per stage, releasing the stage with tcgen05.commit.  Warps 2-5
+// are the epilogue: each reads its quarter of the accumulator's 128 lanes with tcgen05.ld and writes the result.
+//
+// * The tile shape (prompt-sized M): one persistent block per SM walks 128 x BN tiles; the ring runs on across
+//   tiles and two accumulators alternate in tensor memory, so a tile's epilogue runs under the next tile's products.
+//   Epilogues: bfloat16 (+ bias), float (+ bias), SwiGLU over a tile whose first half are gate columns and second
+//   half the matching up columns.
+// * The swapped shape (decode, M = 1..64): the weight matrix supplies the 128 rows and the batch the BN columns, the
+//   tile is stored transposed, and K may be split over several blocks (float partials, summed by a second kernel or
+//   by their reader) so that the weights stream from HBM once at full width.
 //
 // Every wait on an mbarrier is bounded: when a wait runs out, the kernel records it in the status
 // word, all roles leave their loops, tensor memory is freed and the block returns.
@@ -123,11 +126,12 @@ __device__ __forceinline__ float bias_at(const GemmParams& p, int i) {
     return p.bias_f ? p.bias_f[i] : (p.bias_h ? __bfloat162float(p.bias_h[i]) : 0.f);
 }
 
-// map_a: the operand that supplies the tile's 128 rows (TMEM lanes); map_b: the operand that supplies its BN
-// columns.  Without SWAP map_a = activations and map_b = weights; with SWAP the other way round.
-template <int BN, int EPI, bool SWAP>
-__global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                                                       const GemmParams p) {
+// ---------------------------------------------------------------- the swapped shape (at most 64 rows of activations)
+// map_a: the weights, which supply the tile's 128 rows (TMEM lanes); map_b: the activations, which supply its BN columns.
+// One block per tile and split of K.
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS) gemm_swapped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                                               const GemmParams p) {
     using L = Layout<BN>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -170,14 +174,12 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ C
             for (int i = 0; i < ahead; ++i) {
                 unsigned char* a_tile = tiles + (size_t)i * L::STAGE_BYTES;
                 mbar_expect_tx(&full[i], L::STAGE_BYTES);
-                if (SWAP) tma_load_2d(a_tile, &map_a, &full[i], (kb_begin + i) * BK, row0);
-                else tma_load_2d(a_tile + L::A_BYTES, &map_b, &full[i], (kb_begin + i) * BK, col0);
+                tma_load_2d(a_tile, &map_a, &full[i], (kb_begin + i) * BK, row0);
             }
             wait_for_previous_kernels();
             for (int i = 0; i < ahead; ++i) {
                 unsigned char* a_tile = tiles + (size_t)i * L::STAGE_BYTES;
-                if (SWAP) tma_load_2d(a_tile + L::A_BYTES, &map_b, &full[i], (kb_begin + i) * BK, col0);
-                else tma_load_2d(a_tile, &map_a, &full[i], (kb_begin + i) * BK, row0);
+                tma_load_2d(a_tile + L::A_BYTES, &map_b, &full[i], (kb_begin + i) * BK, col0);
             }
             for (int i = ahead; i < n_kb; ++i) {
                 const int s = i % L::STAGES;
@@ -215,9 +217,8 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ C
         tc_fence_after();
         if (ok) {
             const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
-            constexpr int COLS = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
 #pragma unroll 1
-            for (int c = 0; c < COLS; c += 16) {
+            for (int c = 0; c < BN; c += 16) {
                 float v[16];
                 if (n_kb > 0) {
                     tmem_ld16(lane_addr + c, v);
@@ -225,66 +226,199 @@ __global__ void __launch_bounds__(THREADS) gemm_kernel(const __grid_constant__ C
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = 0.f;
                 }
-                if constexpr (EPI == EPI_SWIGLU) {  // columns [0, BN/2) are gates, [BN/2, BN) the matching up columns
-                    float u[16];
-                    tmem_ld16(lane_addr + BN / 2 + c, u);
-                    const int out_col = blockIdx.y * (BN / 2) + c;
-                    if (r < p.m) {
-                        bf16* dst = reinterpret_cast<bf16*>(p.c) + (size_t)r * p.ldc + out_col;
+                // lanes are output columns (weight rows r), TMEM columns are output rows (batch): store transposed
+                if (r < p.n) {
+                    const float b = (EPI == EPI_PARTIAL) ? 0.f : bias_at(p, r);
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float g = __bfloat162float(__float2bfloat16_rn(v[j])), uu = __bfloat162float(__float2bfloat16_rn(u[j]));
-                            v[j] = g / (1.0f + expf(-g)) * uu;
-                        }
-                        if (out_col + 16 <= p.n / 2 && (p.ldc & 7) == 0) {
-                            uint4 w[2];
-                            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(w);
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                            reinterpret_cast<uint4*>(dst)[0] = w[0];
-                            reinterpret_cast<uint4*>(dst)[1] = w[1];
-                        } else {
-                            for (int j = 0; j < 16; ++j)
-                                if (out_col + j < p.n / 2) dst[j] = __float2bfloat16_rn(v[j]);
-                        }
-                    }
-                } else if constexpr (SWAP) {
-                    // lanes are output columns (weight rows r), TMEM columns are output rows (batch): store transposed
-                    if (r < p.n) {
-                        const float b = (EPI == EPI_PARTIAL) ? 0.f : bias_at(p, r);
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int mrow = col0 + c + j;
-                            if (mrow >= p.m) break;
-                            if constexpr (EPI == EPI_BF16) reinterpret_cast<bf16*>(p.c)[(size_t)mrow * p.ldc + r] = __float2bfloat16_rn(v[j] + b);
-                            else if constexpr (EPI == EPI_F32) reinterpret_cast<float*>(p.c)[(size_t)mrow * p.ldc + r] = v[j] + b;
-                            else p.partial[((size_t)blockIdx.z * p.m + mrow) * p.n + r] = v[j];
-                        }
-                    }
-                } else {
-                    const int col = col0 + c;
-                    if (r < p.m && col < p.n) {
-                        if constexpr (EPI == EPI_BF16) {
-                            bf16* dst = reinterpret_cast<bf16*>(p.c) + (size_t)r * p.ldc + col;
-                            if (col + 16 <= p.n && (p.ldc & 7) == 0) {
-                                uint4 w[2];
-                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(w);
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j] + bias_at(p, col + 2 * j), v[2 * j + 1] + bias_at(p, col + 2 * j + 1));
-                                reinterpret_cast<uint4*>(dst)[0] = w[0];
-                                reinterpret_cast<uint4*>(dst)[1] = w[1];
-                            } else {
-                                for (int j = 0; j < 16 && col + j < p.n; ++j) dst[j] = __float2bfloat16_rn(v[j] + bias_at(p, col + j));
-                            }
-                        } else if constexpr (EPI == EPI_F32) {
-                            float* dst = reinterpret_cast<float*>(p.c) + (size_t)r * p.ldc + col;
-                            for (int j = 0; j < 16 && col + j < p.n; ++j) dst[j] = v[j] + bias_at(p, col + j);
-                        } else {
-                            float* dst = p.partial + ((size_t)blockIdx.z * p.m + r) * p.n + col;
-                            for (int j = 0; j < 16 && col + j < p.n; ++j) dst[j] = v[j];
-                        }
+                    for (int j = 0; j < 16; ++j) {
+                        const int mrow = col0 + c + j;
+                        if (mrow >= p.m) break;
+                        if constexpr (EPI == EPI_BF16) reinterpret_cast<bf16*>(p.c)[(size_t)mrow * p.ldc + r] = __float2bfloat16_rn(v[j] + b);
+                        else if constexpr (EPI == EPI_F32) reinterpret_cast<float*>(p.c)[(size_t)mrow * p.ldc + r] = v[j] + b;
+                        else p.partial[((size_t)blockIdx.z * p.m + mrow) * p.n + r] = v[j];
                     }
                 }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *failed) atomicOr(p.status, HB_STATUS_WAIT_EXPIRED);
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(L::TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- the tile shape, one persistent block per SM
+// Every block walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the 128 x BN grid over the output (rows
+// fastest, so blocks that run side by side share a weight tile in L2). The operand ring runs on across tiles, and the
+// accumulator alternates between two regions of tensor memory: while the epilogue warps drain one tile, the tensor core
+// already works on the next. BN is chosen per problem so that the last round of tiles leaves few SMs idle.
+template <int BN>
+struct TileLayout {
+    static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int ROOM = 227 * 1024 - 1024 - 256;
+    static constexpr int STAGES = ROOM / STAGE_BYTES > 6 ? 6 : ROOM / STAGE_BYTES;
+    static constexpr int ACC_STRIDE = 256;  // columns between the two accumulators
+    static constexpr int TMEM_COLS = 512;
+    static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + 256;
+};
+
+// One thread's row of a finished tile: accumulator lane -> output row r, columns col0 .. col0 + BN - 1 (SwiGLU: the tile's
+// first half are gate columns, the second half the matching up columns, and the output has half the width).
+template <int BN, int EPI>
+__device__ __forceinline__ void store_tile_row(const GemmParams& p, unsigned lane_addr, int r, int col0, int tile_n) {
+    constexpr int COLS = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+#pragma unroll 1
+    for (int c = 0; c < COLS; c += 16) {
+        float v[16];
+        tmem_ld16(lane_addr + c, v);
+        if constexpr (EPI == EPI_SWIGLU) {
+            float u[16];
+            tmem_ld16(lane_addr + BN / 2 + c, u);
+            const int out_col = tile_n * (BN / 2) + c;
+            if (r < p.m && out_col < p.n / 2) {
+                bf16* dst = reinterpret_cast<bf16*>(p.c) + (size_t)r * p.ldc + out_col;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {  // the projections are rounded before the activation, as separate kernels would store them
+                    const float g = __bfloat162float(__float2bfloat16_rn(v[j])), uu = __bfloat162float(__float2bfloat16_rn(u[j]));
+                    v[j] = g / (1.0f + expf(-g)) * uu;
+                }
+                if (out_col + 16 <= p.n / 2 && (p.ldc & 7) == 0) {
+                    uint4 w[2];
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(w);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                    reinterpret_cast<uint4*>(dst)[0] = w[0];
+                    reinterpret_cast<uint4*>(dst)[1] = w[1];
+                } else {
+                    for (int j = 0; j < 16; ++j)
+                        if (out_col + j < p.n / 2) dst[j] = __float2bfloat16_rn(v[j]);
+                }
+            }
+        } else {
+            const int col = col0 + c;
+            if (r < p.m && col < p.n) {
+                if constexpr (EPI == EPI_BF16) {
+                    bf16* dst = reinterpret_cast<bf16*>(p.c) + (size_t)r * p.ldc + col;
+                    if (col + 16 <= p.n && (p.ldc & 7) == 0) {
+                        uint4 w[2];
+                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(w);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j] + bias_at(p, col + 2 * j), v[2 * j + 1] + bias_at(p, col + 2 * j + 1));
+                        reinterpret_cast<uint4*>(dst)[0] = w[0];
+                        reinterpret_cast<uint4*>(dst)[1] = w[1];
+                    } else {
+                        for (int j = 0; j < 16 && col + j < p.n; ++j) dst[j] = __float2bfloat16_rn(v[j] + bias_at(p, col + j));
+                    }
+                } else {
+                    float* dst = reinterpret_cast<float*>(p.c) + (size_t)r * p.ldc + col;
+                    for (int j = 0; j < 16 && col + j < p.n; ++j) dst[j] = v[j] + bias_at(p, col + j);
+                }
+            }
+        }
+    }
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS) gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                                                             const GemmParams p, int tiles_m, int tiles_n) {
+    using L = TileLayout<BN>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(tiles + (size_t)L::STAGES * L::STAGE_BYTES);
+    unsigned long long* empty = full + L::STAGES;
+    unsigned long long* acc_full = empty + L::STAGES;  // [2]
+    unsigned long long* acc_empty = acc_full + 2;      // [2]
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    let_next_kernel_start();
+    const int total = tiles_m * tiles_n;
+    const int k_blocks = (p.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < L::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(L::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {  // producer
+            // The first ring of weight tiles is fetched before the kernels ahead in the stream have finished (no kernel
+            // writes weights); the activations, which they produce, follow after the wait.
+            const int t0 = blockIdx.x;
+            const int ahead = min(k_blocks, L::STAGES);
+            for (int i = 0; i < ahead; ++i) {
+                mbar_expect_tx(&full[i], L::STAGE_BYTES);
+                tma_load_2d(tiles + (size_t)i * L::STAGE_BYTES + L::A_BYTES, &map_w, &full[i], i * BK, (t0 / tiles_m) * BN);
+            }
+            wait_for_previous_kernels();
+            for (int i = 0; i < ahead; ++i) tma_load_2d(tiles + (size_t)i * L::STAGE_BYTES, &map_x, &full[i], i * BK, (t0 % tiles_m) * BM);
+            int it = ahead;
+            bool ok = true;
+            for (int t = t0; t < total && ok; t += gridDim.x) {
+                const int row0 = (t % tiles_m) * BM, col0 = (t / tiles_m) * BN;
+                for (int kb = (t == t0 ? ahead : 0); kb < k_blocks; ++kb, ++it) {
+                    const int s = it % L::STAGES;
+                    if (!mbar_wait(&empty[s], ((it / L::STAGES) & 1) ^ 1, failed)) { *failed = 1; ok = false; break; }
+                    unsigned char* a_tile = tiles + (size_t)s * L::STAGE_BYTES;
+                    mbar_expect_tx(&full[s], L::STAGE_BYTES);
+                    tma_load_2d(a_tile, &map_x, &full[s], kb * BK, row0);
+                    tma_load_2d(a_tile + L::A_BYTES, &map_w, &full[s], kb * BK, col0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {  // tensor-core issuer
+            const unsigned idesc = umma_idesc(BN);
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x, i = 0; t < total && ok; t += gridDim.x, ++i) {
+                const int buf = i & 1;
+                if (!mbar_wait(&acc_empty[buf], ((i >> 1) & 1) ^ 1, failed)) { *failed = 1; ok = false; break; }  // the epilogue has drained it
+                tc_fence_after();
+                const unsigned acc = tmem + buf * L::ACC_STRIDE;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % L::STAGES;
+                    if (!mbar_wait(&full[s], (it / L::STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
+                    tc_fence_after();
+                    unsigned char* a_tile = tiles + (size_t)s * L::STAGE_BYTES;
+                    const unsigned long long da = umma_desc(a_tile), db = umma_desc(a_tile + L::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16(acc, da + (unsigned long long)(k * UMMA_K * 2 / 16), db + (unsigned long long)(k * UMMA_K * 2 / 16), idesc,
+                                  (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);  // the stage is free once these products have read it
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+        }
+    } else {  // epilogue: warps 2..5 read TMEM lane quarters 2, 3, 0, 1
+        const int quarter = warp & 3;
+        wait_for_previous_kernels();  // before this thread writes anything
+        bool ok = true;
+        for (int t = blockIdx.x, i = 0; t < total && ok; t += gridDim.x, ++i) {
+            const int buf = i & 1;
+            if (!mbar_wait(&acc_full[buf], (i >> 1) & 1, failed)) { *failed = 1; ok = false; break; }
+            tc_fence_after();
+            const int tile_m = t % tiles_m, tile_n = t / tiles_m;
+            store_tile_row<BN, EPI>(p, tmem + buf * L::ACC_STRIDE + ((unsigned)(quarter * 32) << 16), tile_m * BM + quarter * 32 + lane, tile_n * BN, tile_n);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {  // this warp's quarter of the accumulator may be written again
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
             }
         }
     }
@@ -343,22 +477,64 @@ int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int bo
     return r == CUDA_SUCCESS ? 0 : HB_BAD_ARGUMENT;
 }
 
-template <int BN, int EPI, bool SWAP>
+template <int BN, int EPI>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, EPI, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Layout<BN>::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(gemm_swapped_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Layout<BN>::SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return launch_after_previous(gemm_kernel<BN, EPI, SWAP>, grid, THREADS, Layout<BN>::SMEM, stream, map_a, map_b, p);
+    return launch_after_previous(gemm_swapped_kernel<BN, EPI>, grid, THREADS, Layout<BN>::SMEM, stream, map_a, map_b, p);
+}
+
+template <int BN, int EPI>
+int launch_tiles(const CUtensorMap& map_x, const CUtensorMap& map_w, const GemmParams& p, int tiles_m, int tiles_n, int blocks, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tiles_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileLayout<BN>::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return launch_after_previous(gemm_tiles_kernel<BN, EPI>, dim3(blocks), THREADS, TileLayout<BN>::SMEM, stream, map_x, map_w, p, tiles_m, tiles_n);
+}
+
+template <int BN>
+int launch_tiles_for(int epilogue, const CUtensorMap& map_x, const CUtensorMap& map_w, const GemmParams& p, int tiles_m, int tiles_n, int blocks,
+                     cudaStream_t stream) {
+    if (epilogue == EPI_BF16) return launch_tiles<BN, EPI_BF16>(map_x, map_w, p, tiles_m, tiles_n, blocks, stream);
+    if (epilogue == EPI_F32) return launch_tiles<BN, EPI_F32>(map_x, map_w, p, tiles_m, tiles_n, blocks, stream);
+    return HB_BAD_ARGUMENT;
+}
+
+int sm_count() {
+    static int count = 0;
+    if (!count) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+            count = 148;
+    }
+    return count;
+}
+
+// The tile width that leaves the fewest SMs idle: blocks take ceil(tiles / SMs) rounds of tiles of BN columns each.
+int choose_tile_width(int m, int n, int sms) {
+    const int widths[5] = {256, 224, 192, 160, 128};
+    int best = 256;
+    long long best_cost = -1;
+    for (int bn : widths) {
+        const long long tiles = (long long)((m + BM - 1) / BM) * ((n + bn - 1) / bn);
+        const long long cost = ((tiles + sms - 1) / sms) * bn;
+        if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
+    }
+    return best;
 }
 
 template <int BN>
 int launch_swap(int epi, const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, dim3 grid, cudaStream_t stream) {
-    if (epi == EPI_BF16) return launch<BN, EPI_BF16, true>(map_w, map_x, p, grid, stream);
-    if (epi == EPI_F32) return launch<BN, EPI_F32, true>(map_w, map_x, p, grid, stream);
-    return launch<BN, EPI_PARTIAL, true>(map_w, map_x, p, grid, stream);
+    if (epi == EPI_BF16) return launch<BN, EPI_BF16>(map_w, map_x, p, grid, stream);
+    if (epi == EPI_F32) return launch<BN, EPI_F32>(map_w, map_x, p, grid, stream);
+    return launch<BN, EPI_PARTIAL>(map_w, map_x, p, grid, stream);
 }
 }  // namespace
 
@@ -383,14 +559,21 @@ HB_EXPORT int hb_gemm_bf16(const void* a, int lda, const void* w, int ldw, void*
         if (splits != 1) return HB_BAD_ARGUMENT;
         if (epilogue == EPI_SWIGLU && n % 256) return HB_UNSUPPORTED_SIZE;
         p.k_blocks_per_split = k_blocks;
+        const int sms = sm_count();
+        const int bn = epilogue == EPI_SWIGLU ? 256 : choose_tile_width(m, n, sms);
         if (int code = make_map(&map_x, a, m, k, lda, BM)) return code;
-        if (int code = make_map(&map_w, w, n, k, ldw, 256)) return code;
-        dim3 grid((m + BM - 1) / BM, (n + 255) / 256, 1);
-        if (grid.y > 65535) return HB_UNSUPPORTED_SIZE;
-        if (epilogue == EPI_BF16) return launch<256, EPI_BF16, false>(map_x, map_w, p, grid, stream);
-        if (epilogue == EPI_F32) return launch<256, EPI_F32, false>(map_x, map_w, p, grid, stream);
-        if (epilogue == EPI_SWIGLU) return launch<256, EPI_SWIGLU, false>(map_x, map_w, p, grid, stream);
-        return HB_BAD_ARGUMENT;
+        if (int code = make_map(&map_w, w, n, k, ldw, bn)) return code;
+        const int tiles_m = (m + BM - 1) / BM, tiles_n = (n + bn - 1) / bn;
+        if ((long long)tiles_m * tiles_n > 0x7fffffffLL) return HB_UNSUPPORTED_SIZE;
+        const int blocks = min(tiles_m * tiles_n, sms);
+        if (epilogue == EPI_SWIGLU) return launch_tiles<256, EPI_SWIGLU>(map_x, map_w, p, tiles_m, tiles_n, blocks, stream);
+        switch (bn) {
+            case 256: return launch_tiles_for<256>(epilogue, map_x, map_w, p, tiles_m, tiles_n, blocks, stream);
+            case 224: return launch_tiles_for<224>(epilogue, map_x, map_w, p, tiles_m, tiles_n, blocks, stream);
+            case 192: return launch_tiles_for<192>(epilogue, map_x, map_w, p, tiles_m, tiles_n, blocks, stream);
+            case 160: return launch_tiles_for<160>(epilogue, map_x, map_w, p, tiles_m, tiles_n, blocks, stream);
+            default: return launch_tiles_for<128>(epilogue, map_x, map_w, p, tiles_m, tiles_n, blocks, stream);
+        }
     }
     if ((batch_tile != 16 && batch_tile != 32 && batch_tile != 64) || m > batch_tile || epilogue == EPI_SWIGLU) return HB_BAD_ARGUMENT;
     if (splits > k_blocks) splits = k_blocks;
