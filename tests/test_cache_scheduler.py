@@ -469,3 +469,37 @@ def test_released_requests_are_not_lost_when_many_end_at_once():
         s.complete_arrays(plan.step, np.full(int(plan.sample.sum()), 5, np.int32))
     assert sorted(s.take_released()) == list(range(7)) and s.take_released() == []
     assert [e.kind for e in s.take_events()].count("finished") == 7
+
+
+def test_cancel_and_fail_while_plans_run_ahead():
+    s = Scheduler(SchedulerConfig(num_pages=100, page_size=4, max_seq_len=64, max_batch_tokens=64, max_in_flight=2))
+    for name in "abc":
+        s.enqueue(Request(name, [1, 2, 3], params(6)))
+    first = s.next_plan()   # three prompts, three samples
+    second = s.next_plan()  # three decode rows fed from the device
+    assert [r.token_from for r in second.rows] == [(0, 0), (0, 1), (0, 2)]
+    assert s.cancel("b")  # while both plans are in flight
+    events = s.complete(first, {"a": 10, "b": 11, "c": 12})
+    assert [(e.request, e.kind, e.token) for e in events if e.kind == "token"] == [("a", "token", 10), ("c", "token", 12)]
+    assert ("b", "finished", "cancelled") in [(e.request, e.kind, e.reason) for e in events]
+    third = s.next_plan()  # b is gone; a and c still feed from the device (plan 1 is in flight)
+    assert [(r.request, r.token_from) for r in third.rows] == [("a", (1, 0)), ("c", (1, 2))]
+    events = s.fail(second, "KernelError: boom")  # the older plan in flight fails: its requests fail and are released
+    assert sorted((e.request, e.kind) for e in events) == [("a", "failed"), ("c", "failed")]
+    assert sorted(s.take_released()) == ["a", "b", "c"]
+    assert s.complete(third, {"a": 1, "c": 2}) == []  # rows of requests that are gone are dropped
+    assert s.idle and s.next_plan() is None
+
+
+def test_enqueue_refuses_a_known_id_and_a_full_queue():
+    from hyperion_b200.host import QueueFull
+
+    s = Scheduler(SchedulerConfig(num_pages=100, page_size=4, max_seq_len=64, max_queue=2))
+    s.enqueue(Request("a", [1], params(1)))
+    with pytest.raises(ValueError):
+        s.enqueue(Request("a", [2], params(1)))
+    s.enqueue(Request("b", [1], params(1)))
+    with pytest.raises(QueueFull):
+        s.enqueue(Request("c", [1], params(1)))
+    drive(s)
+    s.enqueue(Request("a", [3], params(1)))  # a finished: its name may come again
