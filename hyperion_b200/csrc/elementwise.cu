@@ -22,9 +22,36 @@ __global__ void embedding_kernel(const TW* __restrict__ table, const int* __rest
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)t * hidden + i] = to_float(row[i]);
 }
 
+// bfloat16 rows whose width is a multiple of 8: one 16-byte load and two 16-byte stores per thread.
+__global__ void embedding_bf16x8_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                                        int hidden, int vocab, int* status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    if (!ok && threadIdx.x == 0) atomicOr(status, HB_STATUS_BAD_TOKEN);
+    const __nv_bfloat16* row = table + (size_t)(ok ? id : 0) * hidden;
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (ok) {
+            const uint4 v = *reinterpret_cast<const uint4*>(row + i);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+            const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]), f2 = __bfloat1622float2(h[2]), f3 = __bfloat1622float2(h[3]);
+            a = make_float4(f0.x, f0.y, f1.x, f1.y);
+            b = make_float4(f2.x, f2.y, f3.x, f3.y);
+        }
+        *reinterpret_cast<float4*>(out + (size_t)t * hidden + i) = a;
+        *reinterpret_cast<float4*>(out + (size_t)t * hidden + i + 4) = b;
+    }
+}
+
 HB_EXPORT int hb_embedding(const void* table, int table_is_bf16, const int* ids, float* out, int tokens, int hidden,
                            int vocab, int* status, cudaStream_t stream) {
     if (tokens <= 0) return 0;
+    if (table_is_bf16 && hidden % 8 == 0 && (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
+        const int threads = min(512, ((hidden / 8 + 31) / 32) * 32);
+        embedding_bf16x8_kernel<<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+        return launch_status();
+    }
     if (table_is_bf16)
         embedding_kernel<<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
     else

@@ -269,9 +269,20 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, int row_
     int bi = 0x7fffffff;
     let_next_kernel_start();
     wait_for_previous_kernels();
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    // the body in 16-byte loads where the row allows it; a thread keeps the lowest index among equal values because
+    // it walks its indices upwards and takes a later value only when it is larger
+    const bool wide = ((((uintptr_t)z) & 15) == 0) && (begin % 4 == 0);
+    const int body_end = wide ? begin + ((end - begin) / 4) * 4 : begin;
+    for (int i = begin + threadIdx.x * 4; i < body_end; i += blockDim.x * 4) {
+        const float4 v4 = *reinterpret_cast<const float4*>(z + i);
+        const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (v[e] > bv || (bi == 0x7fffffff && v[e] == v[e])) { bv = v[e]; bi = i + e; }
+    }
+    for (int i = body_end + threadIdx.x; i < end; i += blockDim.x) {
         const float v = z[i];
-        if (v > bv || (bi == 0x7fffffff && v == v)) { bv = v; bi = i; }
+        if (v > bv || (bi == 0x7fffffff && v == v) || (v == bv && i < bi)) { bv = v; bi = i; }
     }
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) {
