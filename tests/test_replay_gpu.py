@@ -150,3 +150,14 @@ def test_head_size_64_takes_the_tma_attention(model_c, cutting, tmp_path):
         steps, peak = mixed_steps(requests)
     results = run_trace(folder, "bfloat16", steps, tmp_path, max_tokens=peak)
     compare_steps(steps, results, reference, TOLERANCE["bfloat16"])
+
+
+@pytest.mark.parametrize("page_size", [8, 64])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_replay_with_other_page_sizes(model_c, dtype, page_size, tmp_path):
+    """The mixed trace (pages reused) on the configuration with heads of 64, with pages of 8 and of 64 tokens: the
+    page size is a parameter of the cache and of every kernel that walks it, not a constant."""
+    folder, requests, reference = model_c
+    steps, peak = mixed_steps(requests)
+    results = run_trace(folder, dtype, steps, tmp_path, max_tokens=peak, page_size=page_size)
+    compare_steps(steps, results, reference, TOLERANCE[dtype])
