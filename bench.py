@@ -6,7 +6,8 @@ Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch
 untimed and K timed decode steps of ``batch`` requests that were each prefilled with 2,048 random
 token ids, timed with CUDA events on the device.  ``e2e`` is the same through ``Engine.generate``
 (token ids in from the host every step, sampled ids back to the host every step).  ``prefill`` is
-one whole 2,048-token prompt in one step.  ``roofline`` relates the decode step to the bytes it has
+one whole 2,048-token prompt in one step (from its third occurrence on the engine replays a step
+shape from a captured graph, as it does for decode steps; the timed repetitions are such replays).  ``roofline`` relates the decode step to the bytes it has
 to read (every weight it uses once, plus the cache of the live requests).  ``points`` holds decode
 at batch 1 and 64.  Weights (15 GB) are larger than L2, so every step streams them from HBM.
 """

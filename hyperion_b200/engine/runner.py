@@ -25,6 +25,7 @@ from .batch import BadStep, MetadataPacker, Rows, StepContext, StepEntry
 
 GRAPH_TABLE_STEP = 64  # block-table widths of graphed steps are multiples of this many pages
 MAX_GRAPHS = 96
+GRAPH_MAX_OUTPUT_BYTES = 64 << 20
 
 
 class ModelRunner:
@@ -106,7 +107,8 @@ class ModelRunner:
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry], extra_arrays=None, device_tokens=None) -> Optional[torch.Tensor]:
         """Run the entries as one batch.  Returns float logits [wanted, vocab] on the device, in the
-        order of the entries and of each entry's ``want``, or None when nothing was wanted.
+        order of the entries and of each entry's ``want``, or None when nothing was wanted.  The tensor
+        may be written again by the next step (a replayed graph writes its output in place): copy it to keep it.
         ``extra_arrays`` ({name: (int32 values, shape)}) ride along in the step's one host-to-device
         copy and are found in ``self.last_context.extra`` afterwards.
         ``device_tokens`` = (int32 tensor on the device, {index of an entry: index into the tensor}):
@@ -184,26 +186,36 @@ class ModelRunner:
         self.steps_run += 1
         return logits
 
-    # ------------------------------------------------------------------ CUDA graphs for decode steps
+    # ------------------------------------------------------------------ CUDA graphs for steps whose shape repeats
     def _graph_key(self, keys: np.ndarray, counts: np.ndarray, want: np.ndarray, extra_arrays):
-        """Steps of single decoded tokens whose logits are all wanted repeat with the same shape: their
-        launches are captured once per (rows, table width, extra arrays) and replayed, which removes
-        the host's launch cost (the reference captures a graph per decode bucket for the same reason:
-        helios/crates/helios-hal/src/backends/hopper_sm90/session.rs:510-551)."""
-        if not self.use_graphs or len(want) != len(counts) or int(counts.max()) != 1 or not np.array_equal(want, np.arange(len(counts))):
+        """Steps of the same shape (tokens per row, number of wanted places, block-table widths in steps of
+        GRAPH_TABLE_STEP pages, extra arrays) launch the same kernels with the same arguments: everything that
+        differs between them lies in the metadata buffer.  Such a step is captured into a CUDA graph when its
+        shape comes again and replayed from then on, which removes the host's launch cost (the reference captures
+        a graph per decode bucket and per prefill capacity for the same reason:
+        helios/crates/helios-hal/src/backends/hopper_sm90/session.rs:510-551).  Steps of single decoded tokens
+        are captured at their second sighting, other shapes at their third."""
+        if not self.use_graphs:
             return None
+        decode = len(want) == len(counts) and int(counts.max()) == 1 and np.array_equal(want, np.arange(len(counts)))
+        if not decode and len(want) * self.model.spec.vocab_size * 4 > GRAPH_MAX_OUTPUT_BYTES:
+            return None  # a graph keeps its output alive: not for steps that want logits at hundreds of places
         widths = np.zeros(max(1, len(self.cache.paged)), dtype=np.int32)
         host_runtime.check(host_runtime.library().hb_step_decode_widths(self.cache.native, len(keys), host_runtime.address(keys), GRAPH_TABLE_STEP,
                                                                         host_runtime.address(widths)))
         extras = tuple((name, len(values)) for name, (values, _) in (extra_arrays or {}).items())
-        return (len(keys), tuple(widths[: len(self.cache.paged)].tolist()), extras)
+        shape = len(keys) if decode else tuple(counts.tolist())
+        return (shape, len(want), tuple(widths[: len(self.cache.paged)].tolist()), extras)
 
     def _replay(self, key, context: StepContext):
         entry = self.graphs.get(key)
         if entry is None:
+            if len(self._graph_seen) > 4 * MAX_GRAPHS:  # shapes that never came again are forgotten
+                self._graph_seen.clear()
             seen = self._graph_seen.get(key, 0) + 1
             self._graph_seen[key] = seen
-            if seen < 2 or len(self.graphs) >= MAX_GRAPHS:  # the first step of a shape runs directly (it also warms the libraries up)
+            needed = 2 if isinstance(key[0], int) else 3
+            if seen < needed or len(self.graphs) >= MAX_GRAPHS:  # the first steps of a shape run directly (they also warm the libraries up)
                 return self.model.forward(context, self.cache)
             before = native.LAUNCHES[0]
             graph = torch.cuda.CUDAGraph()

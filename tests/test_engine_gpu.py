@@ -275,21 +275,20 @@ def test_bfloat16_steps_give_the_same_bits_every_time(folders, name):
     prompts = [random_ids(600 + i, n, config.vocab_size) for i, n in enumerate([70, 33, 5])]
 
     def run(tag):
-        logits = []
+        logits = []  # copied at once: a replayed graph writes its output in place
         names = [f"{tag}{i}" for i in range(3)]
-        logits.append(engine.step([StepEntry(names[0], prompts[0][:40], [0, 39]), StepEntry(names[1], prompts[1], [32])]))
+        logits.append(engine.step([StepEntry(names[0], prompts[0][:40], [0, 39]), StepEntry(names[1], prompts[1], [32])]).cpu())
         logits.append(engine.step([StepEntry(names[0], prompts[0][40:], [29]), StepEntry(names[2], prompts[2], [4]),
-                                   StepEntry(names[1], [7], [0])]))
-        for k in range(6):  # decoded tokens: the third such step on is a replayed graph
-            logits.append(engine.step([StepEntry(n, [11 + k], [0]) for n in names]))
-        out = [x.cpu().clone() for x in logits]
+                                   StepEntry(names[1], [7], [0])]).cpu())
+        for k in range(6):  # decoded tokens
+            logits.append(engine.step([StepEntry(n, [11 + k], [0]) for n in names]).cpu())
         for n in names:
             engine.finish(n)
-        return out
+        return logits
 
-    run("warm1")
-    run("warm2")  # from here on every decode step of this shape is a replay (the library's products may round differently
-    first = run("a")  # inside a captured graph than in a direct launch, so like is compared with like)
+    for warm in range(3):
+        run(f"warm{warm}")  # from here on every step of these shapes is a replay (the library's products may round
+    first = run("a")  # differently inside a captured graph than in a direct launch, so like is compared with like)
     for repeat in range(8):
         poison = [torch.full((n,), float("nan"), device="cuda") for n in (1 << 12, 1 << 16, 1 << 20, 1 << 22)]
         del poison
