@@ -161,6 +161,11 @@ int table_width(const hb::CacheIndex& index, int group, int n_rows, const int64_
         width = std::max(width, blocks);
     }
     if (table_step > 0) width = (width + table_step - 1) / table_step * table_step;
+    if (table_step < 0) {  // the next power of two, at least -table_step: few distinct widths over a long context
+        int rounded = -table_step;
+        while (rounded < width) rounded *= 2;
+        width = rounded;
+    }
     return width;
 }
 }  // namespace

@@ -58,7 +58,7 @@ int hb_cache_check(const HbCache* cache);
  *   0 token_ids [T]   1 positions [T]   2 token_row [T]   3 row_start [R + 1]   4 slots [R]   5 want [W]
  *   6 + g: block table of group g [R, width_g], missing pages as -1
  * width_g is the longest table of the step's rows, at least 1, rounded up to a multiple of table_step when
- * that is positive. layout receives (offset, count, rows, columns) per array; *cursor moves past them.
+ * that is positive, and to -table_step times a power of two when it is negative. layout receives (offset, count, rows, columns) per array; *cursor moves past them.
  * Positions start at each request's current length; call it after hb_cache_extend_all and before advancing.
  */
 int hb_step_pack(const HbCache* cache, int n_rows, const int64_t* keys, const int* counts, const int* tokens, int n_want,

@@ -23,7 +23,7 @@ from ..models.model import DecoderModel
 from .batch import BadStep, MetadataPacker, Rows, StepContext, StepEntry
 
 
-GRAPH_TABLE_STEP = 64  # block-table widths of graphed steps are multiples of this many pages
+GRAPH_TABLE_STEP = -64  # block-table widths of graphed steps: 64 pages times a power of two (the runtime's rule for negative steps)
 MAX_GRAPHS = 96
 GRAPH_MAX_OUTPUT_BYTES = 64 << 20
 
@@ -78,7 +78,7 @@ class ModelRunner:
                  pad_tables: bool = False, device_places=None) -> StepContext:
         packer = self.packer
         packer.begin()
-        # a replayed graph needs the same layout for many steps: its table widths are multiples of GRAPH_TABLE_STEP
+        # a replayed graph needs the same layout for many steps: its table widths are 64 pages times a power of two
         packer.add_step(self.cache, keys, counts, tokens, want, GRAPH_TABLE_STEP if pad_tables else 0)
         starts = packer.view("row_start")
         starts = starts[:-1].copy()
@@ -188,8 +188,8 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ CUDA graphs for steps whose shape repeats
     def _graph_key(self, keys: np.ndarray, counts: np.ndarray, want: np.ndarray, extra_arrays):
-        """Steps of the same shape (tokens per row, number of wanted places, block-table widths in steps of
-        GRAPH_TABLE_STEP pages, extra arrays) launch the same kernels with the same arguments: everything that
+        """Steps of the same shape (tokens per row, number of wanted places, block-table widths rounded up to 64 pages
+        times a power of two, extra arrays) launch the same kernels with the same arguments: everything that
         differs between them lies in the metadata buffer.  Such a step is captured into a CUDA graph when its
         shape comes again and replayed from then on, which removes the host's launch cost (the reference captures
         a graph per decode bucket and per prefill capacity for the same reason:
