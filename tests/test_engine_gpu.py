@@ -301,3 +301,34 @@ def test_bfloat16_steps_give_the_same_bits_every_time(folders, name):
 def test_a_cache_that_cannot_fit_is_refused_with_the_numbers(folders):
     with pytest.raises(MemoryError, match=r"needs .* GiB .* are free"):
         engine_for(folders["A"], "bfloat16", max_tokens=10 ** 12)
+
+
+def test_forty_requests_through_a_small_pool_running_ahead_or_not(folders, tmp_path):
+    """Forty requests of random lengths and budgets, a tenth of the vocabulary as end-of-sequence tokens, a pool of 24
+    pages and at most 5 live requests: the loop that runs ahead gives the tokens and reasons of the step-by-step loop,
+    and every page and slot comes back."""
+    import json
+    import random
+    import shutil
+
+    from hyperion_b200.sampling import SamplingParams
+
+    config, _ = TINY["B"]
+    rng = random.Random(11)
+    folder = tmp_path / "many_eos"
+    shutil.copytree(folders["B"], folder)
+    document = json.loads((folder / "config.json").read_text())
+    document["eos_token_id"] = rng.sample(range(config.vocab_size), config.vocab_size // 10)
+    (folder / "config.json").write_text(json.dumps(document))
+    prompts = [random_ids(700 + i, rng.randrange(1, 60), config.vocab_size) for i in range(40)]
+    params = [SamplingParams(temperature=rng.choice([0.0, 0.7, 1.3]), top_k=rng.choice([0, 5]), seed=900 + i, max_tokens=rng.randrange(1, 30))
+              for i in range(40)]
+    results = []
+    for lookahead in (False, True):
+        engine = engine_for(folder, "float32", page_size=16, max_tokens=24 * 16, max_requests=5)
+        results.append(engine.generate(prompts, params, max_batch_tokens=48, prefill_chunk_busy=16, return_reasons=True, lookahead=lookahead))
+        engine.cache.check()
+        assert engine.cache.free_pages() == 24 and not engine.cache.live_requests
+    assert results[0] == results[1]
+    reasons = results[0][1]
+    assert reasons.count("stop") >= 5 and reasons.count("length") >= 5
