@@ -33,6 +33,7 @@ constexpr int TILE_ELEMS = HALVES * PANEL;    // one K (or V) tile
 constexpr int STAGE_BYTES = 2 * TILE_ELEMS * 2;
 constexpr int LDQ = D + 8;                    // padded row of the query tile
 constexpr int CONSUMERS = 4;
+constexpr int FRESH_TOKENS = 4;                // a row that takes the token shape brings at most this many tokens (the planner's TOKEN_SHAPE_MAX)
 constexpr int THREADS = 32 * (CONSUMERS + 1);
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 
@@ -238,20 +239,38 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
         uint4* stage = reinterpret_cast<uint4*>(ring + (size_t)s * STAGE_BYTES);
         for (int e = tid; e < STAGE_BYTES / 16; e += THREADS) stage[e] = make_uint4(0, 0, 0, 0);
     }
-    wait_for_previous_kernels();  // the queries and the newest keys and values come from the kernel before
-    // queries: virtual row v = token * gc + head
-    for (int e = tid; e < ROWS * (D / 8); e += THREADS) {
-        const int v = e / (D / 8), c = e - v * (D / 8);
-        const int tok = v / gc, hh = v - tok * gc;
-        uint4 value = make_uint4(0, 0, 0, 0);
-        if (tok < ntok && hh < heads_here)
-            value = *reinterpret_cast<const uint4*>(a.q + (size_t)(tok0 + tok) * a.q_stride + (size_t)(first_head + hh) * D + c * 8);
-        *reinterpret_cast<uint4*>(qs + v * LDQ + c * 8) = value;
+    // The token shape lets its producer start before the kernels ahead in the stream have finished: keys and values of
+    // earlier steps are in the cache already, only the newest positions (and the queries) come from the kernel before.
+    // Its consumers wait, fetch the queries and meet at a barrier of their own; the tile shape waits as a whole.
+    if (TOKENS) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
     }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
+    if (!TOKENS || warp != CONSUMERS) {
+        wait_for_previous_kernels();  // the queries and the newest keys and values come from the kernel before
+        // queries: virtual row v = token * gc + head
+        const int loaders = TOKENS ? 32 * CONSUMERS : THREADS;
+        for (int e = tid; e < ROWS * (D / 8); e += loaders) {
+            const int v = e / (D / 8), c = e - v * (D / 8);
+            const int tok = v / gc, hh = v - tok * gc;
+            uint4 value = make_uint4(0, 0, 0, 0);
+            if (tok < ntok && hh < heads_here)
+                value = *reinterpret_cast<const uint4*>(a.q + (size_t)(tok0 + tok) * a.q_stride + (size_t)(first_head + hh) * D + c * 8);
+            *reinterpret_cast<uint4*>(qs + v * LDQ + c * 8) = value;
+        }
+    }
+    if (TOKENS) {
+        if (warp != CONSUMERS) asm volatile("bar.sync 1, %0;" ::"n"(32 * CONSUMERS) : "memory");
+    } else {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+    }
 
     if (warp == CONSUMERS) {
+        // a token of this shape sees at most FRESH_TOKENS positions written by the kernel before (its own and those of
+        // the same row's tokens before it): tiles that end below them may be fetched at once
+        bool waited = !TOKENS;
+        const int fresh_from = pos_first - (FRESH_TOKENS - 1);
         // ------------------------------------------------------------------ producer
         // The whole warp takes part: lane p looks up page p of the tile, lane 0 arms the barrier with the byte count,
         // then every lane issues one copy (page, K or V, 64-column panel), so the copies of a tile start together.
@@ -266,17 +285,25 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
             if (lane == 0) ok = mbar_wait(&empty[s], (round & 1) ^ 1, failed) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) {
+                if (!waited) wait_for_previous_kernels();  // no write to global memory before that
                 if (lane == 0) { *failed = 1; atomicOr(a.status, HB_STATUS_WAIT_EXPIRED); }
                 break;
             }
             const int base = start + it * BN;
+            if (!waited && base + BN - 1 >= fresh_from) {
+                wait_for_previous_kernels();
+                waited = true;
+            }
             int my_page = -1;
             const int k0 = base + lane * a.page_size;
             if (lane < pages_per_tile && k0 <= pos_last && k0 + a.page_size - 1 >= need_lo) {
                 const int block = k0 >> shift;
                 const int id = block < a.table_width ? __ldg(table + block) : -1;
                 if (id >= 0 && id < a.pages) my_page = id;
-                else atomicOr(a.status, HB_STATUS_BAD_PAGE);
+                else {
+                    if (!waited) wait_for_previous_kernels();
+                    atomicOr(a.status, HB_STATUS_BAD_PAGE);
+                }
             }
             const unsigned valid = __popc(__ballot_sync(0xffffffffu, my_page >= 0));
             if (lane == 0) {

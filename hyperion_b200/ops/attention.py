@@ -16,7 +16,7 @@ from .. import host as host_runtime
 from .basic import status_word
 from .native import KernelError, check, f32, i32, library, ptr, require_cuda, stream_ptr
 
-TOKEN_SHAPE_MAX = 4
+TOKEN_SHAPE_MAX = 4  # at most csrc/attention_tma.cu's FRESH_TOKENS: its producer fetches older keys before the kernel ahead has finished
 TILE_ROWS = 64
 KEY_TILE = 64
 TARGET_BLOCKS = 148 * 2  # two blocks of the token shape fit one SM
