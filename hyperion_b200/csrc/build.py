@@ -157,13 +157,19 @@ def _host_compiler() -> str:
     raise BuildError("no C++ compiler found (looked at HYPERION_B200_CXX, CXX, g++, c++, clang++): the host runtime cannot be built")
 
 
+def _host_flags() -> list[str]:
+    """``HOST_FLAGS`` plus what ``HYPERION_B200_CXXFLAGS`` adds (for instance ``-fsanitize=address,undefined -g`` to run the
+    host tests under the sanitizers, with the sanitizer's runtime preloaded into the interpreter)."""
+    return HOST_FLAGS + os.environ.get("HYPERION_B200_CXXFLAGS", "").split()
+
+
 def host_library_path() -> Path:
     digest = hashlib.sha256()
     for path in sorted(HOST_DIR.iterdir()):
         if path.suffix in (".cpp", ".hpp", ".h"):
             digest.update(path.name.encode())
             digest.update(path.read_bytes())
-    digest.update(" ".join(HOST_FLAGS).encode())
+    digest.update(" ".join(_host_flags()).encode())
     return _build_dir() / f"hb_host_runtime-{digest.hexdigest()[:16]}.so"
 
 
@@ -176,7 +182,7 @@ def load_host() -> ctypes.CDLL:
     if not target.is_file():
         scratch = target.with_suffix(f".tmp{os.getpid()}.so")
         sources = sorted(str(p) for p in HOST_DIR.glob("*.cpp"))
-        command = [_host_compiler(), *HOST_FLAGS, "-I", str(HOST_DIR), "-o", str(scratch), *sources]
+        command = [_host_compiler(), *_host_flags(), "-I", str(HOST_DIR), "-o", str(scratch), *sources]
         started = time.time()
         print("[hyperion_b200] compiling the host runtime ...", file=sys.stderr, flush=True)
         done = subprocess.run(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
