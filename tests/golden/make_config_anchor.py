@@ -1,0 +1,80 @@
+"""Runs the reference's own config reader on a set of config.json documents and records what it makes of each.
+
+The reference's build-time package is plain Python (ignition/src/hyperion_ignition); its
+``model_config_from_hf`` (compiler/model_config.py:95-169) is what decides which Qwen2 configurations it takes and
+what the fields mean.  This script imports it from a checkout of the reference, feeds it the reference's own two
+configurations (testdata/synthetic/qwen2-tiny-sharded/config.json, ignition/tests/fixtures/qwen2-hf/config.json) and
+variants of them (defaults left out, the nested rope form, every refusal), and writes the documents with the outcomes:
+
+    python tests/golden/make_config_anchor.py /path/to/reference
+
+Output (committed): tests/golden/ignition-config-cases.json.  ``tests/test_config_weights.py`` holds this
+package's reader to the same outcomes.
+"""
+import dataclasses
+import json
+import sys
+import tempfile
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+
+
+def variants(tiny: dict, large: dict) -> list[tuple[str, dict]]:
+    def changed(base, **changes):
+        document = dict(base)
+        for key, value in changes.items():
+            if value is None:
+                document.pop(key, None)
+            else:
+                document[key] = value
+        return document
+
+    nested = changed(large, rope_theta=None, rope_parameters={"rope_theta": 500000.0, "rope_type": "default"})
+    return [
+        ("the reference's tiny checkpoint", tiny),
+        ("the reference's 7B fixture", large),
+        ("head_dim stated", changed(large, head_dim=128)),
+        ("head_dim unlike hidden / heads", changed(tiny, head_dim=32)),
+        ("no num_key_value_heads", changed(tiny, num_key_value_heads=None)),
+        ("rope_theta nested in rope_parameters", nested),
+        ("tied embeddings", changed(tiny, tie_word_embeddings=True)),
+        ("rope_scaling set", changed(large, rope_scaling={"type": "yarn", "factor": 4.0})),
+        ("rope_scaling null", changed(large, rope_scaling=None) | {"rope_scaling": None}),
+        ("use_sliding_window true", changed(large, use_sliding_window=True)),
+        ("hidden_act gelu", changed(large, hidden_act="gelu")),
+        ("partial rotary", changed(large, partial_rotary_factor=0.5)),
+        ("tie_word_embeddings missing", changed(large, tie_word_embeddings=None)),
+        ("rms_norm_eps missing", changed(large, rms_norm_eps=None)),
+        ("rope_theta missing", changed(large, rope_theta=None)),
+        ("kv heads do not divide heads", changed(large, num_key_value_heads=5)),
+        ("hidden not divisible by heads", changed(tiny, hidden_size=66)),
+        ("another architecture", changed(large, architectures=["LlamaForCausalLM"])),
+        ("vocab_size zero", changed(large, vocab_size=0)),
+        ("num_hidden_layers a string", changed(large, num_hidden_layers="28")),
+    ]
+
+
+def main(reference: Path) -> None:
+    sys.path.insert(0, str(reference / "ignition" / "src"))
+    from hyperion_ignition.compiler.model_config import model_config_from_hf
+
+    tiny = json.loads((reference / "testdata" / "synthetic" / "qwen2-tiny-sharded" / "config.json").read_text())
+    large = json.loads((reference / "ignition" / "tests" / "fixtures" / "qwen2-hf" / "config.json").read_text())
+    cases = []
+    for name, document in variants(tiny, large):
+        with tempfile.TemporaryDirectory() as folder:
+            (Path(folder) / "config.json").write_text(json.dumps(document))
+            try:
+                config = model_config_from_hf(Path(folder), ("Qwen2ForCausalLM",), qkv_bias=True)
+                outcome = {"accepted": dataclasses.asdict(config)}
+            except (ValueError, KeyError, TypeError, FileNotFoundError) as error:
+                outcome = {"refused": f"{type(error).__name__}: {error}"}
+        cases.append({"name": name, "config": document, **outcome})
+    (HERE / "ignition-config-cases.json").write_text(json.dumps({
+        "source": "model_config_from_hf of the reference (ignition/src/hyperion_ignition/compiler/model_config.py:95-169)", "cases": cases}, indent=1))
+    print(f"{sum('accepted' in c for c in cases)} accepted, {sum('refused' in c for c in cases)} refused")
+
+
+if __name__ == "__main__":
+    main(Path(sys.argv[1]))

@@ -185,3 +185,26 @@ def test_sharded_folders_and_their_errors(tmp_path):
         read_model_index(folder)
     with pytest.raises(FileNotFoundError):
         read_model_index(tmp_path / "nothing")
+
+
+def test_the_config_reader_takes_and_refuses_what_the_reference_reader_does():
+    """tests/golden/ignition-config-cases.json holds what the reference's own reader made of 20 documents (made by
+    tests/golden/make_config_anchor.py): the same documents are accepted with the same fields, or refused, here."""
+    import json
+    from pathlib import Path
+
+    from hyperion_b200.config import ConfigError, Qwen2Config
+
+    cases = json.loads((Path(__file__).parent / "golden" / "ignition-config-cases.json").read_text())["cases"]
+    assert len(cases) == 20
+    for case in cases:
+        if "refused" in case:
+            with pytest.raises(ConfigError):
+                Qwen2Config.from_hf_dict(case["config"])
+            continue
+        ours, theirs = Qwen2Config.from_hf_dict(case["config"]), case["accepted"]
+        assert (ours.num_hidden_layers, ours.hidden_size, ours.intermediate_size, ours.num_attention_heads, ours.num_key_value_heads,
+                ours.head_dim, ours.vocab_size, ours.max_position_embeddings, ours.rope_theta, ours.rms_norm_eps, ours.tie_word_embeddings,
+                ours.qkv_bias) == (theirs["num_layers"], theirs["hidden_size"], theirs["intermediate_size"], theirs["num_attention_heads"],
+                                   theirs["num_kv_heads"], theirs["head_dim"], theirs["vocab_size"], theirs["max_seq_len"], theirs["rope_theta"],
+                                   theirs["rms_norm_eps"], theirs["tie_word_embeddings"], theirs["qkv_bias"]), case["name"]
