@@ -11,7 +11,8 @@ cuts the oracle down to what the test reads.
 
     python tests/golden/make_anchor.py /path/to/reference
 
-Outputs (committed): tests/golden/qwen2-tiny-sharded/ and tests/golden/qwen2-tiny-oracle.json.
+Outputs (committed): tests/golden/qwen2-tiny-sharded/ (with the reference's expected.json: shard, length and first
+and last 16 bytes of every tensor, written by scripts/gen-sharded-fixture.py:59-66) and tests/golden/qwen2-tiny-oracle.json.
 """
 import json
 import shutil
@@ -26,7 +27,7 @@ def main(reference: Path) -> None:
     target = HERE / "qwen2-tiny-sharded"
     target.mkdir(exist_ok=True)
     for path in sorted(source.iterdir()):
-        if path.suffix == ".safetensors" or path.name in ("config.json", "model.safetensors.index.json"):
+        if path.suffix == ".safetensors" or path.name in ("config.json", "model.safetensors.index.json", "expected.json"):
             shutil.copyfile(path, target / path.name)
     oracle = json.loads((reference / "testdata" / "oracle" / "qwen2-tiny-sharded.compact.json").read_text())
     prompts = []

@@ -208,3 +208,21 @@ def test_the_config_reader_takes_and_refuses_what_the_reference_reader_does():
                 ours.qkv_bias) == (theirs["num_layers"], theirs["hidden_size"], theirs["intermediate_size"], theirs["num_attention_heads"],
                                    theirs["num_kv_heads"], theirs["head_dim"], theirs["vocab_size"], theirs["max_seq_len"], theirs["rope_theta"],
                                    theirs["rms_norm_eps"], theirs["tie_word_embeddings"], theirs["qkv_bias"]), case["name"]
+
+
+def test_the_reader_returns_the_bytes_the_reference_recorded_for_its_checkpoint():
+    """expected.json of the reference's sharded fixture names, for every tensor, its shard, its length in bytes and its
+    first and last 16 bytes (the reference checks device bytes against file bytes the same way,
+    helios/crates/helios-hal/tests/weights_hw.rs:58): the reader finds every tensor in that shard with those bytes."""
+    import json
+    from pathlib import Path
+
+    folder = Path(__file__).parent / "golden" / "qwen2-tiny-sharded"
+    expected = json.loads((folder / "expected.json").read_text())
+    entries = read_model_index(folder)
+    tensors = read_all(folder)
+    assert set(entries) == set(expected) == set(tensors)
+    for name, record in expected.items():
+        raw = tensors[name].contiguous().view(torch.uint8).reshape(-1).numpy().tobytes()
+        assert entries[name].path.name == record["shard"] and len(raw) == record["length"], name
+        assert raw[:16].hex() == record["first16"] and raw[-16:].hex() == record["last16"], name
