@@ -71,9 +71,39 @@ def main(reference: Path) -> None:
             except (ValueError, KeyError, TypeError, FileNotFoundError) as error:
                 outcome = {"refused": f"{type(error).__name__}: {error}"}
         cases.append({"name": name, "config": document, **outcome})
+    from hyperion_ignition.compiler.generation import read_generation
+
+    generation_cases = []
+    for name, config_eos, generation in [
+        ("one id in config.json", 7, None),
+        ("a list in generation_config.json", None, {"eos_token_id": [3, 9]}),
+        ("both, overlapping: config first, no repeats", [9, 4], {"eos_token_id": [3, 9, 4, 11]}),
+        ("sampling defaults", 7, {"temperature": 0.7, "top_p": 0.8, "top_k": 20, "repetition_penalty": 1.05}),
+        ("some sampling defaults, top_k as a float", 7, {"temperature": 0.6, "top_k": 20.0}),
+        ("null values are left out", 7, {"temperature": None, "top_p": 0.9}),
+        ("a negative value", 7, {"temperature": -1.0}),
+        ("a boolean value", 7, {"top_p": True}),
+        ("a negative id", -2, None),
+        ("a boolean id", None, {"eos_token_id": [True]}),
+    ]:
+        document = dict(large)
+        document.pop("eos_token_id", None)
+        if config_eos is not None:
+            document["eos_token_id"] = config_eos
+        with tempfile.TemporaryDirectory() as folder:
+            (Path(folder) / "config.json").write_text(json.dumps(document))
+            if generation is not None:
+                (Path(folder) / "generation_config.json").write_text(json.dumps(generation))
+            try:
+                outcome = {"accepted": read_generation(Path(folder))}
+            except (ValueError, KeyError, TypeError) as error:
+                outcome = {"refused": f"{type(error).__name__}: {error}"}
+        generation_cases.append({"name": name, "config": document, "generation_config": generation, **outcome})
     (HERE / "ignition-config-cases.json").write_text(json.dumps({
-        "source": "model_config_from_hf of the reference (ignition/src/hyperion_ignition/compiler/model_config.py:95-169)", "cases": cases}, indent=1))
-    print(f"{sum('accepted' in c for c in cases)} accepted, {sum('refused' in c for c in cases)} refused")
+        "source": "model_config_from_hf and read_generation of the reference (ignition/src/hyperion_ignition/compiler/model_config.py:95-169, "
+                  "generation.py:51-71)", "cases": cases, "generation_cases": generation_cases}, indent=1))
+    print(f"{sum('accepted' in c for c in cases)} accepted, {sum('refused' in c for c in cases)} refused; generation: "
+          f"{sum('accepted' in c for c in generation_cases)} accepted, {sum('refused' in c for c in generation_cases)} refused")
 
 
 if __name__ == "__main__":

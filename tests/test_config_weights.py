@@ -226,3 +226,31 @@ def test_the_reader_returns_the_bytes_the_reference_recorded_for_its_checkpoint(
         raw = tensors[name].contiguous().view(torch.uint8).reshape(-1).numpy().tobytes()
         assert entries[name].path.name == record["shard"] and len(raw) == record["length"], name
         assert raw[:16].hex() == record["first16"] and raw[-16:].hex() == record["last16"], name
+
+
+def test_generation_defaults_follow_the_reference_reader(tmp_path):
+    """The same folders give the end-of-sequence ids (config.json first, no repeats) and sampling defaults that the
+    reference's ``read_generation`` gave, and what it refused is refused."""
+    import json
+    from pathlib import Path
+
+    from hyperion_b200.config import ConfigError
+    from hyperion_b200.config.generation import GenerationDefaults, read_generation_defaults
+
+    cases = json.loads((Path(__file__).parent / "golden" / "ignition-config-cases.json").read_text())["generation_cases"]
+    assert len(cases) == 10
+    for index, case in enumerate(cases):
+        folder = tmp_path / str(index)
+        folder.mkdir()
+        (folder / "config.json").write_text(json.dumps(case["config"]))
+        if case["generation_config"] is not None:
+            (folder / "generation_config.json").write_text(json.dumps(case["generation_config"]))
+        if "refused" in case:
+            with pytest.raises(ConfigError):
+                read_generation_defaults(folder)
+            continue
+        ours, theirs = read_generation_defaults(folder), case["accepted"]
+        assert list(ours.eos_token_ids) == theirs["eos_token_ids"], case["name"]
+        defaults = GenerationDefaults()
+        for key in ("temperature", "top_p", "top_k", "repetition_penalty"):
+            assert getattr(ours, key) == theirs.get("sampling_defaults", {}).get(key, getattr(defaults, key)), (case["name"], key)
