@@ -99,9 +99,19 @@ def main(reference: Path) -> None:
             except (ValueError, KeyError, TypeError) as error:
                 outcome = {"refused": f"{type(error).__name__}: {error}"}
         generation_cases.append({"name": name, "config": document, "generation_config": generation, **outcome})
+    from hyperion_ignition.compiler.weights import _qwen2_expected
+
+    tensor_cases = []
+    for name, document in (("the reference's tiny checkpoint (untied)", tiny), ("tied", dict(tiny, tie_word_embeddings=True))):
+        with tempfile.TemporaryDirectory() as folder:
+            (Path(folder) / "config.json").write_text(json.dumps(document))
+            config = model_config_from_hf(Path(folder), ("Qwen2ForCausalLM",), qkv_bias=True)
+        expected = _qwen2_expected(config, document["tie_word_embeddings"])
+        tensor_cases.append({"name": name, "config": document, "tensors": {k: list(v) for k, v in expected.items()}})
     (HERE / "ignition-config-cases.json").write_text(json.dumps({
         "source": "model_config_from_hf and read_generation of the reference (ignition/src/hyperion_ignition/compiler/model_config.py:95-169, "
-                  "generation.py:51-71)", "cases": cases, "generation_cases": generation_cases}, indent=1))
+                  "generation.py:51-71)", "cases": cases, "generation_cases": generation_cases,
+        "tensor_cases": tensor_cases, "tensor_source": "_qwen2_expected (compiler/weights.py:175-207): names and shapes, null = the hidden size"}, indent=1))
     print(f"{sum('accepted' in c for c in cases)} accepted, {sum('refused' in c for c in cases)} refused; generation: "
           f"{sum('accepted' in c for c in generation_cases)} accepted, {sum('refused' in c for c in generation_cases)} refused")
 

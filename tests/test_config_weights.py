@@ -254,3 +254,26 @@ def test_generation_defaults_follow_the_reference_reader(tmp_path):
         defaults = GenerationDefaults()
         for key in ("temperature", "top_p", "top_k", "repetition_penalty"):
             assert getattr(ours, key) == theirs.get("sampling_defaults", {}).get(key, getattr(defaults, key)), (case["name"], key)
+
+
+def test_expected_tensor_names_and_shapes_are_those_of_the_reference():
+    """The reference's table of expected tensors (names by Hugging Face convention, shapes with the hidden size left
+    open) for its tiny configuration, tied and untied: the model built from parts expects exactly those."""
+    import json
+    from pathlib import Path
+
+    cases = json.loads((Path(__file__).parent / "golden" / "ignition-config-cases.json").read_text())["tensor_cases"]
+    for case in cases:
+        architecture = get_architecture("Qwen2ForCausalLM")
+        config = architecture.read_config(case["config"])
+        model = DecoderModel(architecture.build_spec(config), torch.float32, torch.device("meta"))
+        ours = model.expected_tensors()
+        assert set(ours) == set(case["tensors"]), case["name"]
+        for name, shape in case["tensors"].items():
+            want = tuple(config.hidden_size if extent is None else extent for extent in shape)
+            got = tuple(ours[name].shape)
+            if name.endswith(("gate_proj.weight", "up_proj.weight")):
+                want = (config.intermediate_size, config.hidden_size)  # the reference leaves both extents open
+            if name.endswith("down_proj.weight"):
+                want = (config.hidden_size, config.intermediate_size)
+            assert got == want, (case["name"], name)
