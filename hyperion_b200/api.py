@@ -149,6 +149,8 @@ class Engine:
         base_options = np.asarray([pack_options(p, 0, 0) for p in per_prompt], dtype=np.int32).reshape(len(prompts), 8)
         greedy = np.asarray([p.greedy for p in per_prompt], dtype=bool)
         cache_key = np.full(len(prompts), -1, dtype=np.int64)  # the cache's key of each request once it is live
+        self._generate_calls = getattr(self, "_generate_calls", 0) + 1
+        names = [("generate", self._generate_calls, index) for index in range(len(prompts))]  # in the cache: apart from a caller's own requests
         outputs: list[list[int]] = [[] for _ in prompts]
         reasons: list[Optional[str]] = [None] * len(prompts)
 
@@ -164,8 +166,8 @@ class Engine:
 
         def free_released():
             for key in scheduler.take_released_keys().tolist():
-                if cache_key[key] >= 0 and self.cache.has(key):
-                    self.cache.free(key)
+                if cache_key[key] >= 0 and self.cache.has(names[key]):
+                    self.cache.free(names[key])
                 cache_key[key] = -1
 
         depth = 2 if lookahead else 1
@@ -175,8 +177,8 @@ class Engine:
         def launch(plan):
             nonlocal newest
             for key in plan.keys[cache_key[plan.keys] < 0].tolist():  # first portion of a prompt: the request becomes live
-                self.cache.add_request(key)
-                cache_key[key] = self.cache.keys.known(key)
+                self.cache.add_request(names[key])
+                cache_key[key] = self.cache.keys.known(names[key])
             tokens, places = plan.tokens, None
             pending = np.flatnonzero(plan.from_step >= 0)
             if len(pending):  # sampled by the plan before, still on the device
@@ -199,7 +201,7 @@ class Engine:
                                                                            host_runtime.address(lengths), host_runtime.address(slots)))
                 options[:, 7] = slots[sampled_rows]
                 extra = {"sampling_options": (options, (len(sampled_rows), 8))}
-            logits = self.runner.step_arrays(plan.keys.tolist(), np.ascontiguousarray(cache_key[plan.keys]), plan.counts, tokens, want, extra,
+            logits = self.runner.step_arrays([names[key] for key in plan.keys.tolist()], np.ascontiguousarray(cache_key[plan.keys]), plan.counts, tokens, want, extra,
                                              device_tokens=(newest[1], places) if places else None)
             if logits is None:
                 return plan, None, None
@@ -242,8 +244,8 @@ class Engine:
                     raise RuntimeError("the scheduler has requests but plans nothing")
         finally:  # whatever ended the loop, this call's requests leave the cache
             for key in np.flatnonzero(cache_key >= 0).tolist():
-                if self.cache.has(key):
-                    self.cache.free(key)
+                if self.cache.has(names[key]):
+                    self.cache.free(names[key])
         self.check()
         return (outputs, reasons) if return_reasons else outputs
 
