@@ -119,7 +119,9 @@ class Engine:
         ``sampling`` is one :class:`SamplingParams` for all prompts or one per prompt; missing fields
         take the model folder's ``generation_config.json`` defaults.  Returns the generated ids per
         prompt (with ``return_reasons`` also why each ended: ``stop``, ``length`` or a failure text).
-        ``on_token(index, token)`` is called as tokens appear.  With ``lookahead`` the next step is
+        ``on_token(index, token)`` is called as tokens appear; when it returns ``False`` that request is cancelled
+        (its pages are freed at once, its reason is ``cancelled``; the reference's scheduler cancels the same way,
+        helios/crates/helios-core/src/step_scheduler.rs:132-154).  With ``lookahead`` the next step is
         launched before the last one's ids have reached the host (it takes them on the device), so
         the device never waits for the host; ids then appear one step late, and a request that
         ends on an end-of-sequence token has run one row in vain.
@@ -159,8 +161,8 @@ class Engine:
             for key, kind, token, text in zip(keys.tolist(), kinds.tolist(), tokens.tolist(), texts):
                 if kind == 0:
                     outputs[key].append(token)
-                    if on_token is not None:
-                        on_token(key, token)
+                    if on_token is not None and on_token(key, token) is False:
+                        scheduler.cancel(key)  # the caller wants no more of this request: it ends with reason "cancelled"
                 else:
                     reasons[key] = text
 

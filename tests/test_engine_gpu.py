@@ -332,3 +332,21 @@ def test_forty_requests_through_a_small_pool_running_ahead_or_not(folders, tmp_p
     assert results[0] == results[1]
     reasons = results[0][1]
     assert reasons.count("stop") >= 5 and reasons.count("length") >= 5
+
+
+@pytest.mark.parametrize("lookahead", [False, True])
+def test_a_callback_that_returns_false_cancels_its_request(folders, lookahead):
+    from hyperion_b200.sampling import SamplingParams
+
+    config, _ = TINY["A"]
+    prompts = [random_ids(800 + i, 9 + i, config.vocab_size) for i in range(3)]
+    params = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    engine = engine_for(folders["A"], "float32", max_tokens=256, max_requests=4)
+    whole = engine.generate(prompts, params, lookahead=lookahead)
+    got, reasons = engine.generate(prompts, params, return_reasons=True, lookahead=lookahead,
+                                   on_token=lambda index, token: not (index == 1 and token == whole[1][4]))
+    stop = whole[1].index(whole[1][4]) + 1  # the token the callback refused was still delivered
+    assert got[1] == whole[1][:stop] and reasons[1] == "cancelled"
+    assert got[0] == whole[0] and got[2] == whole[2] and reasons[0] == reasons[2] == "length"
+    engine.cache.check()
+    assert not engine.cache.live_requests
