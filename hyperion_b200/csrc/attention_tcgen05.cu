@@ -452,7 +452,11 @@ EncodeTiled encode_tiled() {
     return fn;
 }
 
-constexpr size_t SMEM_BYTES = (size_t)2 * STAGES * TILE_BYTES + (size_t)HALVES * QPANEL * sizeof(bf16) + (4 * STAGES + 4) * 8 + 16;
+constexpr size_t SMEM_USED = (size_t)2 * STAGES * TILE_BYTES + (size_t)HALVES * QPANEL * sizeof(bf16) + (4 * STAGES + 4) * 8 + 16;
+// A block holds half of the SM's tensor memory, so two blocks are all an SM can serve. The launch asks for at least
+// 80 KB of shared memory so that no third block becomes resident only to wait for tensor memory: such a block of a
+// kernel launched early (as a programmatic dependent) would hold what a block of the kernel before it still needs.
+constexpr size_t SMEM_BYTES = SMEM_USED > 80 * 1024 ? SMEM_USED : 80 * 1024;
 }  // namespace
 
 // Rows of a tile (tokens x heads of a group) this kernel wants: the host planner cuts rows into tiles of
