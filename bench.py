@@ -242,6 +242,70 @@ def other_workload(name: str) -> int:
     return 0
 
 
+def reference_tables() -> int:
+    """The reference's own published tables at their shapes (docs/performance-log.md:369-384,197,243-244,407, measured on an
+    H100): decode ms per step by batch at context 512 and prefill ms by prompt length, for the 0.5B and the 7B shape."""
+    import torch
+
+    from hyperion_b200.api import Engine
+    from hyperion_b200.config import Qwen2Config
+    from hyperion_b200.engine.batch import StepEntry
+    from hyperion_b200.sampling import GREEDY, pack_options
+
+    shapes = {
+        "0.5b": (Qwen2Config(num_hidden_layers=24, hidden_size=896, intermediate_size=4864, num_attention_heads=14, num_key_value_heads=2, head_dim=64,
+                             vocab_size=151936, max_position_embeddings=32768, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=True),
+                 {"decode_ms_h100": {1: 1.502, 2: 1.747, 4: 1.771, 8: 1.806, 16: 1.918, 32: 2.219}, "prefill_ms_h100": {1024: 6.2, 4096: 23.3, 8192: 59.4, 16384: 175.5}}),
+        "7b": (model_config(28),
+               {"decode_ms_h100": {1: 6.763, 2: 6.780, 4: 6.826, 8: 7.263, 16: 7.793, 32: 8.855}, "prefill_ms_h100": {1024: 32.85, 4096: 146.36, 8192: 343.29, 16384: 916.06}}),
+    }
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, (config, published) in shapes.items():
+        engine = Engine.from_random("Qwen2ForCausalLM", config, seed=0, dtype="bfloat16", page_size=16, max_tokens=32 * 640 + 17000, max_requests=32)
+        vocab = config.vocab_size
+        prefill = {}
+        for tokens in published["prefill_ms_h100"]:
+            ids = random_prompt(tokens, tokens, vocab)
+            times = []
+            for rep in range(5):  # the first two run directly, the third is captured, the last two are replays
+                torch.cuda.synchronize()
+                start.record()
+                engine.step([StepEntry(f"p{tokens}_{rep}", ids, [tokens - 1])])
+                stop.record()
+                torch.cuda.synchronize()
+                times.append(start.elapsed_time(stop))
+                engine.finish(f"p{tokens}_{rep}")
+            prefill[tokens] = round(min(times[3:]), 3)
+        decode = {}
+        for batch in published["decode_ms_h100"]:
+            names = [f"d{batch}_{i}" for i in range(batch)]
+            for i, request in enumerate(names):
+                engine.step([StepEntry(request, random_prompt(i, 512, vocab), [])])
+            options = {"sampling_options": ([w for request in names for w in pack_options(GREEDY, 0, engine.cache.slot(request))], (batch, 8))}
+
+            def one():
+                logits = engine.runner.step([StepEntry(request, [5], [0]) for request in names], options)
+                engine.sampler.sample(logits, engine.runner.last_context.extra["sampling_options"], all_greedy=True)
+
+            for _ in range(5):
+                one()
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(32):
+                one()
+            stop.record()
+            torch.cuda.synchronize()
+            decode[batch] = round(start.elapsed_time(stop) / 32, 3)
+            for request in names:
+                engine.finish(request)
+        engine.check()
+        print(json.dumps({"workload": "reference-tables", "shape": name, "dtype": "bf16", "data": "synthetic: random weights and token ids",
+                          "decode_ms_per_step_at_context_512": decode, "prefill_ms": prefill, "published_h100": published}))
+        del engine
+        torch.cuda.empty_cache()
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -252,12 +316,15 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points, prefill and e2e")
     parser.add_argument("--only", default=None, choices=["prefill"], help="time one part alone (for profiling)")
-    parser.add_argument("--workload", default=None, choices=["mixed-1.5b", "batch-32b"],
+    parser.add_argument("--workload", default=None, choices=["mixed-1.5b", "batch-32b", "reference-tables"],
                         help="one of the other workloads instead: 128 requests with prompts of 16..4096 tokens and 256 decoded tokens "
-                             "each through generate() at the 1.5B shape, or batch 16 with prompts of 4,096 and 512 decoded tokens at the 32B shape")
+                             "each through generate() at the 1.5B shape; batch 16 with prompts of 4,096 and 512 decoded tokens at the 32B shape; "
+                             "or the reference's own published tables (decode by batch at context 512, prefill by length) at the 0.5B and 7B shapes")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    if args.workload == "reference-tables":
+        return reference_tables()
     if args.workload:
         return other_workload(args.workload)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
