@@ -173,17 +173,11 @@ struct AttnArgs {
 // token v / gc, head v % gc of the block's key/value group (gc = min(group, 128) heads per block).
 __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a,
                                                                const int* __restrict__ tiles, int gc, int head_chunks) {
-    // The swizzled tiles need a 1024-byte aligned base.  Dynamic shared memory of a kernel without static shared memory
-    // starts at such an address; the block checks it and leaves with an error status otherwise, rather than spending
-    // the kilobyte of slack that would keep a second block from fitting on the SM.
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char* base = smem_raw;
+    // The swizzled tiles need a 1024-byte aligned base; where dynamic shared memory starts is not promised, so the
+    // launch asks for 1 KB more and the base is rounded up.
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     let_next_kernel_start();
-    if (smem_u32(base) & 1023u) {
-        wait_for_previous_kernels();
-        if (threadIdx.x == 0) atomicOr(a.status, HB_STATUS_WAIT_EXPIRED);
-        return;
-    }
     unsigned char* k_ring = base;                                                   // STAGES K tiles
     unsigned char* v_ring = base + (size_t)STAGES * TILE_BYTES;                     // STAGES V tiles
     bf16* qs = reinterpret_cast<bf16*>(base + (size_t)2 * STAGES * TILE_BYTES);     // HALVES panels of 128 rows x 64
@@ -385,9 +379,14 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
             const unsigned* words = reinterpret_cast<const unsigned*>(packed);
             tmem_st16_words(lane_addr + b * BN, words);
             tmem_st16_words(lane_addr + b * BN + 16, words + 16);
+            // Every thread sees every phase of o_done go by, tile by tile: a wait by parity tells "phase j - 1 is over" only
+            // to a thread that knows phase j - 2 is (a thread two phases behind would read the parity of a later phase as
+            // "not yet" and wait for ever). Here phase j - 2 was waited for one tile ago and the product of tile j cannot
+            // start before this thread hands P(j) over, so the barrier is in phase j - 1 or j. The product of tile j - 1
+            // was issued a whole tile ago; the wait is almost always over at the first look.
+            if (j > 0 && !mbar_wait(o_done, (j - 1) & 1, failed)) { *failed = 1; ok = false; break; }
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                // O may be rescaled only between two products: the one before must be done (it is at most one tile behind)
-                if (!mbar_wait(o_done, (j - 1) & 1, failed)) { *failed = 1; ok = false; break; }
+                // O may be rescaled only between two products: the one before is done
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < D; c += 16) {
@@ -403,10 +402,7 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
-        // The waits on o_done go by phase parity, so no phase may be skipped over: this thread is known to be at most one
-        // product behind (S of the last tile was seen, so every product but the last two is over); it waits for the last
-        // two in turn.
-        if (ok && n_tiles >= 2) ok = mbar_wait(o_done, (n_tiles - 2) & 1, failed);
+        // every phase but the last was seen in the loop
         if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1, failed);
         if (!ok) *failed = 1;
         tc_fence_after();
@@ -430,7 +426,7 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
-    if (tid == 0 && *failed) atomicOr(a.status, HB_STATUS_WAIT_EXPIRED);
+    if (tid == 0 && *failed) atomicOr(a.status, HB_STATUS_WAIT_EXPIRED | HB_STATUS_IN_ATTENTION_TCGEN05);
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -452,7 +448,7 @@ EncodeTiled encode_tiled() {
     return fn;
 }
 
-constexpr size_t SMEM_USED = (size_t)2 * STAGES * TILE_BYTES + (size_t)HALVES * QPANEL * sizeof(bf16) + (4 * STAGES + 4) * 8 + 16;
+constexpr size_t SMEM_USED = 1024 + (size_t)2 * STAGES * TILE_BYTES + (size_t)HALVES * QPANEL * sizeof(bf16) + (4 * STAGES + 4) * 8 + 16;
 // A block holds half of the SM's tensor memory, so two blocks are all an SM can serve. The launch asks for at least
 // 80 KB of shared memory so that no third block becomes resident only to wait for tensor memory: such a block of a
 // kernel launched early (as a programmatic dependent) would hold what a block of the kernel before it still needs.

@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) {
                 if (!waited) wait_for_previous_kernels();  // no write to global memory before that
-                if (lane == 0) { *failed = 1; atomicOr(a.status, HB_STATUS_WAIT_EXPIRED); }
+                if (lane == 0) { *failed = 1; atomicOr(a.status, HB_STATUS_WAIT_EXPIRED | (TOKENS ? HB_STATUS_IN_ATTENTION_TMA_TOKENS : HB_STATUS_IN_ATTENTION_TMA_TILES)); }
                 break;
             }
             const int base = start + it * BN;
@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
     bool ok = true;
     for (int it = first; it < last; ++it) {
         const int s = (it - first) % STAGES, round = (it - first) / STAGES;
-        if (!mbar_wait(&full[s], round & 1, failed)) { *failed = 1; atomicOr(a.status, HB_STATUS_WAIT_EXPIRED); ok = false; break; }
+        if (!mbar_wait(&full[s], round & 1, failed)) { *failed = 1; atomicOr(a.status, HB_STATUS_WAIT_EXPIRED | (TOKENS ? HB_STATUS_IN_ATTENTION_TMA_TOKENS : HB_STATUS_IN_ATTENTION_TMA_TILES)); ok = false; break; }
         const bf16* ks = reinterpret_cast<const bf16*>(ring + (size_t)s * STAGE_BYTES);
         const int base = start + it * BN;
         if (TOKENS) {

@@ -21,7 +21,12 @@ enum : int {
     HB_STATUS_BAD_PAGE = 1,      // a block-table entry that had to be valid was negative or too large
     HB_STATUS_BAD_TOKEN = 2,     // a token id outside the vocabulary
     HB_STATUS_BAD_POSITION = 4,  // a position beyond the position table
-    HB_STATUS_WAIT_EXPIRED = 8,  // a bounded wait on a barrier ran out
+    HB_STATUS_WAIT_EXPIRED = 8,  // a bounded wait on a barrier ran out; one of the bits below says in which kernel
+    HB_STATUS_IN_GEMM_TILES = 0x100,
+    HB_STATUS_IN_GEMM_SWAPPED = 0x200,
+    HB_STATUS_IN_ATTENTION_TMA_TILES = 0x400,
+    HB_STATUS_IN_ATTENTION_TMA_TOKENS = 0x800,
+    HB_STATUS_IN_ATTENTION_TCGEN05 = 0x1000,
 };
 
 __device__ __forceinline__ float to_float(float v) { return v; }

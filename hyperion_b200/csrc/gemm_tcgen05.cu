@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(THREADS) gemm_swapped_kernel(const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && *failed) atomicOr(p.status, HB_STATUS_WAIT_EXPIRED);
+    if (threadIdx.x == 0 && *failed) atomicOr(p.status, HB_STATUS_WAIT_EXPIRED | HB_STATUS_IN_GEMM_SWAPPED);
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(L::TMEM_COLS) : "memory");
@@ -424,7 +424,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tiles_kernel(const __grid_consta
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && *failed) atomicOr(p.status, HB_STATUS_WAIT_EXPIRED);
+    if (threadIdx.x == 0 && *failed) atomicOr(p.status, HB_STATUS_WAIT_EXPIRED | HB_STATUS_IN_GEMM_TILES);
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(L::TMEM_COLS) : "memory");

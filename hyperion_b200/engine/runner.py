@@ -215,8 +215,10 @@ class ModelRunner:
             seen = self._graph_seen.get(key, 0) + 1
             self._graph_seen[key] = seen
             needed = 2 if isinstance(key[0], int) else 3
-            if seen < needed or len(self.graphs) >= MAX_GRAPHS:  # the first steps of a shape run directly (they also warm the libraries up)
+            if seen < needed:  # the first steps of a shape run directly (they also warm the libraries up)
                 return self.model.forward(context, self.cache)
+            if len(self.graphs) >= MAX_GRAPHS:  # the shape that was replayed longest ago makes room
+                self.graphs.pop(next(iter(self.graphs)))
             before = native.LAUNCHES[0]
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, pool=self._graph_pool), native.stream_bound():
@@ -226,6 +228,7 @@ class ModelRunner:
             entry = (graph, logits, native.LAUNCHES[0] - before)
             native.LAUNCHES[0] = before
             self.graphs[key] = entry
+        self.graphs[key] = self.graphs.pop(key)  # most recently used last
         graph, logits, launches = entry
         graph.replay()
         self.graph_launches += launches

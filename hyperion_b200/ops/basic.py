@@ -7,7 +7,9 @@ from .native import KernelError, check, f32, i32, is_bf16, library, ptr, require
 
 _STATUS: dict[int, torch.Tensor] = {}
 STATUS_BITS = {1: "a block-table entry that had to be valid was missing", 2: "a token id outside the vocabulary",
-               4: "a position beyond the position table", 8: "a bounded wait inside a kernel ran out"}
+               4: "a position beyond the position table", 8: "a bounded wait inside a kernel ran out",
+               0x100: "(in the tile-shaped GEMM)", 0x200: "(in the swapped GEMM)", 0x400: "(in the TMA attention, tile shape)",
+               0x800: "(in the TMA attention, token shape)", 0x1000: "(in the tcgen05 attention)"}
 
 
 def status_word(device: torch.device) -> torch.Tensor:
@@ -25,7 +27,7 @@ def raise_on_status(device: torch.device) -> None:
     if value:
         word.zero_()
         reasons = [text for bit, text in STATUS_BITS.items() if value & bit]
-        raise KernelError("a kernel reported: " + "; ".join(reasons))
+        raise KernelError(f"a kernel reported (status word {value:#x}): " + "; ".join(reasons))
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -350,3 +350,36 @@ def test_a_callback_that_returns_false_cancels_its_request(folders, lookahead):
     assert got[0] == whole[0] and got[2] == whole[2] and reasons[0] == reasons[2] == "length"
     engine.cache.check()
     assert not engine.cache.live_requests
+
+
+def test_random_traffic_through_the_bfloat16_kernels_leaves_nothing_behind():
+    """Rounds of random requests (prompts up to 1,500 tokens beside decoding requests, random budgets, portion sizes and
+    sampling) through a model wide enough for the tensor-core attention and products: no kernel reports anything, every
+    page and slot comes back, and every request ends within its budget. The kernels' hand-overs between warps are
+    timing-dependent; a traffic mix is what moves the timing."""
+    import random
+
+    from hyperion_b200.api import Engine
+    from hyperion_b200.config import Qwen2Config
+    from hyperion_b200.sampling import SamplingParams
+
+    config = Qwen2Config(num_hidden_layers=2, hidden_size=1024, intermediate_size=2816, num_attention_heads=8, num_key_value_heads=2,
+                         head_dim=128, vocab_size=3001, max_position_embeddings=4096, rope_theta=1e4, rms_norm_eps=1e-6,
+                         tie_word_embeddings=False, eos_token_ids=tuple(range(0, 3001, 53)))
+    engine = Engine.from_random("Qwen2ForCausalLM", config, seed=3, dtype="bfloat16", page_size=16, max_tokens=12000, max_requests=12)
+    rng = random.Random(2)
+    for _ in range(10):
+        count = rng.randrange(3, 16)
+        prompts = [random_ids(rng.randrange(10 ** 6), rng.randrange(1, 1500), config.vocab_size) for _ in range(count)]
+        params = [SamplingParams(temperature=rng.choice([0.0, 0.8, 1.2]), top_k=rng.choice([0, 20]), top_p=rng.choice([1.0, 0.9]),
+                                 seed=rng.randrange(10 ** 6), max_tokens=rng.randrange(1, 60)) for _ in range(count)]
+        tokens, reasons = engine.generate(prompts, params, max_batch_tokens=rng.choice([512, 2048, 8192]),
+                                          prefill_chunk_busy=rng.choice([64, 512, 2048]), return_reasons=True,
+                                          lookahead=rng.random() < 0.8)
+        engine.check()
+        engine.cache.check()
+        assert not engine.cache.live_requests and engine.cache.free_pages() == engine.cache.num_pages
+        for made, reason, wanted in zip(tokens, reasons, params):
+            assert reason in ("stop", "length")
+            assert len(made) <= wanted.max_tokens and all(0 <= t < config.vocab_size for t in made)
+            assert reason == "stop" or len(made) == wanted.max_tokens
