@@ -383,3 +383,39 @@ def test_random_traffic_through_the_bfloat16_kernels_leaves_nothing_behind():
             assert reason in ("stop", "length")
             assert len(made) <= wanted.max_tokens and all(0 <= t < config.vocab_size for t in made)
             assert reason == "stop" or len(made) == wanted.max_tokens
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pages_whose_offsets_pass_two_to_the_31_elements(dtype):
+    """A pool of 2.3 million tokens per layer (2.4 G elements) with all but its last 400 pages held by another request:
+    the request lives on pages whose element offsets do not fit 32 bits, and its logits (two prompt portions, then
+    single tokens) are the bits it gets on the first pages of a small pool."""
+    from hyperion_b200.api import Engine
+    from hyperion_b200.config import Qwen2Config
+    from hyperion_b200.engine.batch import StepEntry
+
+    config = Qwen2Config(num_hidden_layers=1, hidden_size=1024, intermediate_size=1536, num_attention_heads=8, num_key_value_heads=4,
+                         head_dim=128, vocab_size=2000, max_position_embeddings=4096, rope_theta=1e4, rms_norm_eps=1e-6,
+                         tie_word_embeddings=True, eos_token_ids=(0,))
+    ids = random_ids(5, 1500, config.vocab_size)
+    later = random_ids(6, 6, config.vocab_size)
+
+    def run(engine, held_pages):
+        if held_pages:
+            engine.cache.add_request("holder")
+            engine.cache.extend("holder", held_pages * 16)
+        rows = [engine.step([StepEntry("a", ids[:600], [599])]).float().cpu(),
+                engine.step([StepEntry("a", ids[600:], [len(ids) - 601])]).float().cpu()]
+        rows += [engine.step([StepEntry("a", [token], [0])]).float().cpu() for token in later]
+        engine.check()
+        return torch.cat(rows), engine.cache.table(0, "a")
+
+    small = Engine.from_random("Qwen2ForCausalLM", config, seed=0, dtype=dtype, page_size=16, max_tokens=4096, max_requests=4)
+    want, low = run(small, 0)
+    del small
+    torch.cuda.empty_cache()
+    pages = 2_300_000 // 16
+    big = Engine.from_random("Qwen2ForCausalLM", config, seed=0, dtype=dtype, page_size=16, max_tokens=pages * 16, max_requests=4)
+    got, high = run(big, pages - 400)
+    assert low[0] == 0 and high[0] == pages - 400 and high[0] * 16 * 2 * 4 * 128 > 2 ** 31
+    assert torch.isfinite(got).all() and torch.equal(got, want)
