@@ -86,8 +86,8 @@ class ClockSampler:
 
 def reference_arm() -> int:
     # The reference's runtime is Rust (helios) with CUDA kernels built for sm_80/sm_90; this image has
-    # no cargo or rustc, and `pip install /root/reference` finds no Python project at its root.
-    print(json.dumps({"impl": "reference", "unavailable": "the reference runtime is Rust + sm_90 CUDA; no Rust toolchain in this image and pip finds no installable project (see DESIGN.md)"}))
+    # no cargo or rustc, and pip finds no Python project at the root of the reference's tree.
+    print(json.dumps({"impl": "reference", "unavailable": "the reference runtime is Rust + sm_90 CUDA; no Rust toolchain in this image and pip finds no installable project at its root"}))
     return 0
 
 
