@@ -6,10 +6,14 @@
 // Philox4x32-10 draw keyed by the request's seed with the number of tokens sampled so far as the
 // counter: helios/crates/helios-hal/src/sampler_reference.rs:4-26; argmax takes the lowest index on
 // ties and never a NaN: helios/crates/helios-hal/kernels/elementwise.cu:948-1004).  The method differs:
-// instead of sorting candidates, the k-th largest value and the nucleus boundary are found by
-// bisection over the ordered bit patterns of the adjusted logits, each probe one pass over the row
-// with sums taken in a fixed order, so a row's token depends only on its own logits and options.
+// instead of sorting candidates, the k-th largest value and the nucleus boundary are found by a
+// radix search over the ordered bit patterns of the adjusted logits (histograms of eleven bits at a
+// time, masses as fixed-point integers), so a row's token depends only on its own logits and options.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 constexpr int THREADS = 1024;
@@ -59,15 +63,337 @@ __device__ __forceinline__ int block_sum_int(int v, int* scratch) {
     return total;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Selection by radix instead of bisection: the k-th largest key, and the key at which the mass of the larger keys
+// reaches top_p of the whole, are found eleven bits at a time from histograms in shared memory (three passes over the
+// row instead of thirty-two). Counts are integers; masses are summed as 40-bit fixed point (exp(z - max) * 2^40 as an
+// integer), so a histogram's sums do not depend on the order in which threads add to it and a row's token depends
+// only on its own logits and options.
+//
+// A row of a large vocabulary is shared by the TEAM blocks of a thread-block cluster: each takes a slice of the row,
+// builds its own histograms, and reads the others' through distributed shared memory; every block then takes the same
+// decisions from the same sums, so nothing has to be sent back.
+constexpr int BINS = 2048;
+constexpr int LIST = 1024;  // a top-k set of up to this many tokens is copied out of the row; everything after works on the copy
+constexpr int TEAM = 8;
+constexpr int TEAM_FROM_VOCAB = 8192;  // smaller rows are one block's work
+
+struct Scratch {
+    unsigned long long hist[BINS];   // weight per bin: count or fixed-point mass
+    int count[BINS];                 // elements per bin (kept for the last level of a mass search only)
+    unsigned long long warp_total[THREADS / 32];
+    float fscratch[32];
+    int iscratch[32];
+    int raw_index[LIST];
+    float raw_z[LIST];
+    int list_index[LIST];
+    float list_z[LIST];
+    int chosen_bin;
+    unsigned long long chosen_above;
+    int n_list;
+    int winner;
+    // what a block shows its team
+    float team_float;
+    int team_int;
+    int team_winner;
+    int team_fallback;
+};
+
+// The blocks that share a row. With one block nothing of the cluster is touched.
+struct Team {
+    int size, rank;
+    __device__ __forceinline__ void sync() const {
+        if (size > 1) cg::this_cluster().sync(); else __syncthreads();
+    }
+    template <class T>
+    __device__ __forceinline__ T* peer(T* mine, int r) const {
+        return size > 1 ? cg::this_cluster().map_shared_rank(mine, r) : mine;
+    }
+    __device__ __forceinline__ int sum(int block_total, Scratch& s) const {
+        if (size == 1) return block_total;
+        if (threadIdx.x == 0) s.team_int = block_total;
+        sync();
+        int total = 0;
+        for (int r = 0; r < size; ++r) total += *peer(&s.team_int, r);
+        sync();
+        return total;
+    }
+};
+
+// Which tokens are still in the race: keys above the floor, and of the keys at the floor the lowest indices.
+struct Limits {
+    bool limited;
+    unsigned key_floor;
+    int tie_limit;
+    __device__ __forceinline__ bool kept(unsigned key, int i) const {
+        return !limited || key > key_floor || (key == key_floor && i <= tie_limit);
+    }
+};
+
+// This block's slice [first, last) of the row as it lies in memory: element j is token j, its logit adjusted by
+// penalty and temperature.
+struct RowView {
+    const float* z_row;
+    const unsigned* seen;
+    float penalty, divisor;
+    int first, last;
+    __device__ __forceinline__ void get(int j, float& z, int& i) const { i = j; z = adjusted(z_row, seen, j, penalty, divisor); }
+};
+
+// A short list of (token, adjusted logit) in shared memory, ordered by token.
+struct ListView {
+    const float* z_list;
+    const int* index_list;
+    int first, last;
+    __device__ __forceinline__ void get(int j, float& z, int& i) const { i = index_list[j]; z = z_list[j]; }
+};
+
+__device__ __forceinline__ unsigned long long fixed_weight(float z, float zmax) {
+    return __float2ull_rn(expf(z - zmax) * 1099511627776.0f);  // 2^40; z <= zmax, so at most 2^40
+}
+
+// Inclusive scan over the block's threads in thread order; total = the sum over all threads.
+__device__ __forceinline__ unsigned long long block_scan(unsigned long long v, Scratch& s, unsigned long long& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+        const unsigned long long other = __shfl_up_sync(0xffffffffu, v, offset);
+        if (lane >= offset) v += other;
+    }
+    __syncthreads();
+    if (lane == 31) s.warp_total[warp] = v;
+    __syncthreads();
+    unsigned long long base = 0;
+    total = 0;
+    for (int w = 0; w < THREADS / 32; ++w) {
+        const unsigned long long t = s.warp_total[w];
+        if (w < warp) base += t;
+        total += t;
+    }
+    return v + base;
+}
+
+struct Selected {
+    unsigned key;                 // the largest key K with weight(kept, key >= K) >= need
+    unsigned long long need;      // what had to be reached
+    unsigned long long above;     // weight(kept, key > K)
+    unsigned long long at;        // weight(kept, key == K)
+    int n_at;                     // how many kept elements have key K
+};
+
+// MASS: weights are fixed-point masses, NaN is left out, need = fraction * total (at least 1 unit).
+// else: weights are 1 (NaN counts, with the lowest key), need = count_needed.
+template <bool MASS, class View>
+__device__ Selected radix_select(const View& view, const Team& team, const Limits& lim, float zmax, float fraction, int count_needed, Scratch& s) {
+    const int tid = threadIdx.x;
+    unsigned prefix = 0u;
+    unsigned long long above = 0, need = MASS ? 0ull : (unsigned long long)count_needed;
+    int decided_from = 32;  // bits [decided_from, 32) of the key are fixed
+    int bin = 0;
+    for (int level = 0; level < 3; ++level) {
+        const int width = level == 2 ? 10 : 11;
+        const int shift = decided_from - width;
+        const int bins = 1 << width;
+        for (int b = tid; b < BINS; b += THREADS) { s.hist[b] = 0ull; s.count[b] = 0; }
+        if (tid == 0) s.chosen_bin = -1;
+        __syncthreads();
+        for (int j = view.first + tid; j < view.last; j += THREADS) {
+            float z; int i;
+            view.get(j, z, i);
+            const unsigned key = ordered_key(z);
+            if (MASS && key == 0u) continue;
+            if (!lim.kept(key, i)) continue;
+            if (level > 0 && (key >> decided_from) != (prefix >> decided_from)) continue;
+            const unsigned b = (key >> shift) & (unsigned)(bins - 1);
+            const unsigned long long w = MASS ? fixed_weight(z, zmax) : 1ull;
+            if (w) atomicAdd(&s.hist[b], w);
+            if (MASS && level == 2) atomicAdd(&s.count[b], 1);  // how many share the last level's key; counts are the weights otherwise
+        }
+        team.sync();  // every block's histogram is complete
+        // thread t looks at bins (bins - 1 - 2t) and (bins - 2 - 2t): the scan runs from the largest keys down
+        unsigned long long h0 = 0, h1 = 0;
+        if (2 * tid < bins) {
+            for (int r = 0; r < team.size; ++r) {
+                const unsigned long long* theirs = team.peer(s.hist, r);
+                h0 += theirs[bins - 1 - 2 * tid];
+                h1 += theirs[bins - 2 - 2 * tid];
+            }
+        }
+        unsigned long long total;
+        const unsigned long long inclusive = block_scan(h0 + h1, s, total);
+        if (level == 0 && MASS) {
+            need = (unsigned long long)((double)fraction * (double)total);
+            if (need < 1ull) need = 1ull;
+            if (need > total) need = total;
+        }
+        const unsigned long long want = need - above;  // what this level's bins must still bring
+        const unsigned long long before = inclusive - (h0 + h1);
+        if (2 * tid < bins && before < want && want <= inclusive) {
+            if (before + h0 >= want) { s.chosen_bin = bins - 1 - 2 * tid; s.chosen_above = before; }
+            else { s.chosen_bin = bins - 2 - 2 * tid; s.chosen_above = before + h0; }
+        }
+        __syncthreads();
+        if (s.chosen_bin < 0) {
+            // the bins do not reach what is wanted (nothing kept at all): the lowest bin that holds anything, else bin 0
+            if (tid == 0) {
+                int lowest = 0;
+                unsigned long long sum = 0;
+                for (int b = bins - 1; b >= 0; --b) {
+                    unsigned long long h = 0;
+                    for (int r = 0; r < team.size; ++r) h += team.peer(s.hist, r)[b];
+                    if (h > 0ull) { lowest = b; }
+                }
+                for (int b = bins - 1; b > lowest; --b)
+                    for (int r = 0; r < team.size; ++r) sum += team.peer(s.hist, r)[b];
+                s.chosen_above = sum;
+                s.chosen_bin = lowest;
+            }
+            __syncthreads();
+        }
+        bin = s.chosen_bin;
+        above += s.chosen_above;
+        prefix |= (unsigned)bin << shift;
+        decided_from = shift;
+        if (level < 2) team.sync();  // nobody reads these histograms any more: the next level may clear them
+    }
+    Selected r;
+    r.key = prefix; r.need = need; r.above = above; r.at = 0ull; r.n_at = 0;
+    for (int t = 0; t < team.size; ++t) {
+        r.at += team.peer(s.hist, t)[bin];
+        r.n_at += team.peer(s.count, t)[bin];
+    }
+    if (!MASS) r.n_at = (int)r.at;
+    team.sync();  // the histograms may be cleared by whoever comes next
+    return r;
+}
+
+// Smallest index c such that `wanted` kept elements with this key have an index <= c (bisection over the index; only
+// needed when ties at the floor are cut, which equal logits alone bring about).
+template <class View>
+__device__ int tie_index(const View& view, const Team& team, const Limits& lim, unsigned key_at, int wanted, int vocab, Scratch& s) {
+    int a = 0, b = vocab - 1;
+    while (a < b) {
+        const int mid = (a + b) >> 1;
+        int count = 0;
+        for (int j = view.first + threadIdx.x; j < view.last; j += THREADS) {
+            float z; int i;
+            view.get(j, z, i);
+            const unsigned key = ordered_key(z);
+            count += i <= mid && key == key_at && lim.kept(key, i);
+        }
+        if (team.sum(block_sum_int(count, s.iscratch), s) >= wanted) b = mid; else a = mid + 1;
+    }
+    return a;
+}
+
+// The nucleus over what `lim` keeps, then the draw among what is left. `fallback_token` is taken when nothing has mass.
+// Every block of the team calls this; the block that holds the chosen token writes it. No block returns while another
+// may still read its shared memory.
+template <class View>
+__device__ void nucleus_and_draw(const View& view, const Team& team, Limits lim, const RowOptions& o, float zmax, int vocab, int fallback_token,
+                                 unsigned* seen, int* token_out, Scratch& s) {
+    const int tid = threadIdx.x;
+    // ---- top-p: the smallest prefix (by value descending, ties to the lower index) whose mass reaches top_p * mass
+    if (o.top_p < 1.0f) {
+        const Selected sel = radix_select<true>(view, team, lim, zmax, o.top_p, 0, s);
+        if (sel.n_at > 0) {
+            const unsigned long long w = sel.at / (unsigned long long)sel.n_at;  // equal keys have equal weights
+            long long ties_kept = sel.n_at;
+            if (w > 0ull && sel.need > sel.above) ties_kept = (long long)((sel.need - sel.above + w - 1ull) / w);
+            ties_kept = max(1ll, min((long long)sel.n_at, ties_kept));
+            int tie_limit = (lim.limited && lim.key_floor == sel.key) ? lim.tie_limit : 0x7fffffff;
+            if (ties_kept < sel.n_at) tie_limit = tie_index(view, team, lim, sel.key, (int)ties_kept, vocab, s);
+            lim.limited = true;
+            lim.key_floor = sel.key;
+            lim.tie_limit = tie_limit;
+        }
+    }
+
+    // ---- the draw: walk the kept tokens in index order until the running mass passes u * mass
+    const float u = (float)(philox_first_word(o.counter, o.seed_lo, o.seed_hi) >> 8) * (1.0f / 16777216.0f);
+    const int chunk = (view.last - view.first + THREADS - 1) / THREADS;
+    const int begin = min(view.last, view.first + tid * chunk), end = min(view.last, begin + chunk);
+    float mine = 0.f;
+    int last_kept = -1;
+    for (int j = begin; j < end; ++j) {
+        float z; int i;
+        view.get(j, z, i);
+        const unsigned key = ordered_key(z);
+        if (key != 0u && lim.kept(key, i)) { mine += expf(z - zmax); last_kept = i; }
+    }
+    // exclusive prefix over threads: inclusive scan inside the warp, then the warps in order, then the blocks in order
+    float inclusive = mine;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+        const float other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+        if ((tid & 31) >= offset) inclusive += other;
+    }
+    int fallback = last_kept;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) fallback = max(fallback, __shfl_xor_sync(0xffffffffu, fallback, offset));
+    __syncthreads();
+    if ((tid & 31) == 31) s.fscratch[tid >> 5] = inclusive;
+    if ((tid & 31) == 0) s.iscratch[tid >> 5] = fallback;
+    if (tid == 0) s.winner = 0x7fffffff;
+    __syncthreads();
+    float base = 0.f, block_total = 0.f;
+    for (int w = 0; w < THREADS / 32; ++w) {
+        if (w < (tid >> 5)) base += s.fscratch[w];
+        block_total += s.fscratch[w];
+        fallback = max(fallback, s.iscratch[w]);
+    }
+    if (tid == 0) { s.team_float = block_total; s.team_fallback = fallback; }
+    team.sync();
+    float blocks_before = 0.f, total = 0.f;
+    for (int r = 0; r < team.size; ++r) {
+        const float theirs = *team.peer(&s.team_float, r);
+        if (r < team.rank) blocks_before += theirs;
+        total += theirs;
+        fallback = max(fallback, *team.peer(&s.team_fallback, r));
+    }
+    const float target = u * total;
+    const float before = blocks_before + base + inclusive - mine;
+    if (mine > 0.f && before + mine > target) atomicMin(&s.winner, tid);
+    __syncthreads();
+    if (tid == 0) s.team_winner = s.winner == 0x7fffffff ? 0x7fffffff : team.rank * THREADS + s.winner;
+    team.sync();
+    int winner = 0x7fffffff;
+    for (int r = 0; r < team.size; ++r) winner = min(winner, *team.peer(&s.team_winner, r));
+    team.sync();  // nothing of another block's shared memory is read after this
+    if (winner == 0x7fffffff) {
+        if (team.rank == 0 && tid == 0) {
+            const int token = fallback >= 0 ? fallback : fallback_token;
+            *token_out = token;
+            if (seen) atomicOr(&seen[token >> 5], 1u << (token & 31));
+        }
+        return;
+    }
+    if (winner / THREADS == team.rank && winner % THREADS == tid) {
+        int token = -1;
+        float running = before;
+        for (int j = begin; j < end; ++j) {
+            float z; int i;
+            view.get(j, z, i);
+            const unsigned key = ordered_key(z);
+            if (key != 0u && lim.kept(key, i)) {
+                running += expf(z - zmax);
+                token = i;
+                if (running > target) break;
+            }
+        }
+        *token_out = token;
+        if (seen) atomicOr(&seen[token >> 5], 1u << (token & 31));
+    }
+}
+
 __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict__ logits, int row_stride, int vocab,
                                                          const int* __restrict__ options_raw, unsigned* __restrict__ seen_all,
-                                                         int seen_words, int* __restrict__ tokens) {
-    __shared__ float fscratch[32];
-    __shared__ int iscratch[32];
-    __shared__ float best_value[32];
-    __shared__ int best_index[32];
-    __shared__ int winner;
-    const int row = blockIdx.x, tid = threadIdx.x;
+                                                         int seen_words, int* __restrict__ tokens, int team_size) {
+    __shared__ Scratch s;
+    Team team;
+    team.size = team_size;
+    team.rank = team_size > 1 ? (int)cg::this_cluster().block_rank() : 0;
+    const int row = blockIdx.x / team_size, tid = threadIdx.x;
     const float* z_row = logits + (size_t)row * row_stride;
     RowOptions o;
     {
@@ -77,14 +403,18 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     }
     unsigned* seen = (seen_all && o.slot >= 0) ? seen_all + (size_t)o.slot * seen_words : nullptr;
     const bool greedy = !(o.temperature > 0.f);
-    const float divisor = greedy ? 1.0f : o.temperature;
-    const float penalty = greedy ? 1.0f : o.penalty;
+    const int per_block = (vocab + team.size - 1) / team.size;
+    RowView slice;
+    slice.z_row = z_row; slice.seen = seen;
+    slice.first = min(vocab, team.rank * per_block); slice.last = min(vocab, slice.first + per_block);
+    slice.divisor = greedy ? 1.0f : o.temperature;
+    slice.penalty = greedy ? 1.0f : o.penalty;
 
     // ---- maximum with the lowest index on ties; NaN never wins
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = tid; i < vocab; i += THREADS) {
-        const float z = adjusted(z_row, seen, i, penalty, divisor);
+    for (int i = slice.first + tid; i < slice.last; i += THREADS) {
+        const float z = adjusted(z_row, seen, i, slice.penalty, slice.divisor);
         if (z > bv || (bi == 0x7fffffff && z == z)) { bv = z; bi = i; }
     }
 #pragma unroll
@@ -93,17 +423,26 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
         const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
         if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
     }
-    if ((tid & 31) == 0) { best_value[tid >> 5] = bv; best_index[tid >> 5] = bi; }
+    if ((tid & 31) == 0) { s.fscratch[tid >> 5] = bv; s.iscratch[tid >> 5] = bi; }
     __syncthreads();
-    bv = best_value[0]; bi = best_index[0];
+    bv = s.fscratch[0]; bi = s.iscratch[0];
     for (int w = 1; w < THREADS / 32; ++w) {
-        const float ov = best_value[w];
-        const int oi = best_index[w];
+        const float ov = s.fscratch[w];
+        const int oi = s.iscratch[w];
         if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
     }
+    if (tid == 0) { s.team_float = bv; s.team_int = bi; }
+    team.sync();  // also: the scratch is used again below
+    bv = -INFINITY; bi = 0x7fffffff;
+    for (int r = 0; r < team.size; ++r) {
+        const float ov = *team.peer(&s.team_float, r);
+        const int oi = *team.peer(&s.team_int, r);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    }
+    team.sync();
     if (bi == 0x7fffffff) bi = 0;  // a row of NaN only
     if (greedy) {
-        if (tid == 0) {
+        if (team.rank == 0 && tid == 0) {
             tokens[row] = bi;
             if (seen) atomicOr(&seen[bi >> 5], 1u << (bi & 31));
         }
@@ -111,147 +450,61 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     }
     const float zmax = bv;
 
-    // ---- top-k: the k-th largest key by bisection, then how many ties at it are kept (lowest indices)
-    unsigned key_floor = 0u;      // keys above this are kept whole
-    int tie_limit = 0x7fffffff;   // among keys equal to key_floor, indices up to this are kept
-    bool limited = false;
+    // ---- top-k: the k-th largest key, then how many ties at it are kept (lowest indices)
+    Limits lim;
+    lim.limited = false; lim.key_floor = 0u; lim.tie_limit = 0x7fffffff;
     const int k = (o.top_k > 0 && o.top_k < vocab) ? o.top_k : 0;
     if (k) {
-        unsigned lo = 0u, hi = 0xffffffffu;  // largest K with count(key >= K) >= k
-        while (lo < hi) {
-            const unsigned mid = lo + (unsigned)(((unsigned long long)hi - lo + 1ull) >> 1);
-            int count = 0;
-            for (int i = tid; i < vocab; i += THREADS) count += ordered_key(adjusted(z_row, seen, i, penalty, divisor)) >= mid;
-            if (block_sum_int(count, iscratch) >= k) lo = mid; else hi = mid - 1u;
-        }
-        key_floor = lo;
-        int above = 0;
-        for (int i = tid; i < vocab; i += THREADS) above += ordered_key(adjusted(z_row, seen, i, penalty, divisor)) > key_floor;
-        const int ties_kept = k - block_sum_int(above, iscratch);
-        int a = 0, b = vocab - 1;  // smallest c with count(key == floor, i <= c) >= ties_kept
-        while (a < b) {
-            const int mid = (a + b) >> 1;
-            int count = 0;
-            for (int i = tid; i <= mid; i += THREADS) count += ordered_key(adjusted(z_row, seen, i, penalty, divisor)) == key_floor;
-            if (block_sum_int(count, iscratch) >= ties_kept) b = mid; else a = mid + 1;
-        }
-        tie_limit = a;
-        limited = true;
-    }
-#define HB_KEPT(key, i) (!limited || (key) > key_floor || ((key) == key_floor && (i) <= tie_limit))
-
-    // ---- mass of the kept set
-    float part = 0.f;
-    for (int i = tid; i < vocab; i += THREADS) {
-        const float z = adjusted(z_row, seen, i, penalty, divisor);
-        const unsigned key = ordered_key(z);
-        if (key != 0u && HB_KEPT(key, i)) part += expf(z - zmax);
-    }
-    float mass = block_sum(part, fscratch);
-
-    // ---- top-p: the smallest prefix (by value descending, ties to the lower index) whose mass reaches top_p * mass
-    if (o.top_p < 1.0f) {
-        const float need = o.top_p * mass;
-        unsigned lo = 0u, hi = 0xffffffffu;  // largest K with mass(kept, key >= K) >= need
-        while (lo < hi) {
-            const unsigned mid = lo + (unsigned)(((unsigned long long)hi - lo + 1ull) >> 1);
-            float p = 0.f;
-            for (int i = tid; i < vocab; i += THREADS) {
-                const float z = adjusted(z_row, seen, i, penalty, divisor);
-                const unsigned key = ordered_key(z);
-                if (key != 0u && key >= mid && HB_KEPT(key, i)) p += expf(z - zmax);
-            }
-            if (block_sum(p, fscratch) >= need) lo = mid; else hi = mid - 1u;
-        }
-        const unsigned nucleus_floor = lo;
-        float p = 0.f;
-        int ties = 0;
-        float tie_weight = 0.f;
-        for (int i = tid; i < vocab; i += THREADS) {
-            const float z = adjusted(z_row, seen, i, penalty, divisor);
-            const unsigned key = ordered_key(z);
-            if (key == 0u || !HB_KEPT(key, i)) continue;
-            if (key > nucleus_floor) p += expf(z - zmax);
-            else if (key == nucleus_floor) { ties += 1; tie_weight = expf(z - zmax); }
-        }
-        const float above = block_sum(p, fscratch);
-        const int n_ties = block_sum_int(ties, iscratch);
-        const float w = block_max(tie_weight, fscratch);
-        int ties_kept = w > 0.f ? (int)ceilf((need - above) / w) : n_ties;
-        ties_kept = max(1, min(n_ties, ties_kept));
-        int a = 0, b = vocab - 1;
-        while (a < b) {
-            const int mid = (a + b) >> 1;
-            int count = 0;
-            for (int i = tid; i <= mid; i += THREADS) {
-                const unsigned key = ordered_key(adjusted(z_row, seen, i, penalty, divisor));
-                count += key == nucleus_floor && HB_KEPT(key, i);
-            }
-            if (block_sum_int(count, iscratch) >= ties_kept) b = mid; else a = mid + 1;
-        }
-        key_floor = nucleus_floor;
-        tie_limit = a;
-        limited = true;
-        mass = above + (float)ties_kept * w;
-    }
-
-    // ---- the draw: walk the kept tokens in index order until the running mass passes u * mass
-    const float u = (float)(philox_first_word(o.counter, o.seed_lo, o.seed_hi) >> 8) * (1.0f / 16777216.0f);
-    const int chunk = (vocab + THREADS - 1) / THREADS;
-    const int begin = min(vocab, tid * chunk), end = min(vocab, begin + chunk);
-    float mine = 0.f;
-    int last_kept = -1;
-    for (int i = begin; i < end; ++i) {
-        const float z = adjusted(z_row, seen, i, penalty, divisor);
-        const unsigned key = ordered_key(z);
-        if (key != 0u && HB_KEPT(key, i)) { mine += expf(z - zmax); last_kept = i; }
-    }
-    // exclusive prefix over threads: inclusive scan inside the warp, then the warps in order
-    float inclusive = mine;
-#pragma unroll
-    for (int offset = 1; offset < 32; offset <<= 1) {
-        const float other = __shfl_up_sync(0xffffffffu, inclusive, offset);
-        if ((tid & 31) >= offset) inclusive += other;
-    }
-    __syncthreads();
-    if ((tid & 31) == 31) fscratch[tid >> 5] = inclusive;
-    if (tid == 0) winner = 0x7fffffff;
-    __syncthreads();
-    float base = 0.f;
-    for (int w = 0; w < (tid >> 5); ++w) base += fscratch[w];
-    float total = 0.f;
-    for (int w = 0; w < THREADS / 32; ++w) total += fscratch[w];
-    const float target = u * total;
-    const float before = base + inclusive - mine;
-    if (mine > 0.f && before + mine > target) atomicMin(&winner, tid);
-    __syncthreads();
-    int fallback = last_kept;
-#pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) fallback = max(fallback, __shfl_xor_sync(0xffffffffu, fallback, offset));
-    __syncthreads();
-    if ((tid & 31) == 0) iscratch[tid >> 5] = fallback;
-    __syncthreads();
-    if (tid == (winner == 0x7fffffff ? 0 : winner)) {
-        int token = -1;
-        if (winner != 0x7fffffff) {
-            float running = before;
-            for (int i = begin; i < end; ++i) {
-                const float z = adjusted(z_row, seen, i, penalty, divisor);
-                const unsigned key = ordered_key(z);
-                if (key != 0u && HB_KEPT(key, i)) {
-                    running += expf(z - zmax);
-                    token = i;
-                    if (running > target) break;
+        const Selected sel = radix_select<false>(slice, team, lim, zmax, 0.f, k, s);
+        const int ties_kept = max(1, min(sel.n_at, k - (int)sel.above));
+        Limits all_ties;
+        all_ties.limited = true; all_ties.key_floor = sel.key; all_ties.tie_limit = 0x7fffffff;
+        const int tie_limit = ties_kept < sel.n_at ? tie_index(slice, team, all_ties, sel.key, ties_kept, vocab, s) : 0x7fffffff;
+        lim.limited = true; lim.key_floor = sel.key; lim.tie_limit = tie_limit;
+        if (k <= LIST) {
+            // copy the kept tokens out (every block its own, the first block then takes them all), order them by token,
+            // and let the first block go on with the copy alone
+            if (tid == 0) s.n_list = 0;
+            __syncthreads();
+            for (int i = slice.first + tid; i < slice.last; i += THREADS) {
+                const float z = adjusted(z_row, seen, i, slice.penalty, slice.divisor);
+                if (lim.kept(ordered_key(z), i)) {
+                    const int at = atomicAdd(&s.n_list, 1);
+                    if (at < LIST) { s.raw_index[at] = i; s.raw_z[at] = z; }
                 }
             }
-        } else {
-            for (int w = 0; w < THREADS / 32; ++w) token = max(token, iscratch[w]);
-            if (token < 0) token = bi;
+            team.sync();
+            int n = min(s.n_list, LIST);
+            if (team.rank == 0) {
+                for (int r = 1; r < team.size; ++r) {
+                    const int theirs = min(*team.peer(&s.n_list, r), LIST - n);
+                    const int* their_index = team.peer(s.raw_index, r);
+                    const float* their_z = team.peer(s.raw_z, r);
+                    for (int e = tid; e < theirs; e += THREADS) { s.raw_index[n + e] = their_index[e]; s.raw_z[n + e] = their_z[e]; }
+                    n += theirs;
+                }
+            }
+            team.sync();  // the first block has everything: the others are done
+            if (team.rank != 0) return;
+            for (int a = tid; a < n; a += THREADS) {
+                const int mine = s.raw_index[a];
+                int rank = 0;
+                for (int m = 0; m < n; ++m) rank += s.raw_index[m] < mine;
+                s.list_index[rank] = mine;
+                s.list_z[rank] = s.raw_z[a];
+            }
+            __syncthreads();
+            ListView list;
+            list.z_list = s.list_z; list.index_list = s.list_index; list.first = 0; list.last = n;
+            Limits none;
+            none.limited = false; none.key_floor = 0u; none.tie_limit = 0x7fffffff;
+            Team alone;
+            alone.size = 1; alone.rank = 0;
+            nucleus_and_draw(list, alone, none, o, zmax, vocab, bi, seen, tokens + row, s);
+            return;
         }
-        tokens[row] = token;
-        if (seen) atomicOr(&seen[token >> 5], 1u << (token & 31));
     }
-#undef HB_KEPT
+    nucleus_and_draw(slice, team, lim, o, zmax, vocab, bi, seen, tokens + row, s);
 }
 
 
@@ -348,6 +601,18 @@ HB_EXPORT int hb_sample(const float* logits, int row_stride, int rows, int vocab
                         int seen_words, int* tokens, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return HB_BAD_ARGUMENT;
-    sample_kernel<<<rows, THREADS, 0, stream>>>(logits, row_stride, vocab, options, seen, seen_words, tokens);
-    return launch_status();
+    const int team = vocab >= TEAM_FROM_VOCAB ? TEAM : 1;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(rows * team);
+    config.blockDim = dim3(THREADS);
+    config.stream = stream;
+    cudaLaunchAttribute cluster[1];
+    cluster[0].id = cudaLaunchAttributeClusterDimension;
+    cluster[0].val.clusterDim.x = team;
+    cluster[0].val.clusterDim.y = 1;
+    cluster[0].val.clusterDim.z = 1;
+    config.attrs = cluster;
+    config.numAttrs = team > 1 ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&config, sample_kernel, logits, row_stride, vocab, options, seen, seen_words, tokens, team);
+    return e == cudaSuccess ? launch_status() : (int)e;
 }

@@ -333,6 +333,8 @@ def test_sampler_greedy_ties_and_nan(vocab):
     (523, dict(temperature=0.8)), (523, dict(temperature=1.3, top_k=40)), (523, dict(temperature=0.7, top_p=0.9)),
     (523, dict(temperature=1.0, top_k=50, top_p=0.5, repetition_penalty=1.3)), (152064, dict(temperature=0.8, top_k=50, top_p=0.95)),
     (152064, dict(temperature=1.0)), (1000, dict(temperature=1.0, top_k=1)),
+    (152064, dict(temperature=0.9, top_p=0.8)), (152064, dict(temperature=1.1, top_k=3000, top_p=0.9, repetition_penalty=1.1)),
+    (5000, dict(temperature=0.6, top_k=1024)), (5000, dict(temperature=0.6, top_k=1025, top_p=0.3)),
 ])
 def test_sampler_matches_the_host_rule(vocab, params):
     """The device token must be the host reference's token, or the draw must lie within float rounding
@@ -367,6 +369,46 @@ def test_sampler_matches_the_host_rule(vocab, params):
     # the chosen tokens are recorded in the per-request bitmaps
     bitmap = sampler.seen.cpu()
     assert all((int(bitmap[row, got[row] // 32]) >> (got[row] % 32)) & 1 for row in range(rows))
+
+
+@pytest.mark.parametrize("params, allowed", [
+    (dict(temperature=1.0, top_k=3), {2, 5, 9}),             # 2 and 5 stand above; of the four equal ones the lowest index completes the three
+    (dict(temperature=1.0, top_k=5), {2, 5, 9, 40, 41}),
+    (dict(temperature=1.0, top_p=0.6), {2, 5, 9}),           # masses e^2, e^2, then e^1 each: six tenths of the whole need the first tie
+    (dict(temperature=1.0, top_k=2000, top_p=0.6), {2, 5, 9}),
+    (dict(temperature=1.0, top_k=4, top_p=0.99), {2, 5, 9, 40}),
+])
+def test_sampler_cuts_ties_at_the_lowest_indices(params, allowed):
+    """Equal logits at the edge of the top-k set or of the nucleus: the ones with the lowest indices stay. Over many
+    draws every allowed token comes up and no other does."""
+    from hyperion_b200.sampling import Sampler, SamplingParams, pack_options
+
+    vocab, draws = 3000, 600
+    logits = torch.full((1, vocab), -20.0)
+    logits[0, [2, 5]] = 2.0
+    logits[0, [9, 40, 41, 2999]] = 1.0
+    sampling = SamplingParams(seed=77, **params).validated()
+    sampler = Sampler(vocab, torch.device(DEV))
+    options = torch.tensor([pack_options(sampling, step, -1) for step in range(draws)], dtype=torch.int32, device=DEV)
+    got = set(sampler.sample(logits.expand(draws, vocab).contiguous().to(DEV), options).cpu().tolist())
+    assert got == allowed
+
+
+def test_sampler_rows_of_equal_logits_and_of_nan():
+    from hyperion_b200.sampling import Sampler, SamplingParams, pack_options
+
+    vocab = 70000
+    logits = torch.zeros(3, vocab)
+    logits[1] = float("nan")
+    logits[2] = float("nan")
+    logits[2, 31] = 0.5
+    sampler = Sampler(vocab, torch.device(DEV))
+    for params in (dict(temperature=1.0, top_k=7), dict(temperature=1.0, top_p=0.0001), dict(temperature=1.0, top_k=7, top_p=0.5)):
+        sampling = SamplingParams(seed=3, **params).validated()
+        options = torch.tensor([pack_options(sampling, step, -1) for step in range(3)], dtype=torch.int32, device=DEV)
+        got = sampler.sample(logits.to(DEV), options).cpu().tolist()
+        assert 0 <= got[0] < 7, (params, got)   # equal everywhere: only the lowest indices are kept
+        assert got[1] == 0 and got[2] == 31, (params, got)
 
 
 def test_sampler_frequencies_follow_the_softmax():
