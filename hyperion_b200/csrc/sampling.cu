@@ -79,7 +79,8 @@ constexpr int TEAM = 8;
 constexpr int TEAM_FROM_VOCAB = 8192;  // smaller rows are one block's work
 
 struct Scratch {
-    unsigned long long hist[BINS];   // weight per bin: count or fixed-point mass
+    unsigned hist_lo[BINS];          // weight per bin (count or fixed-point mass), low word and high word: 32-bit adds to
+    unsigned hist_hi[BINS];          // shared memory are one instruction, 64-bit ones a compare-and-swap loop
     int count[BINS];                 // elements per bin (kept for the last level of a mass search only)
     unsigned long long warp_total[THREADS / 32];
     float fscratch[32];
@@ -173,6 +174,11 @@ __device__ __forceinline__ unsigned long long block_scan(unsigned long long v, S
     return v + base;
 }
 
+// Bin b's weight in block r of the team.
+__device__ __forceinline__ unsigned long long bin_weight(const Team& team, Scratch& s, int r, int b) {
+    return ((unsigned long long)team.peer(s.hist_hi, r)[b] << 32) + team.peer(s.hist_lo, r)[b];
+}
+
 struct Selected {
     unsigned key;                 // the largest key K with weight(kept, key >= K) >= need
     unsigned long long need;      // what had to be reached
@@ -194,7 +200,7 @@ __device__ Selected radix_select(const View& view, const Team& team, const Limit
         const int width = level == 2 ? 10 : 11;
         const int shift = decided_from - width;
         const int bins = 1 << width;
-        for (int b = tid; b < BINS; b += THREADS) { s.hist[b] = 0ull; s.count[b] = 0; }
+        for (int b = tid; b < BINS; b += THREADS) { s.hist_lo[b] = 0u; s.hist_hi[b] = 0u; s.count[b] = 0; }
         if (tid == 0) s.chosen_bin = -1;
         __syncthreads();
         for (int j = view.first + tid; j < view.last; j += THREADS) {
@@ -206,7 +212,14 @@ __device__ Selected radix_select(const View& view, const Team& team, const Limit
             if (level > 0 && (key >> decided_from) != (prefix >> decided_from)) continue;
             const unsigned b = (key >> shift) & (unsigned)(bins - 1);
             const unsigned long long w = MASS ? fixed_weight(z, zmax) : 1ull;
-            if (w) atomicAdd(&s.hist[b], w);
+            if (w) {
+                // the low word wraps exactly floor(sum / 2^32) times whatever the order of the adds; each wrap is seen by
+                // the add that caused it and carried into the high word
+                const unsigned w_lo = (unsigned)w, w_hi = (unsigned)(w >> 32);
+                const unsigned old = atomicAdd(&s.hist_lo[b], w_lo);
+                const unsigned up = w_hi + ((unsigned)(old + w_lo) < old ? 1u : 0u);
+                if (up) atomicAdd(&s.hist_hi[b], up);
+            }
             if (MASS && level == 2) atomicAdd(&s.count[b], 1);  // how many share the last level's key; counts are the weights otherwise
         }
         team.sync();  // every block's histogram is complete
@@ -214,9 +227,8 @@ __device__ Selected radix_select(const View& view, const Team& team, const Limit
         unsigned long long h0 = 0, h1 = 0;
         if (2 * tid < bins) {
             for (int r = 0; r < team.size; ++r) {
-                const unsigned long long* theirs = team.peer(s.hist, r);
-                h0 += theirs[bins - 1 - 2 * tid];
-                h1 += theirs[bins - 2 - 2 * tid];
+                h0 += bin_weight(team, s, r, bins - 1 - 2 * tid);
+                h1 += bin_weight(team, s, r, bins - 2 - 2 * tid);
             }
         }
         unsigned long long total;
@@ -240,11 +252,11 @@ __device__ Selected radix_select(const View& view, const Team& team, const Limit
                 unsigned long long sum = 0;
                 for (int b = bins - 1; b >= 0; --b) {
                     unsigned long long h = 0;
-                    for (int r = 0; r < team.size; ++r) h += team.peer(s.hist, r)[b];
+                    for (int r = 0; r < team.size; ++r) h += bin_weight(team, s, r, b);
                     if (h > 0ull) { lowest = b; }
                 }
                 for (int b = bins - 1; b > lowest; --b)
-                    for (int r = 0; r < team.size; ++r) sum += team.peer(s.hist, r)[b];
+                    for (int r = 0; r < team.size; ++r) sum += bin_weight(team, s, r, b);
                 s.chosen_above = sum;
                 s.chosen_bin = lowest;
             }
@@ -259,7 +271,7 @@ __device__ Selected radix_select(const View& view, const Team& team, const Limit
     Selected r;
     r.key = prefix; r.need = need; r.above = above; r.at = 0ull; r.n_at = 0;
     for (int t = 0; t < team.size; ++t) {
-        r.at += team.peer(s.hist, t)[bin];
+        r.at += bin_weight(team, s, t, bin);
         r.n_at += team.peer(s.count, t)[bin];
     }
     if (!MASS) r.n_at = (int)r.at;
