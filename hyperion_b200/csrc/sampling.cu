@@ -189,21 +189,27 @@ struct Selected {
 
 // MASS: weights are fixed-point masses, NaN is left out, need = fraction * total (at least 1 unit).
 // else: weights are 1 (NaN counts, with the lowest key), need = count_needed.
+// first_level_ready: the histogram of the first level stands already (the caller built it on an earlier pass).
+// levels: 3 for the exact key; 1 stops after the first eleven bits (key = those bits, at = the weight of their bin)
+// and leaves the histogram standing.
 template <bool MASS, class View>
-__device__ Selected radix_select(const View& view, const Team& team, const Limits& lim, float zmax, float fraction, int count_needed, Scratch& s) {
+__device__ Selected radix_select(const View& view, const Team& team, const Limits& lim, float zmax, float fraction, int count_needed, Scratch& s,
+                                 bool first_level_ready = false, int levels = 3) {
     const int tid = threadIdx.x;
     unsigned prefix = 0u;
     unsigned long long above = 0, need = MASS ? 0ull : (unsigned long long)count_needed;
     int decided_from = 32;  // bits [decided_from, 32) of the key are fixed
     int bin = 0;
-    for (int level = 0; level < 3; ++level) {
+    for (int level = 0; level < levels; ++level) {
         const int width = level == 2 ? 10 : 11;
         const int shift = decided_from - width;
         const int bins = 1 << width;
-        for (int b = tid; b < BINS; b += THREADS) { s.hist_lo[b] = 0u; s.hist_hi[b] = 0u; s.count[b] = 0; }
+        const bool ready = level == 0 && first_level_ready;
+        if (!ready)
+            for (int b = tid; b < BINS; b += THREADS) { s.hist_lo[b] = 0u; s.hist_hi[b] = 0u; s.count[b] = 0; }
         if (tid == 0) s.chosen_bin = -1;
         __syncthreads();
-        for (int j = view.first + tid; j < view.last; j += THREADS) {
+        for (int j = view.first + tid; j < view.last && !ready; j += THREADS) {
             float z; int i;
             view.get(j, z, i);
             const unsigned key = ordered_key(z);
@@ -266,7 +272,7 @@ __device__ Selected radix_select(const View& view, const Team& team, const Limit
         above += s.chosen_above;
         prefix |= (unsigned)bin << shift;
         decided_from = shift;
-        if (level < 2) team.sync();  // nobody reads these histograms any more: the next level may clear them
+        if (level + 1 < levels) team.sync();  // nobody reads these histograms any more: the next level may clear them
     }
     Selected r;
     r.key = prefix; r.need = need; r.above = above; r.at = 0ull; r.n_at = 0;
@@ -296,6 +302,44 @@ __device__ int tie_index(const View& view, const Team& team, const Limits& lim, 
         if (team.sum(block_sum_int(count, s.iscratch), s) >= wanted) b = mid; else a = mid + 1;
     }
     return a;
+}
+
+// Copies the tokens `lim` keeps out of the row: every block its own, the first block then takes them all and orders
+// them by token into the list. Returns their number; only the first block may go on with the list (the others are
+// done once this returns). No more than LIST tokens may be kept.
+__device__ int copy_out(const RowView& slice, const Team& team, const Limits& lim, Scratch& s) {
+    const int tid = threadIdx.x;
+    if (tid == 0) s.n_list = 0;
+    __syncthreads();
+    for (int i = slice.first + tid; i < slice.last; i += THREADS) {
+        const float z = adjusted(slice.z_row, slice.seen, i, slice.penalty, slice.divisor);
+        if (lim.kept(ordered_key(z), i)) {
+            const int at = atomicAdd(&s.n_list, 1);
+            if (at < LIST) { s.raw_index[at] = i; s.raw_z[at] = z; }
+        }
+    }
+    team.sync();
+    int n = min(s.n_list, LIST);
+    if (team.rank == 0) {
+        for (int r = 1; r < team.size; ++r) {
+            const int theirs = min(*team.peer(&s.n_list, r), LIST - n);
+            const int* their_index = team.peer(s.raw_index, r);
+            const float* their_z = team.peer(s.raw_z, r);
+            for (int e = tid; e < theirs; e += THREADS) { s.raw_index[n + e] = their_index[e]; s.raw_z[n + e] = their_z[e]; }
+            n += theirs;
+        }
+    }
+    team.sync();  // the first block has everything
+    if (team.rank != 0) return 0;
+    for (int a = tid; a < n; a += THREADS) {
+        const int mine = s.raw_index[a];
+        int rank = 0;
+        for (int m = 0; m < n; ++m) rank += s.raw_index[m] < mine;
+        s.list_index[rank] = mine;
+        s.list_z[rank] = s.raw_z[a];
+    }
+    __syncthreads();
+    return n;
 }
 
 // The nucleus over what `lim` keeps, then the draw among what is left. `fallback_token` is taken when nothing has mass.
@@ -422,12 +466,19 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     slice.divisor = greedy ? 1.0f : o.temperature;
     slice.penalty = greedy ? 1.0f : o.penalty;
 
-    // ---- maximum with the lowest index on ties; NaN never wins
+    // ---- maximum with the lowest index on ties; NaN never wins. With top-k the same pass counts the keys' first
+    // eleven bits, which need no maximum.
+    const int k = (!greedy && o.top_k > 0 && o.top_k < vocab) ? o.top_k : 0;
+    if (k) {
+        for (int b = tid; b < BINS; b += THREADS) { s.hist_lo[b] = 0u; s.hist_hi[b] = 0u; s.count[b] = 0; }
+        __syncthreads();
+    }
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = slice.first + tid; i < slice.last; i += THREADS) {
         const float z = adjusted(z_row, seen, i, slice.penalty, slice.divisor);
         if (z > bv || (bi == 0x7fffffff && z == z)) { bv = z; bi = i; }
+        if (k) atomicAdd(&s.hist_lo[ordered_key(z) >> 21], 1u);
     }
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) {
@@ -465,47 +516,37 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     // ---- top-k: the k-th largest key, then how many ties at it are kept (lowest indices)
     Limits lim;
     lim.limited = false; lim.key_floor = 0u; lim.tie_limit = 0x7fffffff;
-    const int k = (o.top_k > 0 && o.top_k < vocab) ? o.top_k : 0;
     if (k) {
-        const Selected sel = radix_select<false>(slice, team, lim, zmax, 0.f, k, s);
+        // Where the k-th largest key's first eleven bits are known and few enough tokens share them or stand above, those
+        // are copied out and the rest of the search runs on the copy.
+        const Selected coarse = radix_select<false>(slice, team, lim, zmax, 0.f, k, s, true, 1);
+        if (coarse.above + coarse.at <= (unsigned long long)LIST) {
+            Limits from_bin;
+            from_bin.limited = true; from_bin.key_floor = coarse.key; from_bin.tie_limit = 0x7fffffff;  // coarse.key: the bin's lowest key
+            const int n = copy_out(slice, team, from_bin, s);
+            if (team.rank != 0) return;
+            ListView list;
+            list.z_list = s.list_z; list.index_list = s.list_index; list.first = 0; list.last = n;
+            Team alone;
+            alone.size = 1; alone.rank = 0;
+            const Selected sel = radix_select<false>(list, alone, lim, zmax, 0.f, k, s);
+            const int ties_kept = max(1, min(sel.n_at, k - (int)sel.above));
+            Limits all_ties;
+            all_ties.limited = true; all_ties.key_floor = sel.key; all_ties.tie_limit = 0x7fffffff;
+            const int tie_limit = ties_kept < sel.n_at ? tie_index(list, alone, all_ties, sel.key, ties_kept, vocab, s) : 0x7fffffff;
+            lim.limited = true; lim.key_floor = sel.key; lim.tie_limit = tie_limit;
+            nucleus_and_draw(list, alone, lim, o, zmax, vocab, bi, seen, tokens + row, s);
+            return;
+        }
+        const Selected sel = radix_select<false>(slice, team, lim, zmax, 0.f, k, s, true);
         const int ties_kept = max(1, min(sel.n_at, k - (int)sel.above));
         Limits all_ties;
         all_ties.limited = true; all_ties.key_floor = sel.key; all_ties.tie_limit = 0x7fffffff;
         const int tie_limit = ties_kept < sel.n_at ? tie_index(slice, team, all_ties, sel.key, ties_kept, vocab, s) : 0x7fffffff;
         lim.limited = true; lim.key_floor = sel.key; lim.tie_limit = tie_limit;
         if (k <= LIST) {
-            // copy the kept tokens out (every block its own, the first block then takes them all), order them by token,
-            // and let the first block go on with the copy alone
-            if (tid == 0) s.n_list = 0;
-            __syncthreads();
-            for (int i = slice.first + tid; i < slice.last; i += THREADS) {
-                const float z = adjusted(z_row, seen, i, slice.penalty, slice.divisor);
-                if (lim.kept(ordered_key(z), i)) {
-                    const int at = atomicAdd(&s.n_list, 1);
-                    if (at < LIST) { s.raw_index[at] = i; s.raw_z[at] = z; }
-                }
-            }
-            team.sync();
-            int n = min(s.n_list, LIST);
-            if (team.rank == 0) {
-                for (int r = 1; r < team.size; ++r) {
-                    const int theirs = min(*team.peer(&s.n_list, r), LIST - n);
-                    const int* their_index = team.peer(s.raw_index, r);
-                    const float* their_z = team.peer(s.raw_z, r);
-                    for (int e = tid; e < theirs; e += THREADS) { s.raw_index[n + e] = their_index[e]; s.raw_z[n + e] = their_z[e]; }
-                    n += theirs;
-                }
-            }
-            team.sync();  // the first block has everything: the others are done
+            const int n = copy_out(slice, team, lim, s);
             if (team.rank != 0) return;
-            for (int a = tid; a < n; a += THREADS) {
-                const int mine = s.raw_index[a];
-                int rank = 0;
-                for (int m = 0; m < n; ++m) rank += s.raw_index[m] < mine;
-                s.list_index[rank] = mine;
-                s.list_z[rank] = s.raw_z[a];
-            }
-            __syncthreads();
             ListView list;
             list.z_list = s.list_z; list.index_list = s.list_index; list.first = 0; list.last = n;
             Limits none;
