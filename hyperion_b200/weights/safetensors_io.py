@@ -5,7 +5,8 @@ data_offsets}}`` (``__metadata__`` is ignored) and the payload; a tensor starts 
 ``8 + header_len + begin`` (helios/crates/helios-hal/src/weights_plan.rs:38-46).  The checks follow
 the reference's header reader (ignition/src/hyperion_ignition/compiler/weights.py:45-79): the header
 must fit the file and stay under 64 MiB, every range must lie inside the payload, ``end - begin``
-must equal the element count times the element size, and ranges must not overlap.  A model folder
+must equal the element count times the element size, ranges must not overlap, and no name may
+come twice.  A model folder
 holds either ``model.safetensors`` or a ``model.safetensors.index.json`` whose ``weight_map`` names
 bare shard files (weights.py:127-174); both at once is an error.
 """
@@ -59,6 +60,21 @@ def _numel(shape: Iterable[int]) -> int:
     return n
 
 
+class _DuplicateKey(Exception):
+    pass
+
+
+def _object_without_duplicates(pairs: list[tuple[str, object]]) -> dict:
+    """A JSON object as a dict; a name that comes twice is an error, not the last value winning
+    (the reference refuses duplicate tensor names: helios/crates/helios-hal/src/weights_plan.rs:52-90)."""
+    found: dict = {}
+    for key, value in pairs:
+        if key in found:
+            raise _DuplicateKey(key)
+        found[key] = value
+    return found
+
+
 def read_header(path: Path) -> dict[str, TensorEntry]:
     """The tensors one file declares, checked against the file's size."""
     path = Path(path)
@@ -71,9 +87,11 @@ def read_header(path: Path) -> dict[str, TensorEntry]:
         if header_len > MAX_HEADER_BYTES or 8 + header_len > size:
             raise SafetensorsError(f"{path.name}: header length {header_len} does not fit the file ({size} bytes)")
         try:
-            document = json.loads(handle.read(header_len).decode("utf-8"))
+            document = json.loads(handle.read(header_len).decode("utf-8"), object_pairs_hook=_object_without_duplicates)
         except (UnicodeDecodeError, json.JSONDecodeError) as error:
             raise SafetensorsError(f"{path.name}: header is not JSON ({error})") from None
+        except _DuplicateKey as error:
+            raise SafetensorsError(f"{path.name}: the header names {error.args[0]!r} twice") from None
     if not isinstance(document, dict):
         raise SafetensorsError(f"{path.name}: header must be a JSON object")
     payload = size - 8 - header_len

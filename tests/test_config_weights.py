@@ -162,6 +162,10 @@ def test_malformed_safetensors_are_refused(tmp_path):
     _raw_file(path, {"a": {"dtype": "Q4", "shape": [2], "data_offsets": [0, 4]}}, b"\0" * 4)
     with pytest.raises(SafetensorsError, match="unsupported dtype"):
         read_header(path)
+    twice = b'{"a":{"dtype":"BF16","shape":[2],"data_offsets":[0,4]},"a":{"dtype":"BF16","shape":[2],"data_offsets":[4,8]}}'
+    path.write_bytes(struct.pack("<Q", len(twice)) + twice + b"\0" * 8)
+    with pytest.raises(SafetensorsError, match="names 'a' twice"):
+        read_header(path)
     _raw_file(path, {"__metadata__": {"format": "pt"}, "a": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]}}, struct.pack("<f", 2.5))
     assert read_header(path)["a"].shape == (1,)
 
