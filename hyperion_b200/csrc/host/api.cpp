@@ -7,6 +7,7 @@
 #include <string>
 
 #include "cache_index.hpp"
+#include "safetensors.hpp"
 #include "scheduler.hpp"
 
 #define HB_API extern "C" __attribute__((visibility("default")))
@@ -375,5 +376,31 @@ HB_API int hb_sched_waiting_keys(const HbScheduler* s, int64_t* keys, int capaci
         std::vector<int64_t> waiting = s->scheduler.waiting_keys();
         require((int)waiting.size() <= capacity, "room for fewer waiting requests than there are");
         std::copy(waiting.begin(), waiting.end(), keys);
+    });
+}
+
+// ---------------------------------------------------------------- safetensors header
+struct HbTensorTable { hb::TensorTable table; };
+
+HB_API int hb_safetensors_open(const char* path, HbTensorTable** out) {
+    return guarded([&] {
+        require(path != nullptr && out != nullptr, "hb_safetensors_open: null argument");
+        *out = new HbTensorTable{hb::read_safetensors_header(path)};
+    });
+}
+HB_API void hb_safetensors_close(HbTensorTable* table) { delete table; }
+HB_API int hb_safetensors_count(const HbTensorTable* table) { return (int)table->table.tensors.size(); }
+HB_API int64_t hb_safetensors_payload_start(const HbTensorTable* table) { return table->table.payload_start; }
+HB_API int hb_safetensors_entry(const HbTensorTable* table, int index, const char** name, const char** dtype, int* rank, const int64_t** shape,
+                                int64_t* begin, int64_t* end) {
+    return guarded([&] {
+        require(index >= 0 && index < (int)table->table.tensors.size(), "hb_safetensors_entry: no such tensor");
+        const hb::TensorRecord& record = table->table.tensors[(size_t)index];
+        *name = record.name.c_str();
+        *dtype = record.dtype.c_str();
+        *rank = (int)record.shape.size();
+        *shape = record.shape.data();
+        *begin = record.begin;
+        *end = record.end;
     });
 }

@@ -24,6 +24,7 @@ enum Code : int {
     BAD_STEP = 4,       // a step that is refused whole
     QUEUE_FULL = 5,
     SCHEDULER_ERROR = 6,
+    BAD_FILE = 7,       // a file that is not what its name promises
 };
 
 struct Failure {

@@ -19,6 +19,7 @@ extern "C" {
 #define HB_HOST_BAD_STEP 4
 #define HB_HOST_QUEUE_FULL 5
 #define HB_HOST_SCHEDULER_ERROR 6
+#define HB_HOST_BAD_FILE 7
 
 const char* hb_host_last_error(void);
 
@@ -92,6 +93,19 @@ int hb_sched_take_events(HbScheduler* s, int capacity, int64_t* keys, int* kinds
 int hb_sched_take_released(HbScheduler* s, int capacity, int64_t* keys, int* n_released);
 int hb_sched_state(const HbScheduler* s, int* idle, int* waiting, int* running, int* reserved_pages, int* plans_in_flight);
 int hb_sched_waiting_keys(const HbScheduler* s, int64_t* keys, int capacity);
+
+/* ---- safetensors header ----
+ * Reads and checks the header of one file: it fits the file and 64 MiB, is a JSON object without a name that comes
+ * twice, every tensor has a known dtype, a shape of non-negative extents and a range inside the payload of exactly
+ * shape x element size bytes, and ranges do not overlap. "__metadata__" is skipped. */
+typedef struct HbTensorTable HbTensorTable;
+int hb_safetensors_open(const char* path, HbTensorTable** out);
+void hb_safetensors_close(HbTensorTable* table);
+int hb_safetensors_count(const HbTensorTable* table);
+int64_t hb_safetensors_payload_start(const HbTensorTable* table);
+/* name, dtype: zero-ended, owned by the table; shape: rank extents, owned by the table; begin, end: inside the payload */
+int hb_safetensors_entry(const HbTensorTable* table, int index, const char** name, const char** dtype, int* rank, const int64_t** shape,
+                         int64_t* begin, int64_t* end);
 
 #ifdef __cplusplus
 }

@@ -27,7 +27,7 @@ class QueueFull(RuntimeError):
     pass
 
 
-OK, OUT_OF_PAGES, CACHE_ERROR, BAD_ARGUMENT, BAD_STEP, QUEUE_FULL, SCHEDULER_ERROR = range(7)
+OK, OUT_OF_PAGES, CACHE_ERROR, BAD_ARGUMENT, BAD_STEP, QUEUE_FULL, SCHEDULER_ERROR, BAD_FILE = range(8)
 _ERRORS = {OUT_OF_PAGES: OutOfPages, CACHE_ERROR: CacheError, BAD_ARGUMENT: ValueError, QUEUE_FULL: QueueFull, SCHEDULER_ERROR: RuntimeError}
 
 _library = None
@@ -39,7 +39,7 @@ def library() -> ctypes.CDLL:
     if _library is None:
         lib = build.load_host()
         lib.hb_host_last_error.restype = c_char_p
-        for name in ("hb_pool_delete", "hb_cache_delete", "hb_sched_delete"):
+        for name in ("hb_pool_delete", "hb_cache_delete", "hb_sched_delete", "hb_safetensors_close"):
             getattr(lib, name).restype = None
             getattr(lib, name).argtypes = [c_void_p]
         lib.hb_pool_new.argtypes = [c_int, POINTER(c_void_p)]
@@ -78,6 +78,11 @@ def library() -> ctypes.CDLL:
         lib.hb_sched_take_released.argtypes = [c_void_p, c_int, c_void_p, I32P]
         lib.hb_sched_state.argtypes = [c_void_p, I32P, I32P, I32P, I32P, I32P]
         lib.hb_sched_waiting_keys.argtypes = [c_void_p, c_void_p, c_int]
+        lib.hb_safetensors_open.argtypes = [c_char_p, POINTER(c_void_p)]
+        lib.hb_safetensors_count.argtypes = [c_void_p]
+        lib.hb_safetensors_payload_start.argtypes = [c_void_p]
+        lib.hb_safetensors_payload_start.restype = c_int64
+        lib.hb_safetensors_entry.argtypes = [c_void_p, c_int, POINTER(c_char_p), POINTER(c_char_p), I32P, POINTER(I64P), I64P, I64P]
         _library = lib
     return _library
 
@@ -89,6 +94,24 @@ def check(code: int, errors: dict | None = None) -> None:
     message = (library().hb_host_last_error() or b"").decode("utf-8", "replace")
     kind = (errors or {}).get(code) or _ERRORS.get(code, RuntimeError)
     raise kind(message)
+
+
+def safetensors_header(path: str, error: type) -> tuple[int, list[tuple[str, str, tuple[int, ...], int, int]]]:
+    """(payload start, [(name, dtype, shape, begin, end)]) of one safetensors file, read and checked by the runtime;
+    a file that fails a check raises ``error`` with the runtime's text."""
+    lib = library()
+    table = c_void_p()
+    check(lib.hb_safetensors_open(str(path).encode("utf-8"), byref(table)), {BAD_FILE: error})
+    try:
+        entries = []
+        name, dtype, rank, shape, begin, end = c_char_p(), c_char_p(), c_int(), I64P(), c_int64(), c_int64()
+        for index in range(lib.hb_safetensors_count(table)):
+            check(lib.hb_safetensors_entry(table, index, byref(name), byref(dtype), byref(rank), byref(shape), byref(begin), byref(end)))
+            entries.append((name.value.decode("utf-8"), dtype.value.decode("ascii"), tuple(int(shape[d]) for d in range(rank.value)),
+                            int(begin.value), int(end.value)))
+        return int(lib.hb_safetensors_payload_start(table)), entries
+    finally:
+        lib.hb_safetensors_close(table)
 
 
 def ints(values, dtype=np.int32) -> np.ndarray:

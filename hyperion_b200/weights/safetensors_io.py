@@ -1,4 +1,5 @@
-"""Reading and writing the safetensors container without any helper library.
+"""Reading and writing the safetensors container without any helper library.  The header is parsed
+and checked by the C++ host runtime; this module maps the files and hands out tensors.
 
 Layout: an 8-byte little-endian header length, a JSON header ``{name: {dtype, shape,
 data_offsets}}`` (``__metadata__`` is ignored) and the payload; a tensor starts at
@@ -20,8 +21,6 @@ from pathlib import Path
 from typing import Iterable
 
 import torch
-
-MAX_HEADER_BYTES = 64 << 20
 
 _DTYPES: dict[str, torch.dtype] = {
     "BF16": torch.bfloat16,
@@ -60,66 +59,23 @@ def _numel(shape: Iterable[int]) -> int:
     return n
 
 
-class _DuplicateKey(Exception):
-    pass
-
-
-def _object_without_duplicates(pairs: list[tuple[str, object]]) -> dict:
-    """A JSON object as a dict; a name that comes twice is an error, not the last value winning
-    (the reference refuses duplicate tensor names: helios/crates/helios-hal/src/weights_plan.rs:52-90)."""
-    found: dict = {}
-    for key, value in pairs:
-        if key in found:
-            raise _DuplicateKey(key)
-        found[key] = value
-    return found
-
-
 def read_header(path: Path) -> dict[str, TensorEntry]:
-    """The tensors one file declares, checked against the file's size."""
+    """The tensors one file declares, read and checked against the file's size by the host runtime
+    (``csrc/host/safetensors.cpp``)."""
+    from .. import host as host_runtime
+
     path = Path(path)
-    size = path.stat().st_size
-    with open(path, "rb") as handle:
-        prefix = handle.read(8)
-        if len(prefix) != 8:
-            raise SafetensorsError(f"{path.name}: shorter than its 8-byte header length")
-        (header_len,) = struct.unpack("<Q", prefix)
-        if header_len > MAX_HEADER_BYTES or 8 + header_len > size:
-            raise SafetensorsError(f"{path.name}: header length {header_len} does not fit the file ({size} bytes)")
-        try:
-            document = json.loads(handle.read(header_len).decode("utf-8"), object_pairs_hook=_object_without_duplicates)
-        except (UnicodeDecodeError, json.JSONDecodeError) as error:
-            raise SafetensorsError(f"{path.name}: header is not JSON ({error})") from None
-        except _DuplicateKey as error:
-            raise SafetensorsError(f"{path.name}: the header names {error.args[0]!r} twice") from None
-    if not isinstance(document, dict):
-        raise SafetensorsError(f"{path.name}: header must be a JSON object")
-    payload = size - 8 - header_len
-    entries: dict[str, TensorEntry] = {}
-    for name, meta in document.items():
-        if name == "__metadata__":
-            continue
-        try:
-            dtype_name, shape, (begin, end) = meta["dtype"], tuple(meta["shape"]), meta["data_offsets"]
-        except (KeyError, TypeError, ValueError):
-            raise SafetensorsError(f"{path.name}: tensor {name!r} lacks dtype, shape or data_offsets") from None
-        if dtype_name not in _DTYPES:
-            raise SafetensorsError(f"{path.name}: tensor {name!r} has unsupported dtype {dtype_name!r}")
-        dtype = _DTYPES[dtype_name]
-        if any(isinstance(e, bool) or not isinstance(e, int) or e < 0 for e in shape):
-            raise SafetensorsError(f"{path.name}: tensor {name!r} has a bad shape {shape!r}")
-        if not (0 <= begin <= end <= payload):
-            raise SafetensorsError(f"{path.name}: tensor {name!r} range [{begin}, {end}) lies outside the payload ({payload} bytes)")
-        if end - begin != _numel(shape) * dtype.itemsize:
-            raise SafetensorsError(
-                f"{path.name}: tensor {name!r} holds {end - begin} bytes but shape {list(shape)} of {dtype_name} needs {_numel(shape) * dtype.itemsize}"
-            )
-        entries[name] = TensorEntry(name, dtype, shape, begin, end, path, 8 + header_len)
-    ordered = sorted(entries.values(), key=lambda e: (e.begin, e.end))
-    for before, after in zip(ordered, ordered[1:]):
-        if after.begin < before.end:
-            raise SafetensorsError(f"{path.name}: tensors {before.name!r} and {after.name!r} overlap")
-    return entries
+    if not path.is_file():
+        raise FileNotFoundError(f"{path}: no such file")
+
+    class _Refused(Exception):
+        pass
+
+    try:
+        payload_start, found = host_runtime.safetensors_header(str(path), _Refused)
+    except _Refused as refused:
+        raise SafetensorsError(f"{path.name}: {refused}") from None
+    return {name: TensorEntry(name, _DTYPES[dtype], shape, begin, end, path, payload_start) for name, dtype, shape, begin, end in found}
 
 
 def read_model_index(model_dir: Path) -> dict[str, TensorEntry]:

@@ -281,3 +281,61 @@ def test_expected_tensor_names_and_shapes_are_those_of_the_reference():
             if name.endswith("down_proj.weight"):
                 want = (config.hidden_size, config.intermediate_size)
             assert got == want, (case["name"], name)
+
+
+def test_the_native_header_reader_on_odd_but_legal_and_on_broken_headers(tmp_path):
+    """Names with escapes and non-ASCII letters, metadata of any shape, spaces anywhere, an empty tensor; then headers
+    that are not JSON, nest too deeply, or state offsets and extents that are no integers."""
+    path = tmp_path / "odd.safetensors"
+    header = ('  {"__metadata__": {"note": "a \\"quoted\\" word", "nested": [1, 2.5e3, true, null, {"k": []}]},\n'
+              ' "caf\\u00e9/\\ud83d\\ude00": {"dtype": "I32", "shape": [2, 0, 3], "data_offsets": [4, 4]},\t'
+              ' "w\u00e4": {"shape": [1], "data_offsets": [0, 4], "dtype": "F32", "extra": "ignored"}}  ').encode("utf-8")
+    path.write_bytes(struct.pack("<Q", len(header)) + header + struct.pack("<f", 1.5))
+    found = read_header(path)
+    assert set(found) == {"caf\u00e9/\U0001f600", "w\u00e4"}
+    assert found["caf\u00e9/\U0001f600"].shape == (2, 0, 3) and found["w\u00e4"].dtype == torch.float32
+    assert found["w\u00e4"].payload_start == 8 + len(header)
+
+    def refused(text: bytes, payload: bytes = b"\0" * 8) -> str:
+        path.write_bytes(struct.pack("<Q", len(text)) + text + payload)
+        with pytest.raises(SafetensorsError) as caught:
+            read_header(path)
+        return str(caught.value)
+
+    assert "not JSON" in refused(b'{"a": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]},}')
+    assert "not JSON" in refused(b'{"a": tru}')
+    assert "not JSON" in refused(b'{"a": "\x01"}')
+    assert "not JSON" in refused(b"[" * 100 + b"]" * 100)
+    assert "JSON object" in refused(b'[1, 2]')
+    assert "lacks dtype" in refused(b'{"a": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4.0]}}')
+    assert "lacks dtype" in refused(b'{"a": {"dtype": "F32", "shape": [1], "data_offsets": [0]}}')
+    assert "lacks dtype" in refused(b'{"a": 3}')
+    assert "bad shape" in refused(b'{"a": {"dtype": "F32", "shape": [true], "data_offsets": [0, 4]}}')
+    assert "bad shape" in refused(b'{"a": {"dtype": "F32", "shape": [-1], "data_offsets": [0, 4]}}')
+    assert "needs more than" in refused(b'{"a": {"dtype": "F64", "shape": [4611686018427387904, 4611686018427387904], "data_offsets": [0, 8]}}')
+    assert "outside the payload" in refused(b'{"a": {"dtype": "F32", "shape": [1], "data_offsets": [-4, 0]}}')
+    with pytest.raises(FileNotFoundError):
+        read_header(tmp_path / "missing.safetensors")
+
+
+def test_the_native_header_reader_agrees_with_a_plain_reading_of_written_files(tmp_path):
+    import random
+
+    rng = random.Random(5)
+    for case in range(20):
+        tensors = {}
+        for index in range(rng.randrange(1, 12)):
+            dtype = rng.choice([torch.bfloat16, torch.float32, torch.int32, torch.uint8, torch.int64])
+            shape = [rng.randrange(0, 5) for _ in range(rng.randrange(0, 4))]
+            tensors[f"layer.{index}.{'x' * rng.randrange(1, 40)}"] = torch.zeros(shape, dtype=dtype)
+        path = tmp_path / f"case{case}.safetensors"
+        write_file(path, tensors)
+        raw = path.read_bytes()
+        (length,) = struct.unpack("<Q", raw[:8])
+        plain = json.loads(raw[8 : 8 + length])
+        found = read_header(path)
+        assert set(found) == set(plain)
+        for name, meta in plain.items():
+            entry = found[name]
+            assert list(entry.shape) == meta["shape"] and [entry.begin, entry.end] == meta["data_offsets"]
+            assert entry.payload_start == 8 + length and entry.dtype == tensors[name].dtype
