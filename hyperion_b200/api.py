@@ -57,16 +57,6 @@ class Engine:
         num_pages = max(1, -(-max_tokens // page_size))
         vocab = model.spec.vocab_size
         users = model.cache_users() + [(SAMPLER_STATE, RequestState((Sampler.seen_words(vocab),), torch.int32))]
-        # the reference checks --max-seq-len against the device's memory before it commits the pool
-        # (helios/crates/helios-hal/src/pool_plan.rs:43-60); here the pool is refused with the numbers when it cannot fit
-        itemsize = torch.empty((), dtype=model.dtype).element_size()
-        per_token = sum(2 * need.kv_heads * need.head_dim * itemsize for _, need in users if not isinstance(need, RequestState))
-        wanted = num_pages * page_size * per_token
-        free, _ = torch.cuda.mem_get_info(model.device)
-        if wanted > free:
-            raise MemoryError(f"a cache of {num_pages * page_size} tokens needs {wanted / 2**30:.1f} GiB ({per_token} bytes per token), "
-                              f"{free / 2**30:.1f} GiB are free on {model.device} beside the weights: lower max_tokens "
-                              f"(the command line's --max-seq-len, --max-batch or --cache-tokens)")
         self.cache = CacheManager(users, page_size, num_pages, max_requests, dtype=model.dtype, device=model.device)
         self.runner = ModelRunner(model, self.cache)
         self.sampler = Sampler(vocab, model.device, seen=self.cache.state_storage(SAMPLER_STATE))
@@ -143,11 +133,12 @@ class Engine:
         scheduler = Scheduler(SchedulerConfig(
             num_pages=self.cache.num_pages, page_size=self.page_size, max_seq_len=limit,
             max_batch=min(max_batch or self.cache.max_requests, self.cache.max_requests), max_batch_tokens=max_batch_tokens,
-            prefill_chunk_busy=prefill_chunk_busy, eos_token_ids=tuple(self.defaults.eos_token_ids), max_in_flight=2 if lookahead else 1))
+            prefill_chunk_busy=prefill_chunk_busy, eos_token_ids=tuple(self.defaults.eos_token_ids), max_in_flight=2 if lookahead else 1,
+            group_windows=tuple(self.cache.group_windows)))
         # Requests are known to the scheduler by keys 0..n-1 (their order here) and to the cache by keys of its own.
-        sched_keys = [scheduler.enqueue(Request(index, prompt, params.validated())) for index, (prompt, params) in enumerate(zip(prompts, per_prompt))]
+        per_prompt = [p.validated() for p in per_prompt]  # once: an absent seed is drawn here, for the scheduler's copy and the sampler's alike
+        sched_keys = [scheduler.enqueue(Request(index, prompt, params)) for index, (prompt, params) in enumerate(zip(prompts, per_prompt))]
         assert sched_keys == list(range(len(prompts)))
-        per_prompt = [p.validated() for p in per_prompt]
         base_options = np.asarray([pack_options(p, 0, 0) for p in per_prompt], dtype=np.int32).reshape(len(prompts), 8)
         greedy = np.asarray([p.greedy for p in per_prompt], dtype=bool)
         cache_key = np.full(len(prompts), -1, dtype=np.int64)  # the cache's key of each request once it is live
@@ -175,9 +166,10 @@ class Engine:
         depth = 2 if lookahead else 1
         in_flight: deque = deque()  # (plan, pinned ids or None, event), oldest first
         newest: Optional[tuple[int, torch.Tensor]] = None  # (plan step, its sampled ids on the device)
+        launched = 0  # plans whose ids went into a ring slot: a plan that failed at launch takes none, whatever its step number
 
         def launch(plan):
-            nonlocal newest
+            nonlocal newest, launched
             for key in plan.keys[cache_key[plan.keys] < 0].tolist():  # first portion of a prompt: the request becomes live
                 self.cache.add_request(names[key])
                 cache_key[key] = self.cache.keys.known(names[key])
@@ -207,7 +199,9 @@ class Engine:
                                              device_tokens=(newest[1], places) if places else None)
             if logits is None:
                 return plan, None, None
-            ring = plan.step % depth
+            # the slot of the plan `depth` launches ago, which has been retired: at most `depth` plans are in flight, oldest first
+            ring = launched % depth
+            launched += 1
             chosen = self.sampler.sample(logits, self.runner.last_context.extra["sampling_options"],
                                          out=self._token_ring[ring, : len(sampled_rows)], all_greedy=bool(greedy[plan.keys[sampled_rows]].all()))
             newest = (plan.step, chosen)

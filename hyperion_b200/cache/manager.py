@@ -8,9 +8,11 @@ slot index per live sequence addresses fixed-size device records that are cleare
 (helios/crates/helios-hal/src/backends/hopper_sm90/session.rs:191-204,581-593).  This manager keeps
 those operations and adds two things the reference's single kind of layer never needed:
 
-* *groups*: cache users with the same needs (key/value heads, head size, window) share one pool of
-  pages and one table per request; users with other needs get a pool of their own.  One page id
-  addresses the same page in every member of its group.
+* *groups*: cache users with the same needs (the shape and type of what they keep per token, the
+  window) share one pool of pages and one table per request; users with other needs get a pool of
+  their own.  One page id addresses the same page in every member of its group.  What a user keeps
+  per token is its own business: keys and values of some heads, one latent vector, anything of a
+  fixed shape (:class:`hyperion_b200.parts.base.PagedTokens`).
 * *windows*: a group whose users only ever read the last ``window`` positions gives a page back as
   soon as every position in it has fallen out of the window, while the request lives.
 
@@ -28,7 +30,7 @@ import torch
 
 from .. import host
 from ..host import CacheError, OutOfPages
-from ..parts.base import PagedKV, RequestState
+from ..parts.base import PagedTokens, RequestState
 
 NO_PAGE = -1
 
@@ -66,9 +68,9 @@ class PagePool:
 
 @dataclass
 class PagedGroup:
-    spec: PagedKV
+    spec: PagedTokens
     users: list[int]  # schedule entries whose mixers own a cache in this group, in order
-    storage: Optional[torch.Tensor] = None  # [users, pages, 2, kv_heads, page_size, head_dim]
+    storage: Optional[torch.Tensor] = None  # [users, pages, *outer, page_size, *inner]
 
 
 @dataclass
@@ -82,7 +84,7 @@ class CacheManager:
     """Groups cache users by need, owns the tensors, and keeps pages, tables, slots and lengths in
     the host runtime's ``hb::CacheIndex`` (``csrc/host/cache_index.cpp``)."""
 
-    def __init__(self, users: Sequence[tuple[int, PagedKV | RequestState]], page_size: int, num_pages: int, max_requests: int,
+    def __init__(self, users: Sequence[tuple[int, PagedTokens | RequestState]], page_size: int, num_pages: int, max_requests: int,
                  dtype: torch.dtype = torch.float32, device: Optional[torch.device] = None):
         if page_size <= 0 or page_size & (page_size - 1):
             raise ValueError(f"page_size must be a power of two, got {page_size}")
@@ -93,7 +95,7 @@ class CacheManager:
         self.states: list[StateGroup] = []
         self._where: dict[int, tuple[str, int, int]] = {}  # schedule entry -> (kind, group, index in group)
         for entry, need in users:
-            if isinstance(need, PagedKV):
+            if isinstance(need, PagedTokens):
                 group = next((i for i, g in enumerate(self.paged) if g.spec == need), None)
                 if group is None:
                     self.paged.append(PagedGroup(need, []))
@@ -115,9 +117,18 @@ class CacheManager:
         host.check(self._lib.hb_cache_new(page_size, num_pages, max_requests, len(self.paged), host.address(windows), ctypes.byref(self._handle)))
         self.keys = host.KeyMap()
         self.device = device
+        self.dtype = dtype
         if device is not None:
+            # the reference checks --max-seq-len against the device's memory before it commits the pool
+            # (helios/crates/helios-hal/src/pool_plan.rs:43-60); here the pool is refused with the numbers when it cannot fit
+            wanted = num_pages * page_size * self.bytes_per_token()
+            if device.type == "cuda" and wanted > torch.cuda.mem_get_info(device)[0]:
+                free = torch.cuda.mem_get_info(device)[0]
+                raise MemoryError(f"a cache of {num_pages * page_size} tokens needs {wanted / 2**30:.1f} GiB ({self.bytes_per_token()} bytes per token), "
+                                  f"{free / 2**30:.1f} GiB are free on {device} beside the weights: lower max_tokens "
+                                  f"(the command line's --max-seq-len, --max-batch or --cache-tokens)")
             for g in self.paged:
-                g.storage = torch.zeros((len(g.users), num_pages, 2, g.spec.kv_heads, page_size, g.spec.head_dim), dtype=dtype, device=device)
+                g.storage = torch.zeros((len(g.users), *g.spec.storage_shape(num_pages, page_size)), dtype=g.spec.dtype or dtype, device=device)
             for s in self.states:
                 s.storage = torch.zeros((len(s.users), max_requests, *s.spec.shape), dtype=s.spec.dtype, device=device)
 
@@ -132,8 +143,18 @@ class CacheManager:
         return self._handle
 
     # ------------------------------------------------------------------ lookups
+    def has_user(self, entry: int) -> bool:
+        """Whether the schedule entry asked for a cache of its own."""
+        return entry in self._where
+
     def where(self, entry: int) -> tuple[str, int, int]:
+        """(``"paged"`` | ``"state"``, the group, the entry's index in it)."""
         return self._where[entry]
+
+    @property
+    def group_windows(self) -> list[int]:
+        """Per paged group its window (0 = it keeps every key): what the scheduler reserves pages by."""
+        return [g.spec.window for g in self.paged]
 
     def _key(self, request: Hashable) -> int:
         key = self.keys.known(request)
@@ -177,11 +198,8 @@ class CacheManager:
         return value.value
 
     def bytes_per_token(self) -> int:
-        total = 0
-        for g in self.paged:
-            itemsize = g.storage.element_size() if g.storage is not None else 2
-            total += len(g.users) * 2 * g.spec.kv_heads * g.spec.head_dim * itemsize
-        return total
+        """Bytes a token costs over all paged groups and their users."""
+        return sum(len(g.users) * g.spec.bytes_per_token(self.dtype) for g in self.paged)
 
     # ------------------------------------------------------------------ requests
     def add_request(self, request: Hashable) -> int:

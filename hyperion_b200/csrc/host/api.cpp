@@ -148,6 +148,9 @@ HB_API int hb_cache_lengths(const HbCache* cache, int n, const int64_t* keys, in
 HB_API int hb_cache_check(const HbCache* cache) {
     return guarded([&] { cache->index.check(); });
 }
+HB_API int hb_cache_worst_case_pages(int page_size, int window, int tokens, int largest_portion, int* pages) {
+    return guarded([&] { *pages = hb::CacheIndex::worst_case_pages(page_size, window, tokens, largest_portion); });
+}
 
 // ---------------------------------------------------------------- step assembly
 namespace {
@@ -272,11 +275,13 @@ HB_API int hb_plan_attention(int n_rows, const int* counts, int tokens_per_tile,
 }
 
 // ---------------------------------------------------------------- scheduler
-HB_API int hb_sched_new(int num_pages, int page_size, int max_seq_len, int max_batch, int max_batch_tokens, int prefill_chunk_busy,
-                        int max_queue, int max_in_flight, int n_eos, const int* eos, HbScheduler** out) {
+HB_API int hb_sched_new(int num_pages, int page_size, int n_groups, const int* group_windows, int max_seq_len, int max_batch, int max_batch_tokens,
+                        int prefill_chunk_busy, int max_queue, int max_in_flight, int n_eos, const int* eos, HbScheduler** out) {
     return guarded([&] {
+        if (n_groups < 0) throw hb::Failure{hb::BAD_ARGUMENT, "n_groups must not be negative"};
         hb::SchedulerConfig config;
         config.num_pages = num_pages;
+        config.group_windows.assign(group_windows, group_windows + n_groups);
         config.page_size = page_size;
         config.max_seq_len = max_seq_len;
         config.max_batch = max_batch;

@@ -83,6 +83,16 @@ int CacheIndex::first_needed_block(int group, int length) const {
     return std::max(0, length - window + 1) / page_size_;
 }
 
+int CacheIndex::worst_case_pages(int page_size, int window, int tokens, int largest_portion) {
+    if (page_size < 1 || window < 0 || tokens < 0 || largest_portion < 1) throw Failure{BAD_ARGUMENT, "worst_case_pages: bad sizes"};
+    const long long all = ((long long)tokens + page_size - 1) / page_size;
+    if (window == 0) return (int)all;
+    // before a step the table holds blocks from first_needed_block(length) on; the step adds blocks up to its last token:
+    // ceil((a + window - 1 + n) / page) - floor(a / page) <= ceil((window + n - 1) / page) + 1 for every start a
+    const long long spanned = ((long long)window + largest_portion - 1 + page_size - 1) / page_size + 1;
+    return (int)std::min(all, spanned);
+}
+
 void CacheIndex::pages_needed(int64_t key, int new_tokens, int* out) const {
     const RequestRecord& r = record(key);
     const int blocks = (r.length + new_tokens + page_size_ - 1) / page_size_;

@@ -79,6 +79,11 @@ class CacheIndex {
     void free(int64_t key);
     void check() const;
 
+    // The most pages of one group that a request of up to `tokens` tokens can hold at any moment, when no step brings it
+    // more than `largest_portion` tokens: all its blocks for a group that keeps every key (window 0), else the blocks
+    // that the window behind the next position and one portion ahead of it can touch.
+    static int worst_case_pages(int page_size, int window, int tokens, int largest_portion);
+
   private:
     RequestRecord& mutable_record(int64_t key);
     int first_needed_block(int group, int length) const;

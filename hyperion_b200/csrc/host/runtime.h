@@ -53,6 +53,8 @@ int hb_cache_free_pages(const HbCache* cache, int group, int* pages);
 int hb_cache_live(const HbCache* cache, int64_t* keys, int capacity, int* n_live);
 int hb_cache_lengths(const HbCache* cache, int n, const int64_t* keys, int* lengths, int* slots); /* -1 for unknown keys */
 int hb_cache_check(const HbCache* cache);
+/* The most pages of one group a request of `tokens` tokens can hold when no step brings it more than largest_portion tokens. */
+int hb_cache_worst_case_pages(int page_size, int window, int tokens, int largest_portion, int* pages);
 
 /* ---- step assembly ----
  * Writes the arrays every step carries, each starting at a multiple of 4 words, into out[*cursor ...]:
@@ -73,7 +75,9 @@ int hb_plan_attention(int n_rows, const int* counts, int tokens_per_tile, int to
 
 /* ---- scheduler ---- */
 typedef struct HbScheduler HbScheduler;
-int hb_sched_new(int num_pages, int page_size, int max_seq_len, int max_batch, int max_batch_tokens, int prefill_chunk_busy, int max_queue,
+/* group_windows: one entry per paged group of the cache (0 = it keeps every key); pages are reserved per group */
+int hb_sched_new(int num_pages, int page_size, int n_groups, const int* group_windows, int max_seq_len, int max_batch, int max_batch_tokens,
+                 int prefill_chunk_busy, int max_queue,
                  int max_in_flight, int n_eos, const int* eos, HbScheduler** out);
 void hb_sched_delete(HbScheduler* s);
 int hb_sched_enqueue(HbScheduler* s, int64_t key, int n_prompt, const int* prompt, int max_tokens, int ignore_eos);

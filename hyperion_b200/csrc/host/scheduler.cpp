@@ -8,20 +8,30 @@ Scheduler::Scheduler(SchedulerConfig config) : config_(std::move(config)) {
     if (config_.max_batch_tokens < 1 || config_.prefill_chunk_busy < 1 || config_.max_batch < 1)
         throw Failure{BAD_ARGUMENT, "max_batch_tokens, prefill_chunk_busy and max_batch must be at least 1"};
     if (config_.page_size < 1 || config_.max_in_flight < 1) throw Failure{BAD_ARGUMENT, "page_size and max_in_flight must be at least 1"};
+    for (int window : config_.group_windows)
+        if (window < 0) throw Failure{BAD_ARGUMENT, "a group's window must not be negative"};
 }
 
 void Scheduler::enqueue(int64_t key, std::vector<int> prompt, int max_tokens, bool ignore_eos) {
     if ((int)waiting_.size() >= config_.max_queue) throw Failure{QUEUE_FULL, std::to_string(waiting_.size()) + " requests are waiting"};
+    if (max_tokens < 1) throw Failure{BAD_ARGUMENT, "max_tokens must be at least 1"};
     if (running_.count(key)) throw Failure{BAD_ARGUMENT, "the request id is already known"};
     for (const Request& r : waiting_)
         if (r.key == key) throw Failure{BAD_ARGUMENT, "the request id is already known"};
     waiting_.push_back(Request{key, std::move(prompt), max_tokens, ignore_eos});
 }
 
+std::vector<int> Scheduler::reserved_per_group() const {
+    std::vector<int> totals(config_.group_windows.size(), 0);
+    for (const auto& item : running_)
+        for (size_t g = 0; g < totals.size(); ++g) totals[g] += item.second.reserved_pages[g];
+    return totals;
+}
+
 int Scheduler::reserved_pages() const {
-    int total = 0;
-    for (const auto& item : running_) total += item.second.reserved_pages;
-    return total;
+    int most = 0;
+    for (int total : reserved_per_group()) most = std::max(most, total);
+    return most;
 }
 
 std::vector<int64_t> Scheduler::waiting_keys() const {
@@ -32,7 +42,8 @@ std::vector<int64_t> Scheduler::waiting_keys() const {
 
 void Scheduler::admit() {
     const SchedulerConfig& c = config_;
-    int reserved = reserved_pages();
+    const size_t groups = c.group_windows.size();
+    std::vector<int> reserved = reserved_per_group(), need(groups, 0);
     while (!waiting_.empty() && (int)running_.size() < c.max_batch) {
         Request& request = waiting_.front();
         const int prompt = (int)request.prompt.size();
@@ -42,14 +53,23 @@ void Scheduler::admit() {
             waiting_.pop_front();
             continue;
         }
-        const int need = pages(std::min(prompt + request.max_tokens, c.max_seq_len));
-        if (need > c.num_pages) {
+        // the request's greatest length, in 64 bits: max_tokens may be anything up to INT_MAX
+        const int tokens = (int)std::min<long long>((long long)prompt + request.max_tokens, c.max_seq_len);
+        const int portion = std::max(1, std::min(prompt, c.max_batch_tokens));  // the largest portion a step can bring
+        int most = 0;
+        bool fits = true;
+        for (size_t g = 0; g < groups; ++g) {
+            need[g] = CacheIndex::worst_case_pages(c.page_size, c.group_windows[g], tokens, portion);
+            most = std::max(most, need[g]);
+            fits = fits && reserved[g] + need[g] <= c.num_pages;
+        }
+        if (most > c.num_pages) {
             events_.push_back(Event{request.key, EVENT_FAILED, 0,
-                                    "needs " + std::to_string(need) + " pages, the pool has " + std::to_string(c.num_pages)});
+                                    "needs " + std::to_string(most) + " pages, the pool has " + std::to_string(c.num_pages)});
             waiting_.pop_front();
             continue;
         }
-        if (reserved + need > c.num_pages) return;  // waits for running requests to finish; order is kept
+        if (!fits) return;  // waits for running requests to finish; order is kept
         Sequence s;
         s.request = std::move(request);
         s.reserved_pages = need;
@@ -57,7 +77,7 @@ void Scheduler::admit() {
         waiting_.pop_front();
         running_.emplace(key, std::move(s));
         order_.push_back(key);
-        reserved += need;
+        for (size_t g = 0; g < groups; ++g) reserved[g] += need[g];
     }
 }
 
@@ -68,11 +88,34 @@ const Plan* Scheduler::next_plan() {
     Plan plan;
     int budget = c.max_batch_tokens;
     bool decoding = false;
+    // Decode rows start at the cursor and wrap around; when the budget ends before every decoding request had its
+    // row, the next step starts behind the last one served, so that they take turns (the reference's round robin
+    // over its largest bucket, step_scheduler.rs:273-289). The plan keeps admission order among the rows it holds.
+    const size_t n = order_.size();
+    if (decode_cursor_ >= n) decode_cursor_ = 0;
+    // Prompts that wait keep up to half of the budget, so that decoding requests alone cannot shut a newcomer out.
+    long long prompt_tokens = 0;
     for (int64_t key : order_) {
-        Sequence& s = running_.at(key);
-        if (s.feed == Sequence::NONE) continue;
+        const Sequence& s = running_.at(key);
+        prompt_tokens += (long long)s.request.prompt.size() - s.fed;
+    }
+    const int decode_budget = std::max(1, budget - (int)std::min<long long>(budget / 2, prompt_tokens));
+    std::vector<size_t> chosen;
+    bool skipped = false;
+    size_t last = 0;
+    for (size_t k = 0; k < n; ++k) {
+        const size_t at = (decode_cursor_ + k) % n;
+        if (running_.at(order_[at]).feed == Sequence::NONE) continue;
         decoding = true;
-        if (budget == 0) continue;
+        if ((int)chosen.size() == decode_budget) { skipped = true; continue; }
+        chosen.push_back(at);
+        last = at;
+    }
+    decode_cursor_ = skipped ? (last + 1) % n : 0;
+    std::sort(chosen.begin(), chosen.end());
+    for (size_t at : chosen) {
+        const int64_t key = order_[at];
+        Sequence& s = running_.at(key);
         PlanRow row;
         row.key = key;
         row.sample = true;
@@ -127,7 +170,9 @@ const Plan* Scheduler::in_flight(int step) const {
 
 void Scheduler::drop(int64_t key) {
     running_.erase(key);
-    order_.erase(std::find(order_.begin(), order_.end(), key));
+    const auto found = std::find(order_.begin(), order_.end(), key);
+    if ((size_t)(found - order_.begin()) < decode_cursor_) --decode_cursor_;  // the cursor stays on the same request
+    order_.erase(found);
     released_.push_back(key);
 }
 

@@ -6,9 +6,14 @@
 // admission by worst-case reservation of pages, so pages never run out under a running request and
 // nothing is preempted (step_scheduler.rs:160-201); the oldest prompt first, with smaller portions
 // while requests are decoding (step_scheduler.rs:206-213,238-241); an end-of-sequence token ends a
-// request and is not emitted (step_scheduler.rs:364-383). Unlike the reference a step mixes decode
+// request and is not emitted (step_scheduler.rs:364-383); when more requests decode than the step's
+// token budget holds, they take turns from a cursor that moves on, so none starves
+// (step_scheduler.rs:273-289). Unlike the reference a step mixes decode
 // rows and prompt portions, and plans may be made before the results of the plans before them are
 // in: a row whose token is still on the device carries PENDING_TOKEN and names where it comes from.
+// Pages are reserved per group of the cache: a group that keeps every key costs a request the pages
+// of its whole length, a windowed group the pages its window and one portion can span, and a model
+// without paged groups costs none (CacheIndex::worst_case_pages).
 #pragma once
 #include <cstdint>
 #include <deque>
@@ -23,8 +28,9 @@ namespace hb {
 constexpr int PENDING_TOKEN = -1;
 
 struct SchedulerConfig {
-    int num_pages = 0;
+    int num_pages = 0;             // pages in the pool of every paged group
     int page_size = 1;
+    std::vector<int> group_windows{0};  // one entry per paged group of the cache: 0 = keeps every key, else its window
     int max_seq_len = 0;
     int max_batch = 64;            // most requests live at a time
     int max_batch_tokens = 2048;   // token budget of one step
@@ -72,7 +78,7 @@ class Scheduler {
     std::vector<Event> take_events();
     std::vector<int64_t> take_released();
     bool idle() const { return waiting_.empty() && running_.empty(); }
-    int reserved_pages() const;
+    int reserved_pages() const;  // of the group that has reserved most
     int waiting() const { return (int)waiting_.size(); }
     int running() const { return (int)running_.size(); }
     int plans_in_flight() const { return (int)in_flight_.size(); }
@@ -88,7 +94,7 @@ class Scheduler {
     };
     struct Sequence {
         Request request;
-        int reserved_pages = 0;
+        std::vector<int> reserved_pages;  // per paged group
         int fed = 0;              // prompt tokens already planned
         int planned_samples = 0;  // sampled rows planned so far, results in or not
         int generated = 0;        // tokens whose values are in
@@ -98,7 +104,7 @@ class Scheduler {
         bool prefilling() const { return fed < (int)request.prompt.size(); }
     };
 
-    int pages(int tokens) const { return (tokens + config_.page_size - 1) / config_.page_size; }
+    std::vector<int> reserved_per_group() const;
     void admit();
     void finish(int64_t key, const char* reason);
     void drop(int64_t key);
@@ -111,6 +117,7 @@ class Scheduler {
     std::vector<int64_t> released_;
     std::deque<Plan> in_flight_;  // oldest first
     int step_ = 0;
+    size_t decode_cursor_ = 0;  // index into order_ where the next step's decode rows start
 };
 
 }  // namespace hb

@@ -66,10 +66,17 @@ class Rows(Sequence):
 
 @dataclass
 class PagedView:
-    kv: torch.Tensor  # [pages, 2, kv_heads, page_size, head_dim] of this schedule entry
+    """What a mixer with a paged cache request is handed: its own pages and the step's block tables of its group."""
+
+    storage: torch.Tensor  # [pages, *outer, page_size, *inner] of this schedule entry (keys and values: [pages, 2, kv_heads, page_size, head_dim])
     block_table: torch.Tensor  # [rows, width] int32 on the device
     page_size: int
     group: int
+
+    @property
+    def kv(self) -> torch.Tensor:
+        """The same tensor, under the name attention parts use."""
+        return self.storage
 
 
 @dataclass

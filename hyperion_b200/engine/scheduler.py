@@ -43,6 +43,7 @@ from ..sampling.params import SamplingParams
 
 PENDING_TOKEN = -1  # stands in a plan row for a sampled token that has not reached the host yet
 EVENT_KINDS = ("token", "finished", "failed")
+MAX_TOKENS_LIMIT = 2**31 - 1
 
 
 @dataclass
@@ -63,6 +64,9 @@ class SchedulerConfig:
     max_queue: int = 1 << 16
     eos_token_ids: tuple[int, ...] = ()
     max_in_flight: int = 1  # plans that may be made before the oldest one's results are in
+    # one entry per paged group of the cache, 0 = the group keeps every key, else its window; pages are reserved per
+    # group (a windowed group costs what its window and one portion span, a model without paged groups nothing)
+    group_windows: tuple[int, ...] = (0,)
 
 
 @dataclass
@@ -108,7 +112,9 @@ class Scheduler:
         self._lib = host.library()
         self._handle = ctypes.c_void_p()
         eos = host.ints(list(config.eos_token_ids))
-        host.check(self._lib.hb_sched_new(config.num_pages, config.page_size, config.max_seq_len, config.max_batch, config.max_batch_tokens,
+        windows = host.ints(list(config.group_windows))
+        host.check(self._lib.hb_sched_new(config.num_pages, config.page_size, len(windows), host.address(windows), config.max_seq_len, config.max_batch,
+                                          config.max_batch_tokens,
                                           config.prefill_chunk_busy, config.max_queue, config.max_in_flight, len(eos), host.address(eos),
                                           ctypes.byref(self._handle)))
         self.keys = host.KeyMap()
@@ -125,6 +131,8 @@ class Scheduler:
         """Queue a request; returns the key the runtime knows it by."""
         if self.keys.known(request.id) is not None:
             raise ValueError(f"request id {request.id!r} is already known")
+        if not 0 < request.params.max_tokens <= MAX_TOKENS_LIMIT:  # the runtime takes it as a 32-bit int
+            raise ValueError(f"max_tokens must be in 1..={MAX_TOKENS_LIMIT}, got {request.params.max_tokens}")
         key = self.keys.key(request.id)
         prompt = host.ints(list(request.prompt))
         try:

@@ -67,7 +67,8 @@ def library() -> ctypes.CDLL:
         lib.hb_step_pack.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int64, POINTER(c_int64), c_void_p]
         lib.hb_step_decode_widths.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p]
         lib.hb_plan_attention.argtypes = [c_int, c_void_p, c_int, c_int, c_void_p, I32P, c_void_p, I32P]
-        lib.hb_sched_new.argtypes = [c_int] * 9 + [c_void_p, POINTER(c_void_p)]
+        lib.hb_cache_worst_case_pages.argtypes = [c_int, c_int, c_int, c_int, I32P]
+        lib.hb_sched_new.argtypes = [c_int, c_int, c_int, c_void_p] + [c_int] * 7 + [c_void_p, POINTER(c_void_p)]
         lib.hb_sched_enqueue.argtypes = [c_void_p, c_int64, c_int, c_void_p, c_int, c_int]
         lib.hb_sched_next_plan.argtypes = [c_void_p, I32P, I32P, I32P]
         lib.hb_sched_plan.argtypes = [c_void_p, c_int] + [c_void_p] * 7

@@ -15,7 +15,7 @@ import torch
 
 from ..engine.batch import PagedView, StateView, StepContext
 from ..parts import base as parts
-from ..parts.base import BuildContext, PagedKV, RequestState, WeightSpec
+from ..parts.base import BuildContext, PagedTokens, RequestState, WeightSpec
 from ..parts.spec import ModelSpec
 
 
@@ -64,10 +64,13 @@ class DecoderModel:
         """``tensors`` by full name, on the device, already checked against ``expected_tensors``."""
         for prefix, part in self._named_parts():
             part.load({name: tensors[prefix + name] for name in part.weights()})
-        if getattr(self.head, "tied", False):
-            self.head.tie(self.embedding.table)
+        if self.head.wants_shared_table():
+            table = self.embedding.shared_table()
+            if table is None:
+                raise ValueError("the head is tied to the embedding, which has no table to share")
+            self.head.use_shared_table(table)
 
-    def cache_users(self) -> list[tuple[int, PagedKV | RequestState]]:
+    def cache_users(self) -> list[tuple[int, PagedTokens | RequestState]]:
         """(schedule entry, what its mixer keeps) for every entry that owns a cache."""
         users = []
         for index, run in enumerate(self.spec.schedule):
@@ -108,7 +111,7 @@ class DecoderModel:
         return self.head.forward(x)
 
     def _cache_view(self, entry: int, step: StepContext, cache):
-        if cache is None or entry not in cache._where:
+        if cache is None or not cache.has_user(entry):
             return None
         kind, group, _ = cache.where(entry)
         if kind == "paged":

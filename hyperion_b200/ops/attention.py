@@ -14,12 +14,12 @@ import torch
 
 from .. import host as host_runtime
 from .basic import status_word
-from .native import KernelError, check, f32, i32, library, ptr, require_cuda, stream_ptr
+from .native import KernelError, check, f32, i32, library, ptr, require_cuda, sm_count, stream_ptr
 
 TOKEN_SHAPE_MAX = 4  # at most csrc/attention_tma.cu's FRESH_TOKENS: its producer fetches older keys before the kernel ahead has finished
 TILE_ROWS = 64
 KEY_TILE = 64
-TARGET_BLOCKS = 148 * 2  # two blocks of the token shape fit one SM
+BLOCKS_PER_SM = 2  # two blocks of the token shape fit one SM
 
 
 def supported(head_dim: int) -> bool:
@@ -64,12 +64,14 @@ def plan(rows, tokens_per_tile: int) -> tuple[np.ndarray, np.ndarray]:
     return tiles[: 3 * n_tiles.value], items[: n_items.value]
 
 
-def choose_splits(n_items: int, heads: int, kv_heads: int, longest_context: int) -> int:
-    """Splits of the keys for the token shape: about two blocks per SM in all, at least 3 key tiles each."""
+def choose_splits(n_items: int, heads: int, kv_heads: int, longest_context: int, sms: int | None = None) -> int:
+    """Splits of the keys for the token shape: about two blocks per SM of the device (``sms``, asked from the current
+    device when absent) in all, at least 3 key tiles each."""
     group = heads // kv_heads
     blocks = n_items * kv_heads * ((group + 15) // 16)
     key_tiles = -(-longest_context // KEY_TILE)
-    return max(1, min(TARGET_BLOCKS // max(1, blocks), key_tiles // 3, 64))
+    target = BLOCKS_PER_SM * (sms or sm_count())
+    return max(1, min(target // max(1, blocks), key_tiles // 3, 64))
 
 
 def _common(q, out, cache, block_table, token_row, positions):

@@ -14,11 +14,10 @@ from typing import Optional
 import torch
 
 from .basic import status_word
-from .native import KernelError, check, i32, library, ptr, require_cuda, stream_ptr
+from .native import KernelError, check, i32, library, ptr, require_cuda, sm_count, stream_ptr
 
 EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
 SWIGLU_BLOCK = 128  # the fused epilogue wants 128 gate rows followed by their 128 up rows, repeated
-SMS = 148
 
 
 def supported(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -42,11 +41,13 @@ def batch_tile_for(m: int) -> int:
     return 0 if m > 64 else (16 if m <= 16 else (32 if m <= 32 else 64))
 
 
-def choose_splits(n: int, k: int) -> int:
-    """Split K so that about one block per SM streams the weights; every split keeps at least 4 k-blocks."""
+def choose_splits(n: int, k: int, sms: Optional[int] = None) -> int:
+    """Split K so that about one block per SM of the device (``sms``, asked from the current device when absent) streams
+    the weights; every split keeps at least 4 k-blocks."""
+    sms = sms or sm_count()
     tiles = -(-n // 128)
     k_blocks = -(-k // 64)
-    return max(1, min(SMS // tiles if tiles < SMS else 1, k_blocks // 4, 16))
+    return max(1, min(sms // tiles if tiles < sms else 1, k_blocks // 4, 16))
 
 
 @dataclass

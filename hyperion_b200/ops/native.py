@@ -56,6 +56,18 @@ def require_cuda(*tensors: torch.Tensor | None) -> None:
             raise KernelError("the kernels run on a CUDA device only; got a tensor on " + str(tensor.device))
 
 
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Multiprocessors of the device (the current one by default), asked once per device: grids and split counts follow it."""
+    index = torch.cuda.current_device() if device is None or torch.device(device).index is None else torch.device(device).index
+    found = _sm_counts.get(index)
+    if found is None:
+        found = _sm_counts[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return found
+
+
 LAUNCHES = [0]  # launcher calls that succeeded, for reports of how much of a step is this package's own code
 
 

@@ -12,11 +12,13 @@ What a part must offer:
 ``load(tensors)``                         the tensors, on the device, in their stored element type
 ``forward(...)``                          see each base class
 
-A mixer additionally states what it keeps between steps (``cache_request``): pages of keys and
-values (:class:`PagedKV`), a record of fixed size per request (:class:`RequestState`), or nothing.
+A mixer additionally states what it keeps between steps (``cache_request``): a payload of fixed
+shape per token, kept in pages (:class:`PagedTokens`; keys and values are the case :func:`PagedKV`), a
+record of fixed size per request (:class:`RequestState`), or nothing.
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 from typing import Any, Callable, Mapping, Optional
 
@@ -33,13 +35,33 @@ class WeightSpec:
 
 
 @dataclass(frozen=True)
-class PagedKV:
-    """Keys and values per token, kept in pages. ``window`` > 0: only the last ``window`` positions
-    are ever read again, so older pages may be given back while the request lives."""
+class PagedTokens:
+    """A payload of fixed shape per token, kept in pages.  The cache manager gives the mixer a tensor
+    [pages, *outer, page_size, *inner]: a token at position p of a request lies at
+    ``[block_table[row, p // page_size], ..., p % page_size, ...]``.  ``window`` > 0: only the last
+    ``window`` positions are ever read again, so older pages are given back while the request lives.
+    ``dtype`` None: the model's activation type.  Users with equal requests share one pool of pages
+    and one block table per request."""
 
-    kv_heads: int
-    head_dim: int
+    outer: tuple[int, ...] = ()
+    inner: tuple[int, ...] = ()
     window: int = 0
+    dtype: Optional[torch.dtype] = None
+
+    @property
+    def values_per_token(self) -> int:
+        return math.prod(self.outer) * math.prod(self.inner)
+
+    def bytes_per_token(self, activation_dtype: torch.dtype) -> int:
+        return self.values_per_token * torch.empty((), dtype=self.dtype or activation_dtype).element_size()
+
+    def storage_shape(self, num_pages: int, page_size: int) -> tuple[int, ...]:
+        return (num_pages, *self.outer, page_size, *self.inner)
+
+
+def PagedKV(kv_heads: int, head_dim: int, window: int = 0) -> PagedTokens:
+    """Keys and values per token: pages of [2, kv_heads, page_size, head_dim]."""
+    return PagedTokens((2, int(kv_heads)), (int(head_dim),), int(window))
 
 
 @dataclass(frozen=True)
@@ -103,7 +125,7 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_request(self) -> PagedKV | RequestState | None:
+    def cache_request(self) -> PagedTokens | RequestState | None:
         return None
 
     def forward(self, x: torch.Tensor, step: Any, cache: Any, own_cache: bool) -> torch.Tensor:
@@ -124,10 +146,21 @@ class Embedding(Part):
         """int32 ids -> float residual stream [tokens, hidden]."""
         raise NotImplementedError
 
+    def shared_table(self) -> Optional[torch.Tensor]:
+        """The [vocab, hidden] table a tied output head may use as its matrix, or None if this embedding has none to share."""
+        return None
+
 
 class Head(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """Normalised rows -> float logits [rows, vocab]."""
+        raise NotImplementedError
+
+    def wants_shared_table(self) -> bool:
+        """True when the head owns no matrix and takes the embedding's (``use_shared_table`` is then called after loading)."""
+        return False
+
+    def use_shared_table(self, table: torch.Tensor) -> None:
         raise NotImplementedError
 
 

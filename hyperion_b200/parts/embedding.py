@@ -35,6 +35,9 @@ class TokenEmbedding(Embedding):
     def forward(self, token_ids):
         return ops.embedding(self.table, token_ids)
 
+    def shared_table(self):
+        return self.table
+
 
 class LinearHead(Head):
     def __init__(self, spec: PartSpec, build: BuildContext):
@@ -51,7 +54,12 @@ class LinearHead(Head):
         if not self.tied:
             self.weight = tensors["weight"].contiguous()
 
-    def tie(self, table: torch.Tensor) -> None:
+    def wants_shared_table(self) -> bool:
+        return self.tied
+
+    def use_shared_table(self, table: torch.Tensor) -> None:
+        if tuple(table.shape) != (self.vocab, self.hidden):
+            raise ValueError(f"the tied head wants a table of {(self.vocab, self.hidden)}, the embedding shares {tuple(table.shape)}")
         self.weight = table
 
     def kernel_modules(self):

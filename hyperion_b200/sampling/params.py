@@ -45,8 +45,8 @@ class SamplingParams:
             raise InvalidParameter("repetition_penalty", "must be positive")
         if self.temperature == 0 and self.repetition_penalty != 1.0:
             raise InvalidParameter("repetition_penalty", "is not supported with temperature 0 (greedy decoding)")
-        if isinstance(self.max_tokens, bool) or not isinstance(self.max_tokens, int) or self.max_tokens <= 0:
-            raise InvalidParameter("max_tokens", "must be a positive integer")
+        if isinstance(self.max_tokens, bool) or not isinstance(self.max_tokens, int) or not 0 < self.max_tokens < 1 << 31:
+            raise InvalidParameter("max_tokens", "must be a positive integer below 2^31")
         seed = self.seed
         if seed is None:
             seed = int.from_bytes(os.urandom(8), "little")

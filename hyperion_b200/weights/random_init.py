@@ -1,13 +1,15 @@
 """Seeded random weights: in memory for a model, or written out as a model folder.
 
 The reference has no random-weight mode; its tiny fixture is a saved default initialisation
-(scripts/gen-sharded-fixture.py:32-50).  Here every tensor is drawn from its own generator, seeded
-from the seed and the tensor's name, so a tensor's values do not depend on which other tensors
-exist: matrices and biases N(0, std), norm weights 1 + N(0, std), rounded to bfloat16.
+(scripts/gen-sharded-fixture.py:32-50).  Here every tensor is a pure function of the seed, its own
+name and the element's index (``philox_normal``): matrices and biases N(0, std), norm weights
+1 + N(0, std), rounded to bfloat16.  The device fills a tensor with a kernel and the host with numpy,
+and both give the same bits, so ``Engine.from_random(seed)`` holds the very model that
+``write_model_folder(seed)`` writes, and a tensor's values do not depend on which other tensors exist.
 """
 from __future__ import annotations
 
-import hashlib
+import ctypes
 import json
 from pathlib import Path
 from typing import Any
@@ -15,28 +17,35 @@ from typing import Any
 import torch
 
 from ..parts.base import WeightSpec
+from . import philox_normal
 from .safetensors_io import write_file
 
 
-def _tensor_seed(seed: int, name: str) -> int:
-    return int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:7], "little")
-
-
 def random_tensor(name: str, wanted: WeightSpec, seed: int, std: float, device: torch.device, dtype: torch.dtype) -> torch.Tensor:
-    generator = torch.Generator(device=device)
-    generator.manual_seed(_tensor_seed(seed, name))
+    """The tensor ``name`` of the model with this seed, made where it is wanted: by the kernel of ``csrc/random_normal.cu``
+    on a CUDA device, by numpy elsewhere; the values are the same."""
+    device = torch.device(device)
     if wanted.integer:
         return torch.zeros(wanted.shape, dtype=torch.int32, device=device)
-    # drawn in chunks so that a 1e9-element matrix never holds a float32 copy of itself
-    out = torch.empty(wanted.shape, dtype=dtype, device=device)
-    flat = out.view(-1)
-    chunk = 1 << 26
-    for start in range(0, flat.numel(), chunk):
-        part = torch.randn(min(chunk, flat.numel() - start), generator=generator, device=device, dtype=torch.float32) * std
-        if wanted.init == "one_plus_normal":
-            part += 1.0
-        flat[start : start + part.numel()] = part.to(dtype)
-    return out
+    if dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError(f"random weights are made as bfloat16 or float32, got {dtype}")
+    key = philox_normal.tensor_key(seed, name)
+    mean = 1.0 if wanted.init == "one_plus_normal" else 0.0
+    count = 1
+    for extent in wanted.shape:
+        count *= int(extent)
+    if device.type == "cuda":
+        from ..ops.native import check, library, ptr, stream_ptr
+
+        out = torch.empty(wanted.shape, dtype=dtype, device=device)
+        constants = philox_normal.constants()
+        with torch.cuda.device(device):
+            check(library("random_normal").hb_random_normal(ptr(out), int(dtype == torch.bfloat16), ctypes.c_longlong(count), ctypes.c_uint(key[0]),
+                                                            ctypes.c_uint(key[1]), ctypes.c_double(std), ctypes.c_double(mean), ctypes.byref(constants),
+                                                            stream_ptr()), "random_normal")
+        return out
+    values = torch.from_numpy(philox_normal.normal_float32(count, key, std, mean))
+    return values.to(dtype).view(wanted.shape).to(device)
 
 
 def random_tensors(model, seed: int, std: float = 0.02, stored: torch.dtype = torch.bfloat16, device=None) -> dict[str, torch.Tensor]:
@@ -57,15 +66,18 @@ def init_random(model, seed: int, std: float = 0.02) -> None:
 
 
 def write_model_folder(folder: Path, architecture: str, config: Any, seed: int, std: float = 0.02,
-                       stored: torch.dtype = torch.bfloat16) -> Path:
-    """Write ``config.json`` and ``model.safetensors`` for ``config`` with weights from ``seed``."""
+                       stored: torch.dtype = torch.bfloat16, device=None) -> Path:
+    """Write ``config.json`` and ``model.safetensors`` for ``config`` with weights from ``seed``.  ``device``: where the
+    values are made (a CUDA device when one is visible, else the host); the file is the same either way."""
     from ..models import DecoderModel, get_architecture
 
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
     entry = get_architecture(architecture)
     model = DecoderModel(entry.build_spec(config), torch.float32, torch.device("meta"))
-    tensors = random_tensors(model, seed, std, stored, device=torch.device("cpu"))
+    if device is None:
+        device = "cuda" if torch.cuda.is_available() else "cpu"
+    tensors = {name: tensor.cpu() for name, tensor in random_tensors(model, seed, std, stored, device=torch.device(device)).items()}
     with open(folder / "config.json", "w", encoding="utf-8") as handle:
         json.dump(entry.write_config(config), handle, indent=1)
     write_file(folder / "model.safetensors", tensors)

@@ -7,7 +7,9 @@ toolchain, but the repository commits a tiny random Qwen2 checkpoint
 float32 top-20 logits and logsumexp at 16 teacher-forced positions of four prompts
 (testdata/oracle/qwen2-tiny-sharded.compact.json, compared by the rule of
 helios/crates/helios-hal/src/oracle.rs:197-217).  This script copies the checkpoint's files and
-cuts the oracle down to what the test reads.
+cuts the oracle down to what the tests read: per position the float32 record and how far the
+reference's own bfloat16 run was from it there (``bf16_deviation``, the width of the tie group in
+oracle.rs:197-217), and the largest such distance over all positions (``bf16_vs_fp32``).
 
     python tests/golden/make_anchor.py /path/to/reference
 
@@ -34,9 +36,11 @@ def main(reference: Path) -> None:
     for prompt in oracle["prompts"]:
         prompts.append({"ids": prompt["ids"], "generated_ids": prompt["generated_ids"],
                         "positions": [{k: row[k] for k in ("position", "argmax", "top_ids", "top_logits", "logsumexp")}
-                                      for row in prompt["reference_fp32"]]})
+                                      for row in prompt["reference_fp32"]],
+                        "bf16_deviation": [row["top_logits"] for row in prompt["bf16_deviation"]]})
     document = {"source": "testdata/oracle/qwen2-tiny-sharded.compact.json of the reference", "format": oracle["format"],
-                "tolerance": {k: oracle["tolerance"][k] for k in ("max_abs_top_logits", "max_abs_logsumexp")}, "prompts": prompts}
+                "tolerance": {k: oracle["tolerance"][k] for k in ("max_abs_top_logits", "max_abs_logsumexp")},
+                "bf16_vs_fp32": {k: oracle["bf16_vs_fp32"][k] for k in ("top_logits", "logsumexp")}, "prompts": prompts}
     (HERE / "qwen2-tiny-oracle.json").write_text(json.dumps(document))
 
 

@@ -45,9 +45,10 @@ def make_folder(tmp: Path, name: str, std: float = WEIGHT_STD) -> Path:
     return write_model_folder(Path(tmp) / f"tiny_{name}", "Qwen2ForCausalLM", config, seed, std)
 
 
-def plain_logits(folder: Path, ids) -> np.ndarray:
+def plain_logits(folder: Path, ids, device: str = "cpu") -> np.ndarray:
+    """The plain implementation's float64 logits of one whole sequence; ``device`` is where torch does that arithmetic."""
     config, weights = qwen2_plain.read_model_folder(folder)
-    return qwen2_plain.forward(config, weights, list(ids)).numpy()
+    return qwen2_plain.forward(config, weights, list(ids), device=device).cpu().numpy()
 
 
 def random_ids(seed: int, count: int, vocab: int) -> list[int]:
@@ -55,13 +56,16 @@ def random_ids(seed: int, count: int, vocab: int) -> list[int]:
     return torch.randint(0, vocab, (count,), generator=generator).tolist()
 
 
-def run_trace(folder: Path, dtype: str, steps: list[dict], out: Path, max_tokens: int, page_size: int = 16, env: dict | None = None) -> dict[int, np.ndarray]:
+def run_trace(folder: Path, dtype: str, steps: list[dict], out: Path, max_tokens: int, page_size: int = 16, env: dict | None = None,
+              pages_log: Path | None = None) -> dict[int, np.ndarray]:
     """Feed ``steps`` to bin/trace_run and read back the logits of every step that wanted some."""
     out = Path(out)
     out.mkdir(parents=True, exist_ok=True)
     text = "".join(json.dumps(step) + "\n" for step in steps)
     command = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
                "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
+    if pages_log is not None:
+        command += ["--pages-log", str(pages_log)]
     done = subprocess.run(command, input=text, capture_output=True, text=True, timeout=900, env={**os.environ, **(env or {})})
     assert done.returncode == 0, f"trace_run failed:\n{done.stdout[-2000:]}\n{done.stderr[-4000:]}"
     finished = [line for line in done.stdout.splitlines() if line.startswith("done ")]
@@ -99,3 +103,42 @@ def compare_steps(steps: list[dict], results: dict[int, np.ndarray], reference: 
         for request in step.get("end", ()):
             fed.pop(request, None)
     return worst
+
+
+def logits_by_position(steps: list[dict], results: dict[int, np.ndarray]) -> dict[tuple[str, int], np.ndarray]:
+    """{(request, position): its logits row} of a replayed trace."""
+    fed: dict[str, int] = {}
+    rows = {}
+    for step in steps:
+        row = 0
+        for entry in step["entries"]:
+            start = fed.get(entry["id"], 0)
+            for index in entry.get("want", ()):
+                rows[(entry["id"], start + index)] = results[step["step"]][row]
+                row += 1
+            fed[entry["id"]] = start + len(entry["tokens"])
+        for request in step.get("end", ()):
+            fed.pop(request, None)
+    return rows
+
+
+def check_pages_log(path: Path, steps: list[dict], pool_pages: int) -> dict:
+    """Replays a page log: no page is ever in two tables, a page given back was held by the request that gives it,
+    nothing is held at the end.  Returns how many pages changed owner."""
+    held: dict[tuple[int, int], str] = {}  # (group, page) -> request
+    last_owner: dict[tuple[int, int], str] = {}
+    handed_on = 0
+    records = [json.loads(line) for line in Path(path).read_text().splitlines()]
+    assert [r["step"] for r in records] == [s["step"] for s in steps]
+    for record in records:
+        for request, group, block, page in record["taken"]:
+            assert 0 <= page < pool_pages and (group, page) not in held, f"step {record['step']}: page {page} of group {group} is held twice"
+            held[(group, page)] = request
+            if last_owner.get((group, page), request) != request:
+                handed_on += 1
+        for request, group, block, page in record["returned"]:
+            assert held.get((group, page)) == request, f"step {record['step']}: {request} gives back page {page} it does not hold"
+            del held[(group, page)]
+            last_owner[(group, page)] = request
+    assert not held, f"pages still held at the end: {held}"
+    return {"handed_on": handed_on, "pages_used": len(last_owner)}

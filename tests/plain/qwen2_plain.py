@@ -85,7 +85,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 def rope_tables(positions: torch.Tensor, head_dim: int, theta: float, dtype=torch.float64) -> tuple[torch.Tensor, torch.Tensor]:
     """cos/sin of position * theta^(-2i/d), i < d/2, computed in float64
     (helios/crates/helios-hal/src/reference.rs:71-87)."""
-    i = torch.arange(head_dim // 2, dtype=torch.float64)
+    i = torch.arange(head_dim // 2, dtype=torch.float64, device=positions.device)
     inv_freq = theta ** (-2.0 * i / head_dim)
     angle = positions.to(torch.float64)[:, None] * inv_freq[None, :]
     return angle.cos().to(dtype), angle.sin().to(dtype)
@@ -149,14 +149,16 @@ def decoder_layer(h: torch.Tensor, w: dict[str, torch.Tensor], layer: int, d: di
     return h + swiglu_mlp(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
 
 
-def forward(config: dict, weights: dict[str, torch.Tensor], ids, dtype=torch.float64) -> torch.Tensor:
+def forward(config: dict, weights: dict[str, torch.Tensor], ids, dtype=torch.float64, device="cpu") -> torch.Tensor:
     """Logits [tokens, vocab] of one whole sequence starting at position 0: embedding, the layers,
     final norm, LM head (lm_head.weight, or the embedding table when tied:
-    helios/crates/helios-hal/src/backends/hopper_sm90/forward.rs:45-51; session.rs:807-810)."""
+    helios/crates/helios-hal/src/backends/hopper_sm90/forward.rs:45-51; session.rs:807-810).
+    ``device``: where torch does this arithmetic (the CPU, or a GPU for models of real widths: the
+    same functions in the same 64-bit type)."""
     d = dims(config)
-    w = {name: tensor.to(dtype) for name, tensor in weights.items() if tensor.is_floating_point()}
-    ids = torch.as_tensor(ids, dtype=torch.long)
-    positions = torch.arange(ids.numel())
+    w = {name: tensor.to(device=device, dtype=dtype) for name, tensor in weights.items() if tensor.is_floating_point()}
+    ids = torch.as_tensor(ids, dtype=torch.long, device=device)
+    positions = torch.arange(ids.numel(), device=device)
     h = embedding(w["model.embed_tokens.weight"], ids)
     for layer in range(d["layers"]):
         h = decoder_layer(h, w, layer, d, positions)

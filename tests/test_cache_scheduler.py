@@ -503,3 +503,130 @@ def test_enqueue_refuses_a_known_id_and_a_full_queue():
         s.enqueue(Request("c", [1], params(1)))
     drive(s)
     s.enqueue(Request("a", [3], params(1)))  # a finished: its name may come again
+
+
+# ---------------------------------------------------------------------- sizes at the edge, turns, and groups of the cache
+def test_a_huge_max_tokens_is_reserved_in_64_bits_and_capped_by_the_context():
+    """prompt + max_tokens passes 2^31: the need is the context limit's, never negative, and the next request still waits."""
+    s = Scheduler(SchedulerConfig(num_pages=8, page_size=4, max_seq_len=32, max_batch_tokens=64))
+    s.enqueue(Request("big", list(range(6)), params(2**31 - 1)))
+    s.enqueue(Request("next", list(range(6)), params(100000)))
+    plan = s.next_plan()
+    assert [r.request for r in plan.rows] == ["big"]
+    assert s.reserved_pages == 8 and len(s.waiting) == 1  # 32 tokens of context = 8 pages: the pool is spoken for
+    with pytest.raises(Exception, match="max_tokens"):
+        SamplingParams(max_tokens=2**31).validated()
+    with pytest.raises(ValueError, match="max_tokens"):
+        s.enqueue(Request("over", [1], SamplingParams(temperature=0.0, max_tokens=2**31)))  # not validated by the caller
+
+
+def test_more_decoding_requests_than_the_budget_take_turns():
+    """6 requests decode under a budget of 4 tokens: nobody waits longer than one step, prompts that wait keep half of the
+    budget, and a second run repeats the plans (the reference's round robin, helios/crates/helios-core/src/step_scheduler.rs:273-289)."""
+    def run():
+        s = Scheduler(SchedulerConfig(num_pages=100, page_size=4, max_seq_len=64, max_batch_tokens=4, prefill_chunk_busy=4))
+        for name in "abcdef":
+            s.enqueue(Request(name, [1], params(5)))
+        plans, events = drive(s)
+        return s, plans, events
+
+    s, plans, events = run()
+    rows = [[(r.request, r.sampled_before > 0) for r in p.rows] for p in plans]
+    assert all(sum(len(r.tokens) for r in p.rows) <= 4 for p in plans)
+    assert rows[0] == [(n, False) for n in "abcd"]  # four prompts of one token
+    assert rows[1] == [("a", True), ("b", True), ("e", False), ("f", False)]  # the prompts that wait keep half of the budget
+    assert rows[2] == [(n, True) for n in "cdef"]  # c and d were left out: they lead now
+    assert rows[3] == [(n, True) for n in "abcd"] and rows[4] == [(n, True) for n in "abef"]
+    assert all(p == sorted(p) for p in rows)  # admission order inside a plan
+    waited = {name: 0 for name in "abcdef"}
+    left = {name: 5 for name in "abcdef"}
+    for plan in rows[2:]:
+        for name in [n for n in "abcdef" if left[n] > 0]:
+            if any(r == name for r, _ in plan):
+                waited[name], left[name] = 0, left[name] - 1
+            else:
+                waited[name] += 1
+                assert waited[name] <= 1, (name, rows)
+    tokens = {name: [e.token for e in events if e.kind == "token" and e.request == name] for name in "abcdef"}
+    assert all(len(t) == 5 for t in tokens.values()) and s.idle
+    again = run()[1]
+    assert [[(r.request, tuple(r.tokens)) for r in p.rows] for p in again] == [[(r.request, tuple(r.tokens)) for r in p.rows] for p in plans]
+
+
+def test_turns_go_on_when_a_request_in_front_of_the_cursor_ends():
+    s = Scheduler(SchedulerConfig(num_pages=100, page_size=4, max_seq_len=64, max_batch_tokens=2, prefill_chunk_busy=2))
+    lengths = dict(zip("abcd", (2, 6, 6, 6)))
+    for name, n in lengths.items():
+        s.enqueue(Request(name, [1], params(n)))
+    plans, events = drive(s)
+    rows = [[r.request for r in p.rows] for p in plans]
+    left, waited = dict(lengths), {name: 0 for name in lengths}
+    for step in rows:
+        for name in [n for n in lengths if left[n] > 0]:
+            if name in step:
+                waited[name], left[name] = 0, left[name] - 1
+            else:
+                waited[name] += 1
+                assert waited[name] <= 3, (name, rows)  # at most the others' turns: 4 requests, 2 rows a step, prompts keep one
+    assert s.idle and all(len([e for e in events if e.kind == "token" and e.request == name]) == n for name, n in lengths.items())
+
+
+def test_worst_case_pages_bounds_what_a_windowed_request_ever_holds():
+    """Random portions through a windowed group: the pages held at any moment never pass the bound admission reserves."""
+    import ctypes
+
+    from hyperion_b200 import host
+
+    def bound(page, window, tokens, portion):
+        value = ctypes.c_int()
+        host.check(host.library().hb_cache_worst_case_pages(page, window, tokens, portion, ctypes.byref(value)))
+        return value.value
+
+    assert bound(4, 0, 33, 7) == 9 and bound(4, 6, 5, 100) == 2 and bound(16, 0, 0, 1) == 0
+    rng = random.Random(5)
+    for _ in range(60):
+        page = rng.choice([1, 2, 4, 8, 16])
+        window = rng.randint(1, 40)
+        portion = rng.randint(1, 30)
+        total = rng.randint(1, 200)
+        m = CacheManager([(0, PagedKV(1, 8, window=window))], page, 400, 1)
+        m.add_request("r")
+        limit, fed, most = bound(page, window, total, portion), 0, 0
+        while fed < total:
+            n = min(rng.randint(1, portion), total - fed)
+            m.extend("r", n)
+            most = max(most, 400 - m.free_pages(0))
+            m.advance("r", n)
+            fed += n
+        assert most <= limit, (page, window, portion, total, most, limit)
+        m.free("r")
+
+
+def test_admission_counts_pages_per_group_of_the_cache():
+    # a windowed group: the window (8) and one portion (4) span ceil(11 / 4) + 1 = 4 pages however long the request gets
+    s = Scheduler(SchedulerConfig(num_pages=8, page_size=4, max_seq_len=1000, max_batch_tokens=4, group_windows=(8,)))
+    for name in "abc":
+        s.enqueue(Request(name, list(range(30)), params(500)))
+    s.next_plan()
+    assert s.reserved_pages == 8 and len(s.waiting) == 1  # two run although each will pass 500 tokens
+    # the same requests with a group that keeps every key beside it: that group decides
+    s = Scheduler(SchedulerConfig(num_pages=8, page_size=4, max_seq_len=1000, max_batch_tokens=4, group_windows=(8, 0)))
+    s.enqueue(Request("a", list(range(30)), params(500)))
+    s.next_plan()
+    assert any(e.kind == "failed" and "needs 133 pages" in e.reason for e in s.take_events())
+    # no paged group at all (a model of fixed per-request state only): pages are not asked for, the request slots decide
+    s = Scheduler(SchedulerConfig(num_pages=1, page_size=4, max_seq_len=1000, max_batch=2, max_batch_tokens=64, group_windows=()))
+    for name in "abc":
+        s.enqueue(Request(name, list(range(30)), params(500)))
+    plan = s.next_plan()
+    assert [r.request for r in plan.rows] == ["a", "b"] and s.reserved_pages == 0 and len(s.waiting) == 1
+
+
+def test_a_cache_user_may_keep_any_payload_of_fixed_shape_per_token():
+    from hyperion_b200.parts.base import PagedTokens
+
+    latent = PagedTokens(inner=(24,))
+    m = CacheManager([(0, PagedKV(2, 16)), (1, latent), (2, latent), (3, PagedTokens(outer=(3,), inner=(2, 5), window=9))], 4, 8, 2)
+    assert [g.users for g in m.paged] == [[0], [1, 2], [3]] and m.group_windows == [0, 0, 9]
+    assert m.bytes_per_token() == (2 * 2 * 16 + 2 * 24 + 3 * 2 * 5) * 4  # float32 by default
+    assert latent.storage_shape(8, 4) == (8, 4, 24) and PagedKV(2, 16).storage_shape(8, 4) == (8, 2, 2, 4, 16)

@@ -289,6 +289,13 @@ def test_bfloat16_steps_give_the_same_bits_every_time(folders, name):
     for warm in range(3):
         run(f"warm{warm}")  # from here on every step of these shapes is a replay (the library's products may round
     first = run("a")  # differently inside a captured graph than in a direct launch, so like is compared with like)
+    # the bits that repeat are the right ones: every replayed step against the plain implementation
+    tail = [11 + k for k in range(6)]
+    want = [plain_logits(folders[name], ids) for ids in (prompts[0] + tail, prompts[1] + [7] + tail, prompts[2] + tail)]
+    rows = [[(0, 0), (0, 39), (1, 32)], [(0, 69), (2, 4), (1, 33)]] + [[(0, 70 + k), (1, 34 + k), (2, 5 + k)] for k in range(6)]
+    for step, (logits, places) in enumerate(zip(first, rows)):
+        for r, (request, position) in enumerate(places):
+            assert relative_error(logits[r].float().numpy(), want[request][position]) <= TOLERANCE["bfloat16"], (step, request, position)
     for repeat in range(8):
         poison = [torch.full((n,), float("nan"), device="cuda") for n in (1 << 12, 1 << 16, 1 << 20, 1 << 22)]
         del poison
@@ -386,7 +393,7 @@ def test_random_traffic_through_the_bfloat16_kernels_leaves_nothing_behind():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_pages_whose_offsets_pass_two_to_the_31_elements(dtype):
+def test_pages_whose_offsets_pass_two_to_the_31_elements(dtype, tmp_path):
     """A pool of 2.3 million tokens per layer (2.4 G elements) with all but its last 400 pages held by another request:
     the request lives on pages whose element offsets do not fit 32 bits, and its logits (two prompt portions, then
     single tokens) are the bits it gets on the first pages of a small pool."""
@@ -419,3 +426,131 @@ def test_pages_whose_offsets_pass_two_to_the_31_elements(dtype):
     got, high = run(big, pages - 400)
     assert low[0] == 0 and high[0] == pages - 400 and high[0] * 16 * 2 * 4 * 128 > 2 ** 31
     assert torch.isfinite(got).all() and torch.equal(got, want)
+    # and those bits are right: the same model as a folder (the seed gives the same weights) through the plain implementation
+    from hyperion_b200.weights import write_model_folder
+
+    folder = write_model_folder(tmp_path / "offsets", "Qwen2ForCausalLM", config, seed=0)
+    reference = plain_logits(folder, ids + later, device="cuda")
+    places = [599, len(ids) - 1] + [len(ids) + k for k in range(len(later))]
+    tolerance = 1e-4 if dtype == "float32" else TOLERANCE["bfloat16"]
+    for row, position in enumerate(places):
+        assert relative_error(got[row].numpy(), reference[position]) <= tolerance, position
+
+
+# ------------------------------------------------------------------------------------------------ anchors
+GOLDEN = __import__("pathlib").Path(__file__).resolve().parent / "golden"
+
+
+def bf16_step(x: float) -> float:
+    """One bfloat16 step at the magnitude of x (helios/crates/helios-hal/src/oracle.rs:179-184)."""
+    return 0.0 if x == 0.0 or not np.isfinite(x) else 2.0 ** (int(np.floor(np.log2(abs(x)))) - 7)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cutting", ["whole", "decode"])
+def test_the_engine_meets_the_reference_oracle_on_its_own_checkpoint(dtype, cutting):
+    """The reference's committed tiny checkpoint (five shards, read by tensor name) through the engine, teacher-forced on
+    the oracle's prompts and generated ids: at every recorded position the top-20 logits and the logsumexp are within the
+    tolerance the oracle declares for a bfloat16 forward (0.02; float32 must be within 1e-5, like the plain implementation),
+    and the argmax is the oracle's or a token of its tie group, whose width is the rule of
+    helios/crates/helios-hal/src/oracle.rs:197-217: min(tolerance, max(the reference's own bfloat16 deviation at this
+    position, two bfloat16 steps of the best logit)).  `decode`: the prompt in one step, then token by token."""
+    import json
+
+    from hyperion_b200.engine.batch import StepEntry
+
+    oracle = json.loads((GOLDEN / "qwen2-tiny-oracle.json").read_text())
+    declared = oracle["tolerance"]["max_abs_top_logits"]
+    limit = 1e-5 if dtype == "float32" else declared
+    assert oracle["bf16_vs_fp32"]["top_logits"] * 1.5 <= declared  # the oracle's tolerance is its bfloat16 drift times a margin, floored
+    engine = engine_for(GOLDEN / "qwen2-tiny-sharded", dtype, max_tokens=1024, max_requests=4)
+    worst = 0.0
+    for index, prompt in enumerate(oracle["prompts"]):
+        ids = prompt["ids"] + prompt["generated_ids"]
+        places = [row["position"] for row in prompt["positions"]]
+        if cutting == "whole":
+            logits = engine.step([StepEntry(index, ids, places)]).float().cpu().numpy()
+        else:
+            head = len(prompt["ids"])
+            parts = [engine.step([StepEntry(index, ids[:head], [head - 1])]).float().cpu().numpy()]
+            for k in range(head, len(ids)):
+                parts.append(engine.step([StepEntry(index, [ids[k]], [0])]).float().cpu().numpy())
+            by_position = dict(zip(range(head - 1, len(ids)), (p[0] for p in parts)))
+            logits = np.stack([by_position[p] for p in places])
+        engine.finish(index)
+        for row, record, deviation in zip(logits, prompt["positions"], prompt["bf16_deviation"]):
+            top = max(abs(float(row[i]) - v) for i, v in zip(record["top_ids"], record["top_logits"]))
+            peak = float(row.max())
+            lse = peak + float(np.log(np.exp(row.astype(np.float64) - peak).sum()))
+            worst = max(worst, top, abs(lse - record["logsumexp"]))
+            picked = int(row.argmax())
+            best = record["top_logits"][0]
+            threshold = min(declared, max(deviation, 2 * bf16_step(best)))
+            gap = best - record["top_logits"][record["top_ids"].index(picked)] if picked in record["top_ids"] else None
+            assert picked == record["argmax"] or (gap is not None and gap <= threshold), (index, record["position"], picked, gap, threshold)
+    assert worst <= limit, worst
+    engine.check()
+
+
+def test_random_weights_in_memory_and_as_a_folder_are_the_same_bits(tmp_path):
+    """One generator for both forms: `Engine.from_random(seed)` (a kernel fills the tensors on the device) and
+    `write_model_folder(seed)` made on the host (numpy) give equal tensors, whatever their sizes and names."""
+    from hyperion_b200.api import Engine
+    from hyperion_b200.models import DecoderModel, get_architecture
+    from hyperion_b200.weights import random_tensors, read_all, write_model_folder
+    from hyperion_b200.weights.random_init import random_tensor
+    from hyperion_b200.parts.base import WeightSpec
+
+    config, seed = TINY["B"]
+    folder = write_model_folder(tmp_path / "host", "Qwen2ForCausalLM", config, seed, 0.06, device="cpu")
+    stored = read_all(folder)
+    entry = get_architecture("Qwen2ForCausalLM")
+    model = DecoderModel(entry.build_spec(config), torch.bfloat16, torch.device("cuda"))
+    made = random_tensors(model, seed, 0.06)
+    assert set(made) == set(stored)
+    for name, tensor in made.items():
+        assert tensor.is_cuda and torch.equal(tensor.cpu().view(torch.int16), stored[name].view(torch.int16)), name
+    norm = stored["model.norm.weight"].float()
+    assert abs(float(norm.mean()) - 1.0) < 0.02 and 0.04 < float(norm.std()) < 0.08
+    # odd lengths, float32 storage, another seed and name: equal again, and different from the first
+    for shape, dtype in (((7, 13), torch.float32), ((1,), torch.bfloat16), ((333,), torch.float32)):
+        wanted = WeightSpec(shape)
+        host, device = (random_tensor("x.weight", wanted, 5, 0.5, torch.device(d), dtype) for d in ("cpu", "cuda"))
+        assert torch.equal(host, device.cpu())
+    assert not torch.equal(random_tensor("x.weight", WeightSpec((333,)), 5, 0.5, torch.device("cuda"), torch.float32),
+                           random_tensor("y.weight", WeightSpec((333,)), 5, 0.5, torch.device("cuda"), torch.float32))
+    # the engine made from the seed steps like the engine loaded from the folder: bit for bit
+    from hyperion_b200.engine.batch import StepEntry
+
+    ids = random_ids(3, 40, config.vocab_size)
+    a = Engine.from_random("Qwen2ForCausalLM", config, seed=seed, std=0.06, dtype="float32", max_tokens=128, max_requests=2)
+    b = Engine.from_folder(folder, dtype="float32", max_tokens=128, max_requests=2)
+    assert torch.equal(a.step([StepEntry("r", ids, [39])]), b.step([StepEntry("r", ids, [39])]))
+
+
+def test_a_step_that_fails_at_launch_under_lookahead_leaves_the_others_their_tokens(folders):
+    """A caller's own request holds pages the scheduler counts as free, so a step of the generation loop runs out of pages
+    when it is launched: its requests fail and are released.  Three requests decode under a budget of two tokens a step,
+    so they take turns and the one that was not in the failed step has a row in flight at that moment; it goes on and
+    reports exactly the tokens it generates alone.  (The step after a failed one must not take the staging slot of the
+    step still in flight.)"""
+    from hyperion_b200.engine.batch import StepEntry
+    from hyperion_b200.sampling import SamplingParams
+
+    config, _ = TINY["A"]
+    prompts = [random_ids(40 + i, 4, config.vocab_size) for i in range(3)]
+    params = SamplingParams(temperature=0.0, max_tokens=36, ignore_eos=True)
+    clean = engine_for(folders["A"], "float32", page_size=16, max_tokens=160, max_requests=4).generate(prompts, params)
+    results = []
+    for lookahead in (False, True):
+        engine = engine_for(folders["A"], "float32", page_size=16, max_tokens=160, max_requests=4)  # 10 pages
+        engine.step([StepEntry("held by the caller", random_ids(1, 60, config.vocab_size), [])])  # 4 of them; 9 are reserved
+        results.append(engine.generate(prompts, params, max_batch_tokens=2, prefill_chunk_busy=2, return_reasons=True, lookahead=lookahead))
+        engine.finish("held by the caller")
+        engine.cache.check()
+        assert not engine.cache.live_requests and engine.cache.free_pages() == 10
+    (tokens, reasons), (tokens_ahead, reasons_ahead) = results
+    assert sorted("OutOfPages" in r for r in reasons) == [False, True, True], reasons  # one step failed: its two requests
+    assert reasons_ahead == reasons
+    survivor = reasons.index("length")
+    assert tokens[survivor] == clean[survivor] and tokens_ahead[survivor] == clean[survivor]

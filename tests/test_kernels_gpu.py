@@ -126,7 +126,7 @@ def paged_case(kv_heads, head_dim, page_size, contexts, dtype, seed=0, pages_ext
     blocks = [-(-c // page_size) for c in contexts]
     pages = sum(blocks) + pages_extra
     order = torch.randperm(pages, generator=g).tolist()
-    cache = torch.full((pages, 2, kv_heads, page_size, head_dim), float("nan"), dtype=dtype)  # unowned slots hold NaN
+    cache = torch.full((pages, 2, kv_heads, page_size, head_dim), float("nan"), dtype=dtype)  # pages nobody holds are NaN
     width = max(blocks) + 2
     table = torch.full((len(contexts), width), -1, dtype=torch.int32)
     keys, values = [], []
@@ -141,7 +141,10 @@ def paged_case(kv_heads, head_dim, page_size, contexts, dtype, seed=0, pages_ext
             n = min(page_size, c - b * page_size)
             cache[page, 0, :, :n] = k[b * page_size : b * page_size + n].transpose(0, 1)
             cache[page, 1, :, :n] = v[b * page_size : b * page_size + n].transpose(0, 1)
-            cache[page, :, :, n:] = 0  # slots of a held page past the context are zero in the engine (never NaN keys at masked places)
+            # slots of a held page past the context: in the engine they hold what the page's last owner left there, finite
+            # keys and values of any size; a kernel that lets one of them into a sum is off by far more than the tolerance
+            sign = torch.where(torch.rand((2, kv_heads, page_size - n, head_dim), generator=g) < 0.5, -1.0, 1.0)
+            cache[page, :, :, n:] = (sign * 300.0).to(dtype)
     return cache, table, keys, values
 
 

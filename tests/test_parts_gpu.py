@@ -234,6 +234,7 @@ def test_layers_of_different_kinds_twice_run_and_shared_cache(mixed_folder, dtyp
     sizes = [9, 2, 30, 1, 5, 17, 1, 1, 40, 3]
     k = 0
     order = ["a", "b"]
+    cut = {name: [] for name in requests}  # the logits of this cutting, per request in position order
     while order:
         entries = []
         for name in list(order):
@@ -246,6 +247,7 @@ def test_layers_of_different_kinds_twice_run_and_shared_cache(mixed_folder, dtyp
             n = len(entry.tokens)
             ref = want[entry.request][fed[entry.request]:fed[entry.request] + n]
             assert np.abs(logits[row:row + n] - ref).max() <= tolerance * np.abs(ref).max(), (entry.request, fed[entry.request])
+            cut[entry.request].append(logits[row:row + n].copy())
             row += n
             fed[entry.request] += n
             if fed[entry.request] == len(requests[entry.request]):
@@ -257,6 +259,11 @@ def test_layers_of_different_kinds_twice_run_and_shared_cache(mixed_folder, dtyp
     engine.check()
     # the windowed group held far fewer pages than the full one at the end of a long request
     assert cache.free_pages(1) == cache.num_pages
+    if dtype == "float32":  # each request whole in one step gives the very bits of the cutting above: window, shared cache and all
+        for name, ids in requests.items():
+            whole = engine.step([StepEntry(("whole", name), ids, list(range(len(ids))))]).cpu().numpy()
+            engine.finish(("whole", name))
+            assert np.array_equal(whole.view(np.uint32), np.concatenate(cut[name]).view(np.uint32)), name
 
 
 # ------------------------------------------------------------------------------------------------
@@ -350,6 +357,21 @@ def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(tmp_path):
     got_a.append(mixed[18:])
     assert np.abs(mixed[:18] - want["c"]).max() <= 1e-4 * np.abs(want["c"]).max()
     assert np.abs(np.concatenate(got_a) - want["a"]).max() <= 1e-4 * np.abs(want["a"]).max()
+    engine.finish("a")
+    engine.finish("c")
+    # generation: the model keeps no pages, so admission asks for none (the cache of 64 tokens would not hold these requests
+    # if they were counted in pages) and only the two request slots bound how many run at a time
+    from hyperion_b200.sampling import SamplingParams
+
+    prompts = [a, b, c]
+    engine.runner.use_graphs = False  # this toy decides on the host by slot numbers, which a replayed graph would repeat
+    tokens, reasons = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=60, ignore_eos=True), return_reasons=True, lookahead=False)
+    assert reasons == ["length"] * 3 and [len(t) for t in tokens] == [60, 60, 60]
+    for prompt, made in zip(prompts, tokens):
+        ref = toy_plain(TOY, weights, prompt + made).numpy()
+        for i, token in enumerate(made[:8]):
+            row = ref[len(prompt) + i - 1]
+            assert row.max() - row[token] <= 1e-4 * np.abs(row).max()
 
 
 # ------------------------------------------------------------------------------------------------
@@ -490,3 +512,123 @@ def test_a_routed_feed_forward_and_another_position_encoding(tmp_path):
     got.append(engine.step([StepEntry("a", a[26:], list(range(34)))]).cpu().numpy())
     assert np.abs(np.concatenate(got) - want_a).max() <= 1e-4 * np.abs(want_a).max()
     assert np.abs(mixed[1:] - want_b).max() <= 1e-4 * np.abs(want_b).max()
+
+
+# ------------------------------------------------------------------------------------------------
+# A toy mixer whose paged payload is one latent vector per token (not keys and values of heads): it states the shape,
+# the cache manager sizes pages from it, the step hands it its pages and block table.  Nothing in the package knows it.
+LATENT = {"architectures": ["TestLatentLM"], "hidden": 40, "vocab": 89, "inter": 56, "latent": 12, "eps": 1e-6, "max_positions": 256}
+
+
+def register_latent():
+    from hyperion_b200.models import Architecture, register_architecture
+    from hyperion_b200.parts import LayerSpec, Mixer, ModelSpec, PagedTokens, PartSpec, Run, WeightSpec, register_mixer
+
+    class LatentAttention(Mixer):
+        """c_t = x_t W_c is kept per token; y_t = (sum_j softmax_j(q_t . c_j) c_j) W_o over j <= t with q_t = x_t W_q."""
+
+        def __init__(self, spec, build):
+            super().__init__(spec, build)
+            self.hidden, self.latent = spec.params["hidden_size"], spec.params["latent"]
+
+        def weights(self):
+            return {"c.weight": WeightSpec((self.latent, self.hidden)), "q.weight": WeightSpec((self.latent, self.hidden)),
+                    "o.weight": WeightSpec((self.hidden, self.latent))}
+
+        def load(self, tensors):
+            self.w_c, self.w_q, self.w_o = (tensors[n].float() for n in ("c.weight", "q.weight", "o.weight"))
+
+        def cache_request(self):
+            return PagedTokens(inner=(self.latent,), dtype=torch.float32)
+
+        def forward(self, x, step, cache, own_cache):
+            # everything that changes from step to step is read on the device: positions, rows, block tables
+            pages, page_size, latent = cache.storage.shape
+            xf = x.float()
+            c, q = xf @ self.w_c.t(), xf @ self.w_q.t()
+            rows, positions = step.token_row.long(), step.positions.long()
+            page = cache.block_table[rows, positions // page_size].long()
+            cache.storage[page, positions % page_size] = c
+            table = cache.block_table[rows].long()  # [tokens, width]
+            keys = cache.storage[table.clamp(min=0)].reshape(len(rows), -1, latent)  # every slot the row's table names
+            slot_position = torch.arange(keys.shape[1], device=x.device)[None, :]
+            scores = torch.einsum("tl,tsl->ts", q, keys).masked_fill(slot_position > positions[:, None], float("-inf"))
+            mixed = torch.einsum("ts,tsl->tl", torch.softmax(scores, dim=-1), torch.nan_to_num(keys))
+            return (mixed @ self.w_o.t()).to(self.dtype)
+
+    def spec(c):
+        sizes = {"vocab_size": c["vocab"], "hidden_size": c["hidden"]}
+        norm = {"hidden_size": c["hidden"], "eps": c["eps"]}
+        layers = tuple(LayerSpec("prenorm", PartSpec("test_latent_attention", f"l{i}.mix.", {"hidden_size": c["hidden"], "latent": c["latent"]}),
+                                 PartSpec("swiglu", f"l{i}.mlp.", {"hidden_size": c["hidden"], "intermediate_size": c["inter"]}),
+                                 {"input": PartSpec("rmsnorm", f"l{i}.n1.", norm), "post_mixer": PartSpec("rmsnorm", f"l{i}.n2.", norm)})
+                       for i in range(2))
+        return ModelSpec("TestLatentLM", c["hidden"], c["vocab"], c["max_positions"], PartSpec("token_embedding", "embed.", sizes), layers,
+                         (Run(0), Run(1)), PartSpec("rmsnorm", "norm.", norm), PartSpec("linear_head", "head.", {**sizes, "tied": True}))
+
+    register_mixer("test_latent_attention", LatentAttention)
+    register_architecture(Architecture("TestLatentLM", lambda document: dict(document), spec, lambda config: dict(config)))
+
+
+def latent_plain(c, w, ids):
+    w = {k: v.double() for k, v in w.items()}
+    t = len(ids)
+    h = plain.embedding(w["embed.weight"], torch.tensor(ids))
+    causal = torch.arange(t)[None, :] <= torch.arange(t)[:, None]
+    for i in range(2):
+        x = plain.rmsnorm(h, w[f"l{i}.n1.weight"], c["eps"])
+        latent, q = x @ w[f"l{i}.mix.c.weight"].t(), x @ w[f"l{i}.mix.q.weight"].t()
+        probs = torch.softmax((q @ latent.t()).masked_fill(~causal, float("-inf")), dim=-1)
+        h = h + (probs @ latent) @ w[f"l{i}.mix.o.weight"].t()
+        x = plain.rmsnorm(h, w[f"l{i}.n2.weight"], c["eps"])
+        h = h + plain.swiglu_mlp(x, w[f"l{i}.mlp.gate_proj.weight"], w[f"l{i}.mlp.up_proj.weight"], w[f"l{i}.mlp.down_proj.weight"])
+    return plain.linear(plain.rmsnorm(h, w["norm.weight"], c["eps"]), w["embed.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_mixer_that_keeps_one_latent_per_token_in_pages(tmp_path, dtype):
+    from hyperion_b200.api import Engine
+    from hyperion_b200.engine.batch import StepEntry
+    from hyperion_b200.sampling import SamplingParams
+    from hyperion_b200.weights import read_all, write_model_folder
+
+    register_latent()
+    folder = write_model_folder(tmp_path / "latent", "TestLatentLM", LATENT, seed=21, std=0.3)
+    weights = read_all(folder)
+    engine = Engine.from_folder(folder, dtype=dtype, page_size=8, max_tokens=96, max_requests=3)
+    cache = engine.cache
+    assert len(cache.paged) == 1 and cache.paged[0].users == [0, 1] and cache.paged[0].storage.shape == (2, 12, 8, LATENT["latent"])
+    assert cache.paged[0].storage.dtype == torch.float32 and cache.bytes_per_token() == 2 * LATENT["latent"] * 4
+    g = torch.Generator().manual_seed(3)
+    requests = {name: torch.randint(0, LATENT["vocab"], (n,), generator=g).tolist() for name, n in (("a", 50), ("b", 21), ("c", 40))}
+    want = {name: latent_plain(LATENT, weights, ids).numpy() for name, ids in requests.items()}
+    tolerance = 1e-4 if dtype == "float32" else 3e-2
+    fed = {name: 0 for name in requests}
+    order, sizes, k = ["a", "b"], [7, 2, 13, 1, 1, 20, 3], 0
+    while order:
+        entries = []
+        for name in list(order):
+            n = min(sizes[k % len(sizes)], len(requests[name]) - fed[name])
+            k += 1
+            entries.append(StepEntry(name, requests[name][fed[name]:fed[name] + n], list(range(n))))
+        logits = engine.step(entries).float().cpu().numpy()
+        row = 0
+        for entry in entries:
+            n = len(entry.tokens)
+            ref = want[entry.request][fed[entry.request]:fed[entry.request] + n]
+            assert np.abs(logits[row:row + n] - ref).max() <= tolerance * np.abs(ref).max(), (entry.request, fed[entry.request])
+            row += n
+            fed[entry.request] += n
+            if fed[entry.request] == len(requests[entry.request]):
+                engine.finish(entry.request)
+                order.remove(entry.request)
+                if entry.request == "b":
+                    order.append("c")  # on the pages b gave back: 50 + 21 + 40 tokens do not fit 96 at once
+        cache.check()
+    assert cache.free_pages(0) == cache.num_pages
+    # through the scheduler too: admission reserves pages of this group by its own need
+    tokens = engine.generate([requests["b"]], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True), lookahead=False)
+    ref = latent_plain(LATENT, weights, requests["b"] + tokens[0]).numpy()
+    for i, token in enumerate(tokens[0]):
+        row = ref[len(requests["b"]) + i - 1]
+        assert row.max() - row[token] <= 2 * tolerance * np.abs(row).max()
