@@ -2,14 +2,20 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
 
-Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch (default 8): W
-untimed and K timed decode steps of ``batch`` requests that were each prefilled with 2,048 random
-token ids, timed with CUDA events on the device.  ``e2e`` is the same through ``Engine.generate``
-(token ids in from the host every step, sampled ids back to the host every step).  ``prefill`` is
-one whole 2,048-token prompt in one step (from its third occurrence on the engine replays a step
-shape from a captured graph, as it does for decode steps; the timed repetitions are such replays).  ``roofline`` relates the decode step to the bytes it has
-to read (every weight it uses once, plus the cache of the live requests).  ``points`` holds decode
-at batch 1 and 64.  Weights (15 GB) are larger than L2, so every step streams them from HBM.
+Prints ONE JSON line.  Every decode figure is taken over the whole range the configuration names: ``batch``
+requests are each prefilled with 2,048 random token ids and then decoded to a context of 4,096 (one new token per
+request per step, output head and token choice included).  After W untimed steps the rest of the range is timed in
+windows of exactly K steps, a CUDA event between every two windows (at least ten windows: K is capped at a tenth of
+the range).  ``value`` is decoded tokens per second over all windows at the given batch (default 8), ``ms_per_step``
+the same as time per step; ``windows`` gives the median, the 10th and the 90th percentile of the windows' time per
+step and the rate of the windows at contexts of about 2,048, 3,072 and 4,096 (the reference's protocol: at least ten
+windows, median [p10, p90], docs/performance-log.md:5).  ``points`` holds the same whole-range figure at batch 1 and
+64.  ``e2e`` is the same range through ``Engine.generate`` (token ids in from the host, sampled ids back to the host
+every step), timed on the host.  ``prefill`` is one whole 2,048-token prompt in one step (from its third occurrence on
+the engine replays a step shape from a captured graph, as it does for decode steps; the timed repetitions are such
+replays).  ``roofline`` relates the decode step to the bytes it has to read (every weight it uses once, plus the
+cache of the live requests at the mean context of the timed steps).  Weights (15 GB) are larger than L2, so every
+step streams them from HBM.
 """
 from __future__ import annotations
 
@@ -29,8 +35,10 @@ sys.path.insert(0, str(ROOT))
 PROMPT = 2048
 CONTEXT = 4096
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# H100 decode at batch 8 (context 512) published by the reference: docs/performance-log.md:239-242
+# What the reference publishes for this model: decode by batch on one H100 at context 512 (docs/performance-log.md:239-242).
+# It has no number on a B200, none at contexts of 2,048 to 4,096 by batch, and none at batch 64.
 BASELINE_TOK_S = {1: 146.0, 8: 1087.0}
+BASELINE_LABEL = {"gpu": "H100 80GB", "context": 512, "unit": "tokens/s", "source": "docs/performance-log.md:239-242 of the reference"}
 
 
 def peaks() -> tuple[dict, str]:
@@ -118,9 +126,17 @@ def random_prompt(seed: int, count: int, vocab: int) -> list[int]:
     return torch.randint(0, vocab, (count,), generator=torch.Generator().manual_seed(seed)).tolist()
 
 
-def time_decode(engine, batch: int, steps: int, warmup: int) -> dict:
-    """``batch`` requests prefilled to 2,048 tokens, then W untimed + K timed decode steps (one new
-    token per request per step, LM head and token choice included), CUDA events around the K steps."""
+def percentile(values: list[float], fraction: float) -> float:
+    ordered = sorted(values)
+    at = fraction * (len(ordered) - 1)
+    low = int(at)
+    high = min(low + 1, len(ordered) - 1)
+    return ordered[low] + (ordered[high] - ordered[low]) * (at - low)
+
+
+def time_decode(engine, batch: int, window: int, warmup: int, decode_tokens: int = CONTEXT - PROMPT) -> dict:
+    """``batch`` requests prefilled to 2,048 tokens and decoded by ``decode_tokens`` more: W untimed steps, then windows
+    of exactly ``window`` steps with a CUDA event between every two, to the end of the range."""
     import torch
 
     from hyperion_b200.engine.batch import StepEntry
@@ -131,8 +147,11 @@ def time_decode(engine, batch: int, steps: int, warmup: int) -> dict:
     names = [f"bench{batch}_{i}" for i in range(batch)]
     for i, name in enumerate(names):
         engine.step([StepEntry(name, random_prompt(i, PROMPT, vocab), [])])
-    feed = [random_prompt(1000 + s, batch, vocab) for s in range(steps + warmup)]
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    window = max(1, min(window, (decode_tokens - warmup) // 10))
+    n_windows = (decode_tokens - warmup) // window
+    steps = n_windows * window
+    feed = torch.randint(0, vocab, (warmup + steps, batch), generator=torch.Generator().manual_seed(1000 + batch)).tolist()
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(n_windows + 1)]
     options = {"sampling_options": ([w for name in names for w in pack_options(GREEDY, 0, engine.cache.slot(name))], (batch, 8))}
 
     def one(s):
@@ -144,21 +163,31 @@ def time_decode(engine, batch: int, steps: int, warmup: int) -> dict:
     torch.cuda.synchronize()
     launches_before = native.LAUNCHES[0] + getattr(engine.runner, "graph_launches", 0)
     host_start = time.perf_counter()
-    start.record()
-    for s in range(warmup, warmup + steps):
-        one(s)
-    stop.record()
+    events[0].record()
+    for w in range(n_windows):
+        for s in range(warmup + w * window, warmup + (w + 1) * window):
+            one(s)
+        events[w + 1].record()
     torch.cuda.synchronize()
     host_ms = (time.perf_counter() - host_start) * 1e3
-    ms = start.elapsed_time(stop)
+    per_window = [events[w].elapsed_time(events[w + 1]) / window for w in range(n_windows)]  # ms per step
+    ms = events[0].elapsed_time(events[-1])
     launches = native.LAUNCHES[0] + getattr(engine.runner, "graph_launches", 0) - launches_before
     mean_context = PROMPT + warmup + (steps + 1) / 2
     h2d = engine.runner.packer._cursor * 4
     for name in names:
         engine.finish(name)
     engine.check()
+
+    def rate_at(context: int) -> float:
+        index = min(n_windows - 1, max(0, (context - PROMPT - warmup) // window))
+        return round(batch / (per_window[index] / 1e3), 1)
+
     return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "host_ms_per_step": host_ms / steps,
-            "launches": launches, "mean_context": mean_context, "h2d_bytes": h2d}
+            "launches": launches, "mean_context": mean_context, "h2d_bytes": h2d, "steps": steps, "window": window,
+            "windows": {"count": n_windows, "steps_each": window, "ms_per_step_median": round(statistics.median(per_window), 4),
+                        "ms_per_step_p10": round(percentile(per_window, 0.1), 4), "ms_per_step_p90": round(percentile(per_window, 0.9), 4),
+                        "tokens_per_s_at_context": {str(c): rate_at(c) for c in (PROMPT, (PROMPT + PROMPT + decode_tokens) // 2, PROMPT + decode_tokens)}}}
 
 
 def time_prefill(engine, reps: int = 5, warmup: int = 3) -> dict:
@@ -183,10 +212,11 @@ def time_prefill(engine, reps: int = 5, warmup: int = 3) -> dict:
     return {"ms": statistics.median(times)}
 
 
-def time_e2e(engine, batch: int, steps: int, warmup: int) -> dict:
-    """Decode throughput through ``Engine.generate``: prompts go in from the host; every step copies its
-    metadata from pinned memory and its sampled ids back to pinned memory, where the callback reads them
-    (one step behind the device, which takes each token from the step before on the device)."""
+def time_e2e(engine, batch: int, window: int, warmup: int, decode_tokens: int = CONTEXT - PROMPT) -> dict:
+    """The same range through ``Engine.generate``: prompts go in from the host; every step copies its metadata from
+    pinned memory and its sampled ids back to pinned memory, where the callback reads them (one step behind the device,
+    which takes each token from the step before on the device).  Timed on the host, from the W-th token of the last
+    request to its last token."""
     from hyperion_b200.sampling import SamplingParams
 
     vocab = engine.model.spec.vocab_size
@@ -197,11 +227,15 @@ def time_e2e(engine, batch: int, steps: int, warmup: int) -> dict:
         if index == batch - 1:
             stamps.append(time.perf_counter())
 
-    engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=warmup + steps + 1, ignore_eos=True), max_batch=batch,
+    engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=decode_tokens, ignore_eos=True), max_batch=batch,
                     max_batch_tokens=batch * PROMPT, prefill_chunk_busy=PROMPT, on_token=on_token)
+    steps = len(stamps) - 1 - warmup
     seconds = stamps[-1] - stamps[warmup]
+    window = max(1, min(window, steps // 10))
+    per_window = [(stamps[warmup + (w + 1) * window] - stamps[warmup + w * window]) / window * 1e3 for w in range(steps // window)]
     return {"tok_s": batch * steps / seconds, "ms_per_step": seconds / steps * 1e3, "h2d_bytes": engine.runner.packer._cursor * 4,
-            "d2h_bytes": batch * 4}
+            "d2h_bytes": batch * 4, "steps": steps, "ms_per_step_median": round(statistics.median(per_window), 4),
+            "ms_per_step_p10": round(percentile(per_window, 0.1), 4), "ms_per_step_p90": round(percentile(per_window, 0.9), 4)}
 
 
 def other_workload(name: str) -> int:
@@ -309,10 +343,12 @@ def reference_tables() -> int:
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=128)
-    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--steps", type=int, default=128, help="decode steps per timed window (at most a tenth of the range, so that there are ten windows)")
+    parser.add_argument("--warmup", type=int, default=8, help="untimed decode steps before the first window (at least 3)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=28, help="fewer than the configuration's 28 only to save memory or time")
+    parser.add_argument("--decode-tokens", type=int, default=CONTEXT - PROMPT,
+                        help="tokens decoded after the 2,048-token prompts (the configuration's range is 2,048, to context 4,096); fewer only for profiling")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points, prefill and e2e")
     parser.add_argument("--only", default=None, choices=["prefill"], help="time one part alone (for profiling)")
@@ -331,18 +367,18 @@ def main() -> int:
         if int(os.environ.get("RANK", "0")) == 0:
             print("bench.py: this engine runs on one GPU; --gpus > 1 is not supported")
         return 2
-    if args.warmup < 3:
-        args.warmup = 3
+    args.warmup = max(3, args.warmup)
+    args.steps = max(1, args.steps)
+    decode_tokens = max(args.warmup + 10, min(args.decode_tokens, CONTEXT - PROMPT))
 
     import torch
 
     from hyperion_b200.api import Engine
-    from hyperion_b200.ops import native
 
     measured, source = peaks()
     config = model_config(args.layers)
     largest = args.batch if args.skip_points else max(args.batch, 64)
-    tokens_needed = largest * (PROMPT + 64 + max(args.steps + args.warmup, 64 + 8)) + PROMPT
+    tokens_needed = largest * (PROMPT + decode_tokens + 16) + PROMPT + 16
     engine = Engine.from_random("Qwen2ForCausalLM", config, seed=0, dtype="bfloat16", page_size=16,
                                 max_tokens=tokens_needed, max_requests=max(largest, 8))
     if args.only == "prefill":  # for profiling: the prefill step alone
@@ -352,40 +388,52 @@ def main() -> int:
         return 0
     clocks = ClockSampler()
     clocks.start()
-    main_run = time_decode(engine, args.batch, args.steps, args.warmup)
+    main_run = time_decode(engine, args.batch, args.steps, args.warmup, decode_tokens)
     clock_record = clocks.stop()
+
+    def roofline(run: dict, batch: int) -> dict:
+        bytes_per_step = weight_bytes(config) + batch * run["mean_context"] * engine.cache.bytes_per_token()
+        achieved = bytes_per_step / (run["ms_per_step"] / 1e3) / 1e9
+        return {"bound": "hbm", "achieved": round(achieved, 1), "peak": measured["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / measured["hbm_gbs"], 4), "of": source, "mean_context": round(run["mean_context"], 1)}
 
     record = {
         "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen2.5-7B)",
-        "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": main_run["window"], "warmup": args.warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        # the only published number there is: another GPU and a shorter context (see "baseline"), so a ratio across hardware
         "vs_baseline": round(main_run["tok_s"] / BASELINE_TOK_S[args.batch], 3) if args.batch in BASELINE_TOK_S else None,
+        "baseline": {**BASELINE_LABEL, "value": BASELINE_TOK_S.get(args.batch)},
         "dtype": "bf16", "data": "synthetic: seeded random weights (N(0, 0.02)) and uniform random token ids",
         "impl": "ours",
         "config": {"model": "Qwen2.5-7B shape", "layers": args.layers, "layers_of_config": 28, "hidden": config.hidden_size,
                    "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
                    "intermediate": config.intermediate_size, "vocab": config.vocab_size, "global_batch": args.batch,
-                   "seq_len": CONTEXT, "prompt_len": PROMPT, "decode_from_context": PROMPT, "page_size": 16, "parallelism": "single GPU",
+                   "seq_len": PROMPT + decode_tokens, "prompt_len": PROMPT, "decoded_tokens_per_request": decode_tokens,
+                   "timed_steps": main_run["steps"], "page_size": 16, "parallelism": "single GPU",
                    "l2": "weights (15 GB) exceed L2; every step streams them", "peaks": source},
+        "windows": main_run["windows"],
         "clocks": clock_record,
         "gpu_launches": main_run["launches"],
         "host_ms_per_step": round(main_run["host_ms_per_step"], 4),
+        "roofline": roofline(main_run, args.batch),
     }
-    bytes_per_step = weight_bytes(config) + args.batch * main_run["mean_context"] * engine.cache.bytes_per_token()
-    achieved = bytes_per_step / (main_run["ms_per_step"] / 1e3) / 1e9
-    record["roofline"] = {"bound": "hbm", "achieved": round(achieved, 1), "peak": measured["hbm_gbs"], "unit": "GB/s",
-                          "frac": round(achieved / measured["hbm_gbs"], 4), "of": source}
     if not args.skip_points:
         prefill = time_prefill(engine)
         flops = prefill_flops(config, PROMPT)
         record["prefill"] = {"value": round(PROMPT / (prefill["ms"] / 1e3), 1), "tokens": PROMPT, "ms": round(prefill["ms"], 3),
                              "frac": round(flops / (prefill["ms"] / 1e3) / (measured["bf16_tflops"] * 1e12), 4), "of": source}
-        short = min(args.steps, 64)
-        record["points"] = {"decode_b1": round(time_decode(engine, 1, short, args.warmup)["tok_s"], 1),
-                            "decode_b64": round(time_decode(engine, 64, short, args.warmup)["tok_s"], 1)}
-        e2e = time_e2e(engine, args.batch, min(args.steps, 64), args.warmup)
+        record["points"], record["points_detail"] = {}, {}
+        for batch in (1, 64):
+            run = time_decode(engine, batch, args.steps, args.warmup, decode_tokens)
+            record["points"][f"decode_b{batch}"] = round(run["tok_s"], 1)
+            record["points_detail"][f"decode_b{batch}"] = {"ms_per_step": round(run["ms_per_step"], 4), "timed_steps": run["steps"], "windows": run["windows"],
+                                                           "roofline_frac": roofline(run, batch)["frac"]}
+        e2e = time_e2e(engine, args.batch, args.steps, args.warmup, decode_tokens)
         record["e2e"] = {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d_bytes"],
-                         "d2h_bytes_per_step": e2e["d2h_bytes"], "ms_per_step": round(e2e["ms_per_step"], 4)}
+                         "d2h_bytes_per_step": e2e["d2h_bytes"], "ms_per_step": round(e2e["ms_per_step"], 4), "timed_steps": e2e["steps"],
+                         "ms_per_step_median": e2e["ms_per_step_median"], "ms_per_step_p10": e2e["ms_per_step_p10"],
+                         "ms_per_step_p90": e2e["ms_per_step_p90"], "clock": "host"}
     print(json.dumps(record))
     return 0
 

@@ -111,22 +111,25 @@ class CacheManager:
                 self._where[entry] = ("state", group, len(self.states[group].users) - 1)
             else:
                 raise TypeError(f"unknown cache request {need!r}")
+        self.device = device
+        self.dtype = dtype
+        if device is not None and device.type == "cuda":
+            # the reference checks --max-seq-len against the device's memory before it commits the pool
+            # (helios/crates/helios-hal/src/pool_plan.rs:43-60); here the pool is refused with the numbers when it cannot fit
+            wanted = num_pages * page_size * self.bytes_per_token()
+            free = torch.cuda.mem_get_info(device)[0]
+            if wanted > free:
+                raise MemoryError(f"a cache of {num_pages * page_size} tokens needs {wanted / 2**30:.1f} GiB ({self.bytes_per_token()} bytes per token), "
+                                  f"{free / 2**30:.1f} GiB are free on {device} beside the weights: lower max_tokens "
+                                  f"(the command line's --max-seq-len, --max-batch or --cache-tokens)")
+        if not 0 < num_pages < 2**31:
+            raise ValueError(f"the number of pages must be in 1..2^31 - 1, got {num_pages}")
         self._lib = host.library()
         self._handle = ctypes.c_void_p()
         windows = host.ints([g.spec.window for g in self.paged])
         host.check(self._lib.hb_cache_new(page_size, num_pages, max_requests, len(self.paged), host.address(windows), ctypes.byref(self._handle)))
         self.keys = host.KeyMap()
-        self.device = device
-        self.dtype = dtype
         if device is not None:
-            # the reference checks --max-seq-len against the device's memory before it commits the pool
-            # (helios/crates/helios-hal/src/pool_plan.rs:43-60); here the pool is refused with the numbers when it cannot fit
-            wanted = num_pages * page_size * self.bytes_per_token()
-            if device.type == "cuda" and wanted > torch.cuda.mem_get_info(device)[0]:
-                free = torch.cuda.mem_get_info(device)[0]
-                raise MemoryError(f"a cache of {num_pages * page_size} tokens needs {wanted / 2**30:.1f} GiB ({self.bytes_per_token()} bytes per token), "
-                                  f"{free / 2**30:.1f} GiB are free on {device} beside the weights: lower max_tokens "
-                                  f"(the command line's --max-seq-len, --max-batch or --cache-tokens)")
             for g in self.paged:
                 g.storage = torch.zeros((len(g.users), *g.spec.storage_shape(num_pages, page_size)), dtype=g.spec.dtype or dtype, device=device)
             for s in self.states:

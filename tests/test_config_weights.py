@@ -339,3 +339,38 @@ def test_the_native_header_reader_agrees_with_a_plain_reading_of_written_files(t
             entry = found[name]
             assert list(entry.shape) == meta["shape"] and [entry.begin, entry.end] == meta["data_offsets"]
             assert entry.payload_start == 8 + length and entry.dtype == tensors[name].dtype
+
+
+def test_random_weights_are_a_function_of_seed_name_and_index_only(tmp_path):
+    """The counter-based generator: Philox4x32-10 as the scalar implementation of the sampler computes it, normal
+    deviates of the right moments, a tensor's values independent of which other tensors exist and of how many values are
+    asked for, and the same file for the same seed."""
+    import numpy as np
+
+    from hyperion_b200.sampling import philox4x32_10 as scalar_philox
+    from hyperion_b200.weights import philox_normal
+    from hyperion_b200.weights.random_init import random_tensor
+    from hyperion_b200.parts.base import WeightSpec
+
+    key = philox_normal.tensor_key(7, "model.layers.0.mlp.up_proj.weight")
+    assert key != philox_normal.tensor_key(7, "model.layers.1.mlp.up_proj.weight") != philox_normal.tensor_key(8, "model.layers.1.mlp.up_proj.weight")
+    lo = np.array([0, 1, 2 ** 32 - 1, 12345], dtype=np.uint64)
+    hi = np.array([0, 0, 3, 2 ** 31], dtype=np.uint64)
+    words = philox_normal.philox4x32_10(lo, hi, key)
+    for i in range(4):
+        assert [int(w[i]) for w in words] == scalar_philox([int(lo[i]), int(hi[i]), 0, 0], list(key))
+    values = philox_normal.normal_float32(400_001, key, 1.0)
+    assert abs(float(values.mean())) < 0.01 and abs(float(values.std()) - 1.0) < 0.01
+    assert abs(float(((values.astype(np.float64)) ** 4).mean()) - 3.0) < 0.1 and 4.0 < float(np.abs(values).max()) < 7.0
+    assert 0.67 < float((np.abs(values) < 1.0).mean()) < 0.69
+    # a prefix is a prefix (odd and even counts, chunk borders): element i depends on i alone
+    assert np.array_equal(philox_normal.normal_float32(33_333, key, 1.0), values[:33_333])
+    assert np.array_equal(philox_normal.normal_float32(70_001, key, 1.0, chunk=1000), values[:70_001])
+    scaled = philox_normal.normal_float32(1000, key, 0.02, mean=1.0)
+    assert abs(float(scaled.mean()) - 1.0) < 0.005 and 0.015 < float(scaled.std()) < 0.025
+    tensor = random_tensor("model.layers.0.mlp.up_proj.weight", WeightSpec((10, 40)), 7, 1.0, torch.device("cpu"), torch.bfloat16)
+    assert torch.equal(tensor.view(-1), torch.from_numpy(values[:400]).to(torch.bfloat16))
+    a = write_model_folder(tmp_path / "a", "Qwen2ForCausalLM", TINY_A, seed=3, device="cpu")
+    b = write_model_folder(tmp_path / "b", "Qwen2ForCausalLM", TINY_A, seed=3, device="cpu")
+    c = write_model_folder(tmp_path / "c", "Qwen2ForCausalLM", TINY_A, seed=4, device="cpu")
+    assert (a / "model.safetensors").read_bytes() == (b / "model.safetensors").read_bytes() != (c / "model.safetensors").read_bytes()

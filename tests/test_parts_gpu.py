@@ -87,7 +87,8 @@ def test_embedding_and_head_parts(dtype):
     assert head.weights() == {}
     table = rnd(301, 40, seed=5).to(torch.bfloat16)
     embedding.load({"weight": (table.float() if dtype == torch.float32 else table).to(DEV)})
-    head.tie(embedding.table)
+    assert head.wants_shared_table()
+    head.use_shared_table(embedding.shared_table())
     ids = torch.tensor([300, 0, 17], dtype=torch.int32)
     h = embedding.forward(ids.to(DEV))
     assert torch.equal(h.cpu(), table.float()[ids.long()])
@@ -522,7 +523,10 @@ LATENT = {"architectures": ["TestLatentLM"], "hidden": 40, "vocab": 89, "inter":
 
 def register_latent():
     from hyperion_b200.models import Architecture, register_architecture
-    from hyperion_b200.parts import LayerSpec, Mixer, ModelSpec, PagedTokens, PartSpec, Run, WeightSpec, register_mixer
+    from hyperion_b200.parts import MIXERS, LayerSpec, Mixer, ModelSpec, PagedTokens, PartSpec, Run, WeightSpec, register_mixer
+
+    if "test_latent_attention" in MIXERS:  # the test runs once per element type
+        return
 
     class LatentAttention(Mixer):
         """c_t = x_t W_c is kept per token; y_t = (sum_j softmax_j(q_t . c_j) c_j) W_o over j <= t with q_t = x_t W_q."""
@@ -593,7 +597,7 @@ def test_a_toy_mixer_that_keeps_one_latent_per_token_in_pages(tmp_path, dtype):
     from hyperion_b200.weights import read_all, write_model_folder
 
     register_latent()
-    folder = write_model_folder(tmp_path / "latent", "TestLatentLM", LATENT, seed=21, std=0.3)
+    folder = write_model_folder(tmp_path / "latent", "TestLatentLM", LATENT, seed=21, std=0.12)
     weights = read_all(folder)
     engine = Engine.from_folder(folder, dtype=dtype, page_size=8, max_tokens=96, max_requests=3)
     cache = engine.cache
