@@ -41,13 +41,16 @@ def batch_tile_for(m: int) -> int:
     return 0 if m > 64 else (16 if m <= 16 else (32 if m <= 32 else 64))
 
 
-def choose_splits(n: int, k: int, sms: Optional[int] = None) -> int:
-    """Split K so that about one block per SM of the device (``sms``, asked from the current device when absent) streams
-    the weights; every split keeps at least 4 k-blocks."""
+def choose_splits(n: int, k: int, m: int = 64, sms: Optional[int] = None) -> int:
+    """Split K so that the blocks fill the device (``sms`` multiprocessors, asked from the current device when absent):
+    about two blocks per SM for up to 16 rows of activations (two blocks share an SM, one's start and epilogue pass under
+    the other's stream, and the partial sums are small), about one per SM for more rows (the partial sums, ``splits`` times
+    the output in float, cost more than the overlap gives); every split keeps at least 4 k-blocks."""
     sms = sms or sm_count()
     tiles = -(-n // 128)
     k_blocks = -(-k // 64)
-    return max(1, min(sms // tiles if tiles < sms else 1, k_blocks // 4, 16))
+    target = 2 * sms if m <= 16 else sms
+    return max(1, min(target // tiles if tiles < target else 1, k_blocks // 4, 16))
 
 
 @dataclass
@@ -75,7 +78,7 @@ class SplitSum:
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, epilogue: int = EPI_BF16,
-              out: Optional[torch.Tensor] = None, splits: Optional[int] = None, leave_partials: bool = False):
+              out: Optional[torch.Tensor] = None, splits: Optional[int] = None, leave_partials: bool = False, w_tiled: bool = False):
     """``leave_partials``: when K is split, return a :class:`SplitSum` instead of adding the pieces up."""
     require_cuda(x, w, bias)
     if not supported(x, w):
@@ -99,14 +102,14 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     if tile == 0:
         splits = 1
     else:
-        splits = choose_splits(n, k) if splits is None else splits
+        splits = choose_splits(n, k, m) if splits is None else splits
         if splits > 1:
             workspace = torch.empty(splits * m * n, dtype=torch.float32, device=x.device)
     leave = int(leave_partials and workspace is not None and epilogue in (EPI_BF16, EPI_F32))
     lib = library("gemm_tcgen05")
     check(lib.hb_gemm_bf16(ptr(x), i32(x.stride(0)), ptr(w), i32(w.stride(0)), ptr(out), i32(out.stride(0)), ptr(bias_f), ptr(bias_h),
                            i32(m), i32(n), i32(k), i32(epilogue), i32(tile), i32(splits), ptr(workspace), i32(leave), ptr(status_word(x.device)),
-                           stream_ptr()), "gemm_bf16")
+                           stream_ptr(), i32(w_tiled)), "gemm_bf16")
     if leave:
         return SplitSum(workspace.view(splits, m, n), bias, out_dtype)
     return out
