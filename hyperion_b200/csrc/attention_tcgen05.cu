@@ -15,8 +15,8 @@
 //               with that buffer), and rescales O in tensor memory only when
 //               the maximum has grown by more than 2^8 (until then the stale maximum is kept, which changes no
 //               result: the final division uses the same maximum for numerator and denominator).
-// Every mbarrier wait is bounded; a wait that runs out sets HB_STATUS_WAIT_EXPIRED, all roles leave their loops, tensor
-// memory is freed and the block returns.
+// Every mbarrier wait is bounded; a wait that runs out sets HB_STATUS_WAIT_EXPIRED, all roles leave their loops, the block
+// takes no further item, tensor memory is freed and the block returns.
 //
 // Counterpart in the reference: attention_mma_paged_*_bf16 (mma.sync m16n8k16, 64 x 64 tiles;
 // helios/crates/helios-hal/kernels/elementwise.cu:576-729,749); mask: key position <= query position (:660-663).
@@ -171,8 +171,16 @@ struct AttnArgs {
 
 // tiles[3*i] = first token (flat index), tiles[3*i+1] = token count, tiles[3*i+2] = batch row; virtual row v of a tile is
 // token v / gc, head v % gc of the block's key/value group (gc = min(group, 128) heads per block).
+//
+// The blocks are persistent: a work item is (tile, key/value head and head chunk), item i being tile n_tiles - 1 - i / ys
+// (within a prompt the later tiles walk more keys, so the long items come first), and every block takes the next item
+// from a counter in global memory when it has finished one. A prompt's first tile walks one tile of keys and its last
+// tile all of them; with one block per item the longest item alone set the kernel's time (32 key tiles in a row for a
+// 2,048-token prompt), now the items spread evenly over the blocks. `work` = {next item, blocks that have finished}:
+// the block that finishes last sets both back to zero for the next launch in the stream.
 __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a,
-                                                               const int* __restrict__ tiles, int gc, int head_chunks) {
+                                                               const int* __restrict__ tiles, int n_work_tiles, int ys, int gc, int head_chunks,
+                                                               int* __restrict__ work) {
     // The swizzled tiles need a 1024-byte aligned base; where dynamic shared memory starts is not promised, so the
     // launch asks for 1 KB more and the base is rounded up.
     extern __shared__ unsigned char smem_raw[];
@@ -190,21 +198,11 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
     unsigned long long* o_done = p_full + 1;          // [1]
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(o_done + 1);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* item_slot = failed + 1;             // [2]: the item of this round and of the next
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // tiles are taken from the end of the list: within a prompt the later tiles walk more keys, and starting the long
-    // ones first leaves the short ones to fill the tail
-    const int tile = gridDim.x - 1 - blockIdx.x;
-    const int tok0 = tiles[3 * tile], ntok = tiles[3 * tile + 1], brow = tiles[3 * tile + 2];
-    const int kvh = blockIdx.y / head_chunks, chunk = blockIdx.y - kvh * head_chunks;
+    const int total_items = n_work_tiles * ys;
     const int group = a.heads / a.kv_heads;
-    const int first_head = kvh * group + chunk * gc;
-    const int heads_here = min(gc, group - chunk * gc);
-    const int* table = a.block_table + (size_t)brow * a.table_width;
-    const int pos_first = a.positions[tok0], pos_last = pos_first + ntok - 1;
-    const int need_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
-    const int start = (need_lo / BN) * BN;
-    const int n_tiles = (pos_last - start) / BN + 1;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
@@ -218,215 +216,255 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // stages whose first tile can be fetched in part start as zeros (see attention_tma.cu)
-    for (int s = 0; s < STAGES && s < n_tiles; ++s) {
-        if (s != n_tiles - 1 && !(s == 0 && need_lo > start)) continue;
-        uint4* k_stage = reinterpret_cast<uint4*>(k_ring + (size_t)s * TILE_BYTES);
-        uint4* v_stage = reinterpret_cast<uint4*>(v_ring + (size_t)s * TILE_BYTES);
-        for (int e = tid; e < TILE_BYTES / 16; e += THREADS) { k_stage[e] = make_uint4(0, 0, 0, 0); v_stage[e] = make_uint4(0, 0, 0, 0); }
-    }
-    wait_for_previous_kernels();  // the queries and the newest keys and values come from the kernel before
-    // queries into the swizzled K-major panels: element (row v, column c) -> panel c / 64, row v, chunk ((c % 64) / 8) ^ (v % 8)
-    for (int e = tid; e < BM * (D / 8); e += THREADS) {
-        const int v = e / (D / 8), cc = e - v * (D / 8);
-        const int tok = v / gc, hh = v - tok * gc;
-        uint4 value = make_uint4(0, 0, 0, 0);
-        if (tok < ntok && hh < heads_here)
-            value = *reinterpret_cast<const uint4*>(a.q + (size_t)(tok0 + tok) * a.q_stride + (size_t)(first_head + hh) * D + cc * 8);
-        *reinterpret_cast<uint4*>(qs + (cc >> 3) * QPANEL + v * 64 + (((cc & 7) ^ (v & 7)) << 3)) = value;
-    }
+    // Pages that a tile does not fetch (beyond the last position, before a window's start) leave under masked keys what
+    // the stage held before: earlier keys and values, which are finite. The rings start as zeros so that this holds for
+    // the first tiles too.
+    for (int e = tid; e < 2 * STAGES * TILE_BYTES / 16; e += THREADS) reinterpret_cast<uint4*>(base)[e] = make_uint4(0, 0, 0, 0);
+    wait_for_previous_kernels();  // the queries and the newest keys and values come from the kernel before; so does the counter's reset
+    if (tid == 0) item_slot[0] = atomicAdd(&work[0], 1);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = *tmem_slot;
+    const int shift = 31 - __clz(a.page_size);
+    const unsigned idesc_s = idesc_for(BN, false), idesc_o = idesc_for(D, true);
+    if (warp == 0 && lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ producer (whole warp)
-        const int shift = 31 - __clz(a.page_size);
-        const int pages_per_tile = BN >> shift;
-        const int ops = pages_per_tile * HALVES;
-        const unsigned page_bytes = (unsigned)a.page_size * D * 2u;  // of one page of K, or of V
-        if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
-        bool alive = true;
-        for (int it = 0; it < n_tiles && alive; ++it) {
-            const int s = it % STAGES, round = it / STAGES;
-            const int tile_base = start + it * BN;
-            int my_page = -1;
-            const int k0 = tile_base + lane * a.page_size;
-            if (lane < pages_per_tile && k0 <= pos_last && k0 + a.page_size - 1 >= need_lo) {
-                const int block = k0 >> shift;
-                const int id = block < a.table_width ? __ldg(table + block) : -1;
-                if (id >= 0 && id < a.pages) my_page = id;
-                else atomicOr(a.status, HB_STATUS_BAD_PAGE);
-            }
-            const unsigned valid = __popc(__ballot_sync(0xffffffffu, my_page >= 0));
-            for (int which = 0; which < 2 && alive; ++which) {  // the K tile, then the V tile
-                unsigned long long* full = which ? &v_full[s] : &k_full[s];
-                int ok = 1;
-                if (lane == 0) ok = mbar_wait(which ? &v_empty[s] : &k_empty[s], (round & 1) ^ 1, failed) ? 1 : 0;
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) { if (lane == 0) *failed = 1; alive = false; break; }
-                if (lane == 0) {
-                    if (valid) mbar_expect_tx(full, valid * page_bytes); else mbar_arrive(full);
-                }
-                __syncwarp();
-                bf16* tile = reinterpret_cast<bf16*>((which ? v_ring : k_ring) + (size_t)s * TILE_BYTES);
-                for (int op0 = 0; op0 < ops; op0 += 32) {
-                    const int op = op0 + lane;
-                    const int p = min(op, ops - 1) / HALVES, h = op % HALVES;
-                    const int page = __shfl_sync(0xffffffffu, my_page, p);
-                    if (op < ops && page >= 0)
-                        tma_load_2d(tile + h * PANEL + p * a.page_size * 64, &kv_map, full, h * 64,
-                                    ((page * 2 + which) * a.kv_heads + kvh) * a.page_size);
-                }
-            }
+    // g0: key tiles of the items before this one. Rings and barriers run on across items: stage g % STAGES, phase by g.
+    int g0 = 0;
+    for (int round = 0;; ++round) {
+        const int item = item_slot[round & 1];
+        if (item >= total_items || *failed) break;  // the same for every thread: both were written before the barrier behind us
+        const int tile = n_work_tiles - 1 - item / ys, y = item % ys;
+        const int tok0 = tiles[3 * tile], ntok = tiles[3 * tile + 1], brow = tiles[3 * tile + 2];
+        const int kvh = y / head_chunks, chunk = y - kvh * head_chunks;
+        const int first_head = kvh * group + chunk * gc;
+        const int heads_here = min(gc, group - chunk * gc);
+        const int* table = a.block_table + (size_t)brow * a.table_width;
+        const int pos_first = a.positions[tok0], pos_last = pos_first + ntok - 1;
+        const int need_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+        const int start = (need_lo / BN) * BN;
+        const int n_tiles = (pos_last - start) / BN + 1;
+
+        // queries into the swizzled K-major panels: element (row v, column c) -> panel c / 64, row v, chunk ((c % 64) / 8) ^ (v % 8)
+        // (every product of the item before has finished: its rows were read out of tensor memory before the barrier behind us)
+        for (int e = tid; e < BM * (D / 8); e += THREADS) {
+            const int v = e / (D / 8), cc = e - v * (D / 8);
+            const int tok = v / gc, hh = v - tok * gc;
+            uint4 value = make_uint4(0, 0, 0, 0);
+            if (tok < ntok && hh < heads_here)
+                value = *reinterpret_cast<const uint4*>(a.q + (size_t)(tok0 + tok) * a.q_stride + (size_t)(first_head + hh) * D + cc * 8);
+            *reinterpret_cast<uint4*>(qs + (cc >> 3) * QPANEL + v * 64 + (((cc & 7) ^ (v & 7)) << 3)) = value;
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ tensor-core issuer (one lane)
-        if (lane == 0) {
-            const unsigned idesc_s = idesc_for(BN, false), idesc_o = idesc_for(D, true);
-            bool ok = true;
-            auto issue_s = [&](int j) {
-                const bf16* ks = reinterpret_cast<const bf16*>(k_ring + (size_t)(j % STAGES) * TILE_BYTES);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+
+        if (warp == 0) {
+            // ------------------------------------------------------------------ producer (whole warp)
+            const int pages_per_tile = BN >> shift;
+            const int ops = pages_per_tile * HALVES;
+            const unsigned page_bytes = (unsigned)a.page_size * D * 2u;  // of one page of K, or of V
+            bool alive = true;
+            for (int it = 0; it < n_tiles && alive; ++it) {
+                const int g = g0 + it, s = g % STAGES, turn = g / STAGES;
+                const int tile_base = start + it * BN;
+                int my_page = -1;
+                const int k0 = tile_base + lane * a.page_size;
+                if (lane < pages_per_tile && k0 <= pos_last && k0 + a.page_size - 1 >= need_lo) {
+                    const int block = k0 >> shift;
+                    const int id = block < a.table_width ? __ldg(table + block) : -1;
+                    if (id >= 0 && id < a.pages) my_page = id;
+                    else atomicOr(a.status, HB_STATUS_BAD_PAGE);
+                }
+                const unsigned valid = __popc(__ballot_sync(0xffffffffu, my_page >= 0));
+                for (int which = 0; which < 2 && alive; ++which) {  // the K tile, then the V tile
+                    unsigned long long* full = which ? &v_full[s] : &k_full[s];
+                    int ok = 1;
+                    if (lane == 0) ok = mbar_wait(which ? &v_empty[s] : &k_empty[s], (turn & 1) ^ 1, failed) ? 1 : 0;
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) { if (lane == 0) *failed = 1; alive = false; break; }
+                    if (lane == 0) {
+                        if (valid) mbar_expect_tx(full, valid * page_bytes); else mbar_arrive(full);
+                    }
+                    __syncwarp();
+                    bf16* stage = reinterpret_cast<bf16*>((which ? v_ring : k_ring) + (size_t)s * TILE_BYTES);
+                    for (int op0 = 0; op0 < ops; op0 += 32) {
+                        const int op = op0 + lane;
+                        const int p = min(op, ops - 1) / HALVES, h = op % HALVES;
+                        const int page = __shfl_sync(0xffffffffu, my_page, p);
+                        if (op < ops && page >= 0)
+                            tma_load_2d(stage + h * PANEL + p * a.page_size * 64, &kv_map, full, h * 64,
+                                        ((page * 2 + which) * a.kv_heads + kvh) * a.page_size);
+                    }
+                }
+            }
+            // the next item, taken while the others still work on this one (they read this round's slot long ago: nobody
+            // passes the barrier at the end of the round before every thread is there)
+            if (lane == 0) item_slot[(round + 1) & 1] = *failed ? total_items : atomicAdd(&work[0], 1);
+        } else if (warp == 1) {
+            // ------------------------------------------------------------------ tensor-core issuer (one lane)
+            if (lane == 0) {
+                bool ok = true;
+                auto issue_s = [&](int g) {
+                    const bf16* ks = reinterpret_cast<const bf16*>(k_ring + (size_t)(g % STAGES) * TILE_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk)
-                    umma(tmem + (j & 1) * BN, desc_k_major(qs + (kk >> 2) * QPANEL) + (unsigned long long)((kk & 3) * 2),
-                         desc_k_major(ks + (kk >> 2) * PANEL) + (unsigned long long)((kk & 3) * 2), idesc_s, kk > 0 ? 1u : 0u);
-                umma_commit(&k_empty[j % STAGES]);  // the K slot is free once this product has read it
-                umma_commit(&s_full[j & 1]);
-            };
-            if (!mbar_wait(&k_full[0], 0, failed)) { *failed = 1; ok = false; }
-            if (ok) { tc_fence_after(); issue_s(0); }
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                if (j + 1 < n_tiles) {
-                    if (!mbar_wait(&k_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
-                    // S(j + 1) lands in the columns that P(j - 1) was read from: the product that read it must be over
-                    if (j > 0 && !mbar_wait(o_done, (j - 1) & 1, failed)) { *failed = 1; ok = false; break; }
+                    for (int kk = 0; kk < D / 16; ++kk)
+                        umma(tmem + (g & 1) * BN, desc_k_major(qs + (kk >> 2) * QPANEL) + (unsigned long long)((kk & 3) * 2),
+                             desc_k_major(ks + (kk >> 2) * PANEL) + (unsigned long long)((kk & 3) * 2), idesc_s, kk > 0 ? 1u : 0u);
+                    umma_commit(&k_empty[g % STAGES]);  // the K slot is free once this product has read it
+                    umma_commit(&s_full[g & 1]);
+                };
+                if (!mbar_wait(&k_full[g0 % STAGES], (g0 / STAGES) & 1, failed)) { *failed = 1; ok = false; }
+                if (ok) { tc_fence_after(); issue_s(g0); }
+                for (int j = 0; j < n_tiles && ok; ++j) {
+                    const int g = g0 + j;
+                    if (j + 1 < n_tiles) {
+                        if (!mbar_wait(&k_full[(g + 1) % STAGES], ((g + 1) / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
+                        // S(g + 1) lands in the columns that P(g - 1) was read from: the product that read it must be over
+                        // (for the item's first tile it is: the item before ended with every product done)
+                        if (j > 0 && !mbar_wait(o_done, (g - 1) & 1, failed)) { *failed = 1; ok = false; break; }
+                        tc_fence_after();
+                        issue_s(g + 1);
+                    }
+                    if (!mbar_wait(p_full, g & 1, failed)) { *failed = 1; ok = false; break; }
+                    if (!mbar_wait(&v_full[g % STAGES], (g / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
                     tc_fence_after();
-                    issue_s(j + 1);
-                }
-                if (!mbar_wait(p_full, j & 1, failed)) { *failed = 1; ok = false; break; }
-                if (!mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
-                tc_fence_after();
-                const bf16* vs = reinterpret_cast<const bf16*>(v_ring + (size_t)(j % STAGES) * TILE_BYTES);
-                // P(j) lies in tensor memory over the first half of S(j)'s columns: 16 keys = 8 columns per product
+                    const bf16* vs = reinterpret_cast<const bf16*>(v_ring + (size_t)(g % STAGES) * TILE_BYTES);
+                    // P(g) lies in tensor memory over the first half of S(g)'s columns: 16 keys = 8 columns per product
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk)
-                    umma_a_in_tmem(tmem + O_COL, tmem + (j & 1) * BN + kk * 8, desc_mn_major(vs, PANEL * 2) + (unsigned long long)(kk * (2048 >> 4)),
-                                   idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&v_empty[j % STAGES]);
-                umma_commit(o_done);
+                    for (int kk = 0; kk < BN / 16; ++kk)
+                        umma_a_in_tmem(tmem + O_COL, tmem + (g & 1) * BN + kk * 8, desc_mn_major(vs, PANEL * 2) + (unsigned long long)(kk * (2048 >> 4)),
+                                       idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(&v_empty[g % STAGES]);
+                    umma_commit(o_done);
+                }
             }
-        }
-    } else {
-        // ------------------------------------------------------------------ softmax: thread = row = tensor-memory lane
-        const int quarter = warp & 3;
-        const int r = quarter * 32 + lane;
-        const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
-        const int tok = r / gc, hh = r - tok * gc;
-        const bool row_valid = tok < ntok && hh < heads_here;
-        const int hi = row_valid ? pos_first + tok : -1;
-        const int lo = (row_valid && a.window > 0) ? max(0, hi - a.window + 1) : 0;
-        float m = -INFINITY, l = 0.f;
-        bool ok = true;
-        for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1;
-            if (!mbar_wait(&s_full[b], (j >> 1) & 1, failed)) { *failed = 1; ok = false; break; }
+        } else {
+            // ------------------------------------------------------------------ softmax: thread = row = tensor-memory lane
+            const int quarter = warp & 3;
+            const int r = quarter * 32 + lane;
+            const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
+            const int tok = r / gc, hh = r - tok * gc;
+            const bool row_valid = tok < ntok && hh < heads_here;
+            const int hi = row_valid ? pos_first + tok : -1;
+            const int lo = (row_valid && a.window > 0) ? max(0, hi - a.window + 1) : 0;
+            float m = -INFINITY, l = 0.f;
+            bool ok = true;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int g = g0 + j, b = g & 1;
+                if (!mbar_wait(&s_full[b], (g >> 1) & 1, failed)) { *failed = 1; ok = false; break; }
+                tc_fence_after();
+                float s[BN];
+                tmem_ld64(lane_addr + b * BN, s);
+                const int tile_base = start + j * BN;
+                float tmax = -INFINITY;
+                if (tile_base + BN - 1 <= hi && tile_base >= lo) {  // every key of the tile is visible to this row
+#pragma unroll
+                    for (int i = 0; i < BN; ++i) {
+                        s[i] *= a.scale_log2;
+                        tmax = fmaxf(tmax, s[i]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < BN; ++i) {
+                        const int pos = tile_base + i;
+                        s[i] = (pos <= hi && pos >= lo) ? s[i] * a.scale_log2 : -INFINITY;
+                        tmax = fmaxf(tmax, s[i]);
+                    }
+                }
+                const float m_new = fmaxf(m, tmax);
+                float alpha = 1.f;
+                if (m == -INFINITY) {
+                    m = m_new;  // nothing visible so far: the row of O holds zeros (or is overwritten by the first product), no rescale
+                } else if (m_new - m > RESCALE_THRESHOLD) {
+                    alpha = exp2f(m - m_new);
+                    m = m_new;
+                }
+                const float m_use = (m == -INFINITY) ? 0.f : m;
+                float sum = 0.f;
+                uint4 packed[BN / 8];
+#pragma unroll
+                for (int c = 0; c < BN / 8; ++c) {
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed[c]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float p0 = fast_exp2(s[c * 8 + 2 * e] - m_use), p1 = fast_exp2(s[c * 8 + 2 * e + 1] - m_use);
+                        sum += p0 + p1;
+                        h2[e] = __floats2bfloat162_rn(p0, p1);
+                    }
+                }
+                l = l * alpha + sum;
+                // P(g) goes into this thread's lane over the columns S(g) came from (the thread holds its S row in registers;
+                // the tensor core writes those columns again only with S(g + 2), issued after the product that reads P(g))
+                const unsigned* words = reinterpret_cast<const unsigned*>(packed);
+                tmem_st16_words(lane_addr + b * BN, words);
+                tmem_st16_words(lane_addr + b * BN + 16, words + 16);
+                // Every thread sees every phase of o_done go by, tile by tile: a wait by parity tells "phase g - 1 is over" only
+                // to a thread that knows phase g - 2 is (a thread two phases behind would read the parity of a later phase as
+                // "not yet" and wait for ever). Here phase g - 2 was waited for one tile ago (or, at an item's second tile, at
+                // the end of the item before) and the product of tile g cannot start before this thread hands P(g) over, so
+                // the barrier is in phase g - 1 or g. The product of tile g - 1 was issued a whole tile ago; the wait is
+                // almost always over at the first look.
+                if (j > 0 && !mbar_wait(o_done, (g - 1) & 1, failed)) { *failed = 1; ok = false; break; }
+                if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                    // O may be rescaled only between two products: the one before is done
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < D; c += 16) {
+                        float o[16];
+                        tmem_ld16(lane_addr + O_COL + c, o);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] *= alpha;
+                        tmem_st16(lane_addr + O_COL + c, o);
+                    }
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full);
+            }
+            // every phase but the item's last was seen in the loop
+            if (ok) ok = mbar_wait(o_done, (g0 + n_tiles - 1) & 1, failed);
+            if (!ok) *failed = 1;
             tc_fence_after();
-            float s[BN];
-            tmem_ld64(lane_addr + b * BN, s);
-            const int tile_base = start + j * BN;
-            float tmax = -INFINITY;
-            if (tile_base + BN - 1 <= hi && tile_base >= lo) {  // every key of the tile is visible to this row
-#pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    s[i] *= a.scale_log2;
-                    tmax = fmaxf(tmax, s[i]);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    const int pos = tile_base + i;
-                    s[i] = (pos <= hi && pos >= lo) ? s[i] * a.scale_log2 : -INFINITY;
-                    tmax = fmaxf(tmax, s[i]);
-                }
-            }
-            const float m_new = fmaxf(m, tmax);
-            float alpha = 1.f;
-            if (m == -INFINITY) {
-                m = m_new;  // nothing visible so far: the row of O holds zeros (or is overwritten by the first product), no rescale
-            } else if (m_new - m > RESCALE_THRESHOLD) {
-                alpha = exp2f(m - m_new);
-                m = m_new;
-            }
-            const float m_use = (m == -INFINITY) ? 0.f : m;
-            float sum = 0.f;
-            uint4 packed[BN / 8];
-#pragma unroll
-            for (int c = 0; c < BN / 8; ++c) {
-                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed[c]);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = fast_exp2(s[c * 8 + 2 * e] - m_use), p1 = fast_exp2(s[c * 8 + 2 * e + 1] - m_use);
-                    sum += p0 + p1;
-                    h2[e] = __floats2bfloat162_rn(p0, p1);
-                }
-            }
-            l = l * alpha + sum;
-            // P(j) goes into this thread's lane over the columns S(j) came from (the thread holds its S row in registers;
-            // the tensor core writes those columns again only with S(j + 2), issued after the product that reads P(j))
-            const unsigned* words = reinterpret_cast<const unsigned*>(packed);
-            tmem_st16_words(lane_addr + b * BN, words);
-            tmem_st16_words(lane_addr + b * BN + 16, words + 16);
-            // Every thread sees every phase of o_done go by, tile by tile: a wait by parity tells "phase j - 1 is over" only
-            // to a thread that knows phase j - 2 is (a thread two phases behind would read the parity of a later phase as
-            // "not yet" and wait for ever). Here phase j - 2 was waited for one tile ago and the product of tile j cannot
-            // start before this thread hands P(j) over, so the barrier is in phase j - 1 or j. The product of tile j - 1
-            // was issued a whole tile ago; the wait is almost always over at the first look.
-            if (j > 0 && !mbar_wait(o_done, (j - 1) & 1, failed)) { *failed = 1; ok = false; break; }
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                // O may be rescaled only between two products: the one before is done
-                tc_fence_after();
+            if (ok) {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
                 for (int c = 0; c < D; c += 16) {
                     float o[16];
                     tmem_ld16(lane_addr + O_COL + c, o);
+                    if (row_valid) {
+                        uint4 w[2];
+                        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(w);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) o[i] *= alpha;
-                    tmem_st16(lane_addr + O_COL + c, o);
+                        for (int i = 0; i < 8; ++i) h2[i] = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv);
+                        uint4* dst = reinterpret_cast<uint4*>(a.out + (size_t)(tok0 + tok) * a.out_stride + (size_t)(first_head + hh) * D + c);
+                        dst[0] = w[0];
+                        dst[1] = w[1];
+                    }
                 }
             }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
         }
-        // every phase but the last was seen in the loop
-        if (ok) ok = mbar_wait(o_done, (n_tiles - 1) & 1, failed);
-        if (!ok) *failed = 1;
+        g0 += n_tiles;
+        // the end of the round: every product of this item is over (the softmax threads saw the last one finish and have
+        // read their rows), the next item's number is in its slot
+        tc_fence_before();
+        __syncthreads();
         tc_fence_after();
-        if (ok) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll
-            for (int c = 0; c < D; c += 16) {
-                float o[16];
-                tmem_ld16(lane_addr + O_COL + c, o);
-                if (row_valid) {
-                    uint4 w[2];
-                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(w);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) h2[i] = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv);
-                    uint4* dst = reinterpret_cast<uint4*>(a.out + (size_t)(tok0 + tok) * a.out_stride + (size_t)(first_head + hh) * D + c);
-                    dst[0] = w[0];
-                    dst[1] = w[1];
-                }
-            }
+    }
+    if (tid == 0) {
+        if (*failed) atomicOr(a.status, HB_STATUS_WAIT_EXPIRED | HB_STATUS_IN_ATTENTION_TCGEN05);
+        __threadfence();
+        if (atomicAdd(&work[1], 1) == (int)gridDim.x - 1) {  // the last block to finish: every block has taken its last number
+            work[0] = 0;
+            work[1] = 0;
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (tid == 0 && *failed) atomicOr(a.status, HB_STATUS_WAIT_EXPIRED | HB_STATUS_IN_ATTENTION_TCGEN05);
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -448,7 +486,7 @@ EncodeTiled encode_tiled() {
     return fn;
 }
 
-constexpr size_t SMEM_USED = 1024 + (size_t)2 * STAGES * TILE_BYTES + (size_t)HALVES * QPANEL * sizeof(bf16) + (4 * STAGES + 4) * 8 + 16;
+constexpr size_t SMEM_USED = 1024 + (size_t)2 * STAGES * TILE_BYTES + (size_t)HALVES * QPANEL * sizeof(bf16) + (4 * STAGES + 4) * 8 + 32;
 // A block holds half of the SM's tensor memory, so two blocks are all an SM can serve. The launch asks for at least
 // 80 KB of shared memory so that no third block becomes resident only to wait for tensor memory: such a block of a
 // kernel launched early (as a programmatic dependent) would hold what a block of the kernel before it still needs.
@@ -462,8 +500,9 @@ HB_EXPORT int hb_attention_tc_tile_rows() { return BM; }
 HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
                                     int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int heads,
                                     int kv_heads, int head_dim, int page_size, int pages, float scale, int window, int* status,
-                                    cudaStream_t stream) {
+                                    int* work, cudaStream_t stream) {
     (void)token_row;
+    if (!work) return HB_BAD_ARGUMENT;
     if (n_tiles <= 0) return 0;
     if (head_dim != D) return HB_UNSUPPORTED_SIZE;
     if (kv_heads <= 0 || heads % kv_heads || q_stride % 8 || out_stride % 8) return HB_BAD_ARGUMENT;
@@ -489,5 +528,13 @@ HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return launch_after_previous(attention_tc_kernel, dim3(n_tiles, kv_heads * head_chunks), THREADS, SMEM_BYTES, stream, map, a, tiles, gc, head_chunks);
+    // two blocks fit an SM (tensor memory, shared memory): that many persistent blocks, or one per item if there are fewer
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+        return HB_BAD_ARGUMENT;
+    const long long items = (long long)n_tiles * kv_heads * head_chunks;
+    if (items > 0x7fffffffLL) return HB_UNSUPPORTED_SIZE;
+    const int blocks = (int)(items < 2LL * sms ? items : 2LL * sms);
+    return launch_after_previous(attention_tc_kernel, dim3(blocks), THREADS, SMEM_BYTES, stream, map, a, tiles, n_tiles, kv_heads * head_chunks, gc,
+                                 head_chunks, work);
 }

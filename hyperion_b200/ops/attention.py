@@ -74,6 +74,19 @@ def choose_splits(n_items: int, heads: int, kv_heads: int, longest_context: int,
     return max(1, min(target // max(1, blocks), key_tiles // 3, 64))
 
 
+_WORK: dict[int, torch.Tensor] = {}
+
+
+def work_counters(device: torch.device) -> torch.Tensor:
+    """Two int32 words per device from which the persistent blocks of the tcgen05 prompt attention take their work items:
+    zero between launches (the kernel's last block sets them back).  Launches on one device follow one another in one
+    stream; two streams launching that kernel at once would share the counter."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _WORK:
+        _WORK[index] = torch.zeros(2, dtype=torch.int32, device=torch.device("cuda", index))
+    return _WORK[index]
+
+
 def _common(q, out, cache, block_table, token_row, positions):
     require_cuda(q, out, cache, block_table, token_row, positions)
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or q.stride(-1) != 1 or not cache.is_contiguous():
@@ -85,9 +98,12 @@ def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n
     _common(q, out, cache, block_table, token_row, positions)
     pages, _, kv_heads, page_size, head_dim = cache.shape
     if uses_tcgen05(head_dim, page_size) and tile_size == 128:
-        entry = library("attention_tcgen05", HB_HEAD_DIM=head_dim).hb_attention_tc_tiles
-    else:
-        entry = _entry(head_dim, page_size, "tiles")
+        check(library("attention_tcgen05", HB_HEAD_DIM=head_dim).hb_attention_tc_tiles(
+            ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table), i32(block_table.shape[1]), ptr(token_row),
+            ptr(positions), ptr(tiles), i32(n_tiles), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale),
+            i32(window or 0), ptr(status_word(q.device)), ptr(work_counters(q.device)), stream_ptr()), "attention_tiles")
+        return
+    entry = _entry(head_dim, page_size, "tiles")
     check(entry(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
                                  i32(block_table.shape[1]), ptr(token_row), ptr(positions), ptr(tiles), i32(n_tiles), i32(heads),
                                  i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale), i32(window or 0),
