@@ -286,27 +286,30 @@ HB_EXPORT int hb_add_rmsnorm(float* h, const void* delta, int delta_is_bf16, con
 }
 
 // ---------------------------------------------------------------- SwiGLU
-// in: [tokens, 2*inter] with the gate in the first `inter` columns and the up projection in the
-// rest; out[t, i] = silu(gate) * up, silu(g) = g / (1 + exp(-g)) in float.
+// in: [tokens, 2*inter]: gate and up columns alternate in blocks of `block` columns (block gate columns, then the block up
+// columns that belong to them; block = inter is the plain arrangement, all gate columns first);
+// out[t, i] = silu(gate_i) * up_i, silu(g) = g / (1 + exp(-g)) in float.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block) {
     const int t = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= inter) return;
-    const float g = to_float(gate_up[(size_t)t * 2 * inter + i]);
-    const float u = to_float(gate_up[(size_t)t * 2 * inter + inter + i]);
+    const size_t at = (size_t)t * 2 * inter + (size_t)(i / block) * 2 * block + i % block;
+    const float g = to_float(gate_up[at]);
+    const float u = to_float(gate_up[at + block]);
     out[(size_t)t * inter + i] = from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
-// bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores, 8 elements per thread.
-__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter) {
+// bfloat16 rows whose width and block are multiples of 8: 16-byte loads and stores, 8 elements per thread.
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter, int block) {
     const int t = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     let_next_kernel_start();
     wait_for_previous_kernels();
     if (i >= inter) return;
-    const uint4 g4 = *reinterpret_cast<const uint4*>(gate_up + (size_t)t * 2 * inter + i);
-    const uint4 u4 = *reinterpret_cast<const uint4*>(gate_up + (size_t)t * 2 * inter + inter + i);
+    const size_t at = (size_t)t * 2 * inter + (size_t)(i / block) * 2 * block + i % block;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gate_up + at);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gate_up + at + block);
     const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
     const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
     uint4 o4;
@@ -319,18 +322,20 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, 
     *reinterpret_cast<uint4*>(out + (size_t)t * inter + i) = o4;
 }
 
-HB_EXPORT int hb_swiglu(const void* gate_up, void* out, int is_bf16, int tokens, int inter, cudaStream_t stream) {
+// block: columns per run of gate (and of up) columns; it divides inter (inter itself: all gate columns first).
+HB_EXPORT int hb_swiglu(const void* gate_up, void* out, int is_bf16, int tokens, int inter, int block, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (tokens > 65535) return HB_UNSUPPORTED_SIZE;
-    if (is_bf16 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+    if (block <= 0 || inter % block) return HB_BAD_ARGUMENT;
+    if (is_bf16 && inter % 8 == 0 && block % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
         dim3 grid8((inter / 8 + 255) / 256, tokens);
-        return launch_after_previous(swiglu_bf16x8_kernel, grid8, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
+        return launch_after_previous(swiglu_bf16x8_kernel, grid8, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block);
     }
     dim3 grid((inter + 255) / 256, tokens);
     if (is_bf16)
-        swiglu_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
+        swiglu_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block);
     else
-        swiglu_kernel<<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter);
+        swiglu_kernel<<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, block);
     return launch_status();
 }
 

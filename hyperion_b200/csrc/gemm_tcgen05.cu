@@ -21,100 +21,9 @@
 // The reference leaves these products to cuBLAS (helios/crates/helios-hal/src/cuda/cublas.rs:158-188,
 // cuda/cublaslt.rs:203-212) and applies bias and SwiGLU in separate kernels
 // (helios/crates/helios-hal/kernels/elementwise.cu:29,134).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "gemm_tcgen05.cuh"
 
 namespace {
-typedef __nv_bfloat16 bf16;
-constexpr int BM = 128, BK = 64, UMMA_K = 16;
-constexpr int THREADS = 192;
-constexpr unsigned WAIT_LIMIT = 1u << 24;
-
-enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
-
-struct GemmParams {
-    void* c;              // output
-    const float* bias_f;  // bias as float (or null)
-    const bf16* bias_h;   // bias as bfloat16 (or null)
-    float* partial;       // split-K partials [splits, rows_out, cols_out] float
-    int m, n, k;          // problem: A [m, k], W [n, k]; output [m, n] (SwiGLU: [m, n / 2])
-    int ldc;              // row stride of the output in elements
-    int k_blocks_per_split;
-    int* status;
-    int w_tiled;          // the weights are stored tile by tile: [n / 128][k / 64][128][64], every 128 x 64 box contiguous
-};
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity; false when the limit ran out or another role failed.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* failed) {
-    const unsigned addr = smem_u32(bar);
-    for (unsigned spin = 0; spin < WAIT_LIMIT; ++spin) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-        if ((spin & 1023) == 1023 && *failed) return false;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-
-// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_u32(tile) & 0x3FFFFu) >> 4);  // start address
-    d |= 1ull << 16;                                               // leading offset: unused for swizzled K-major tiles
-    d |= (unsigned long long)(1024 >> 4) << 32;                    // stride between 8-row groups
-    d |= 1ull << 46;                                               // descriptor version of sm_100
-    d |= 2ull << 61;                                               // 128-byte swizzle
-    return d;
-}
-
-// Instruction descriptor of kind::f16: float accumulator, bfloat16 operands, both K-major, M = 128, N = bn.
-__device__ __forceinline__ unsigned umma_idesc(int bn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// 16 consecutive float columns of this thread's accumulator lane.
-__device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
-    unsigned r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
 template <int BN>
 struct Layout {
     static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -126,10 +35,6 @@ struct Layout {
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     static constexpr size_t smem(int stages) { return 1024 + (size_t)stages * STAGE_BYTES + 256; }
 };
-
-__device__ __forceinline__ float bias_at(const GemmParams& p, int i) {
-    return p.bias_f ? p.bias_f[i] : (p.bias_h ? __bfloat162float(p.bias_h[i]) : 0.f);
-}
 
 // ---------------------------------------------------------------- the swapped shape (at most 64 rows of activations)
 // map_a: the weights, which supply the tile's 128 rows (TMEM lanes); map_b: the activations, which supply its BN columns.
@@ -179,39 +84,39 @@ __global__ void __launch_bounds__(THREADS) gemm_swapped_kernel(const __grid_cons
             for (int i = 0; i < ahead; ++i) {
                 unsigned char* a_tile = tiles + (size_t)i * L::STAGE_BYTES;
                 mbar_expect_tx(&full[i], L::STAGE_BYTES);
-                if (p.w_tiled) tma_load_2d(a_tile, &map_a, &full[i], 0, (blockIdx.x * k_blocks_total + kb_begin + i) * BM);
-                else tma_load_2d(a_tile, &map_a, &full[i], (kb_begin + i) * BK, row0);
+                tma_load_2d(a_tile, &map_a, &full[i], (kb_begin + i) * BK, row0);
             }
             wait_for_previous_kernels();
             for (int i = 0; i < ahead; ++i) {
                 unsigned char* a_tile = tiles + (size_t)i * L::STAGE_BYTES;
                 tma_load_2d(a_tile + L::A_BYTES, &map_b, &full[i], (kb_begin + i) * BK, col0);
             }
+            int s = ahead % stages;
+            unsigned turn = (unsigned)(ahead / stages) & 1u;
             for (int i = ahead; i < n_kb; ++i) {
-                const int s = i % stages;
-                if (!mbar_wait(&empty[s], ((i / stages) & 1) ^ 1, failed)) { *failed = 1; break; }
+                if (!mbar_ready(smem_u32(&empty[s]), turn ^ 1u) && !mbar_wait(&empty[s], turn ^ 1u, failed)) { *failed = 1; break; }
                 unsigned char* a_tile = tiles + (size_t)s * L::STAGE_BYTES;
                 mbar_expect_tx(&full[s], L::STAGE_BYTES);
-                if (p.w_tiled) tma_load_2d(a_tile, &map_a, &full[s], 0, (blockIdx.x * k_blocks_total + kb_begin + i) * BM);
-                else tma_load_2d(a_tile, &map_a, &full[s], (kb_begin + i) * BK, row0);
+                tma_load_2d(a_tile, &map_a, &full[s], (kb_begin + i) * BK, row0);
                 tma_load_2d(a_tile + L::A_BYTES, &map_b, &full[s], (kb_begin + i) * BK, col0);
+                if (++s == stages) { s = 0; turn ^= 1u; }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {  // tensor-core issuer
+        if (lane == 0) {  // tensor-core issuer: descriptors as low words that are only added to, the ring by a counter
             const unsigned idesc = umma_idesc(BN);
+            const unsigned a_low0 = desc_low(tiles), b_low0 = desc_low(tiles + L::A_BYTES), step = (unsigned)L::STAGE_BYTES >> 4;
+            const unsigned full0 = smem_u32(&full[0]), empty0 = smem_u32(&empty[0]);
+            int s = 0;
+            unsigned turn = 0, a_low = a_low0, b_low = b_low0;
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % stages;
-                if (!mbar_wait(&full[s], (i / stages) & 1, failed)) { *failed = 1; ok = false; break; }
-                tc_fence_after();
-                unsigned char* a_tile = tiles + (size_t)s * L::STAGE_BYTES;
-                const unsigned long long da = umma_desc(a_tile), db = umma_desc(a_tile + L::A_BYTES);
-#pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)
-                    umma_bf16(tmem, da + (unsigned long long)(k * UMMA_K * 2 / 16), db + (unsigned long long)(k * UMMA_K * 2 / 16), idesc,
-                              (i > 0 || k > 0) ? 1u : 0u);
-                umma_commit(&empty[s]);  // the stage is free once these products have read it
+            for (int i = 0; i < n_kb; ++i) {
+                if (!mbar_ready(full0 + 8u * (unsigned)s, turn) && !mbar_wait(&full[s], turn, failed)) { *failed = 1; ok = false; break; }
+                umma_stage(tmem, a_low, b_low, idesc, i > 0 ? 1u : 0u);
+                umma_commit_at(empty0 + 8u * (unsigned)s);  // the stage is free once these products have read it
+                a_low += step;
+                b_low += step;
+                if (++s == stages) { s = 0; turn ^= 1u; a_low = a_low0; b_low = b_low0; }
             }
             if (ok) umma_commit(acc_full);
         }
@@ -373,41 +278,41 @@ __global__ void __launch_bounds__(THREADS) gemm_tiles_kernel(const __grid_consta
             }
             wait_for_previous_kernels();
             for (int i = 0; i < ahead; ++i) tma_load_2d(tiles + (size_t)i * L::STAGE_BYTES, &map_x, &full[i], i * BK, (t0 % tiles_m) * BM);
-            int it = ahead;
+            int s = ahead % L::STAGES;
+            unsigned turn = (unsigned)(ahead / L::STAGES) & 1u;
             bool ok = true;
             for (int t = t0; t < total && ok; t += gridDim.x) {
                 const int row0 = (t % tiles_m) * BM, col0 = (t / tiles_m) * BN;
-                for (int kb = (t == t0 ? ahead : 0); kb < k_blocks; ++kb, ++it) {
-                    const int s = it % L::STAGES;
-                    if (!mbar_wait(&empty[s], ((it / L::STAGES) & 1) ^ 1, failed)) { *failed = 1; ok = false; break; }
+                for (int kb = (t == t0 ? ahead : 0); kb < k_blocks; ++kb) {
+                    if (!mbar_ready(smem_u32(&empty[s]), turn ^ 1u) && !mbar_wait(&empty[s], turn ^ 1u, failed)) { *failed = 1; ok = false; break; }
                     unsigned char* a_tile = tiles + (size_t)s * L::STAGE_BYTES;
                     mbar_expect_tx(&full[s], L::STAGE_BYTES);
                     tma_load_2d(a_tile, &map_x, &full[s], kb * BK, row0);
                     tma_load_2d(a_tile + L::A_BYTES, &map_w, &full[s], kb * BK, col0);
+                    if (++s == L::STAGES) { s = 0; turn ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {  // tensor-core issuer
+        if (lane == 0) {  // tensor-core issuer: descriptors as low words that are only added to, the ring by a counter
             const unsigned idesc = umma_idesc(BN);
-            int it = 0;
+            const unsigned a_low0 = desc_low(tiles), b_low0 = desc_low(tiles + L::A_BYTES), step = (unsigned)L::STAGE_BYTES >> 4;
+            const unsigned full0 = smem_u32(&full[0]), empty0 = smem_u32(&empty[0]);
+            int s = 0;
+            unsigned turn = 0, a_low = a_low0, b_low = b_low0;
             bool ok = true;
             for (int t = blockIdx.x, i = 0; t < total && ok; t += gridDim.x, ++i) {
                 const int buf = i & 1;
                 if (!mbar_wait(&acc_empty[buf], ((i >> 1) & 1) ^ 1, failed)) { *failed = 1; ok = false; break; }  // the epilogue has drained it
                 tc_fence_after();
                 const unsigned acc = tmem + buf * L::ACC_STRIDE;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % L::STAGES;
-                    if (!mbar_wait(&full[s], (it / L::STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
-                    tc_fence_after();
-                    unsigned char* a_tile = tiles + (size_t)s * L::STAGE_BYTES;
-                    const unsigned long long da = umma_desc(a_tile), db = umma_desc(a_tile + L::A_BYTES);
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16(acc, da + (unsigned long long)(k * UMMA_K * 2 / 16), db + (unsigned long long)(k * UMMA_K * 2 / 16), idesc,
-                                  (kb > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(&empty[s]);  // the stage is free once these products have read it
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_ready(full0 + 8u * (unsigned)s, turn) && !mbar_wait(&full[s], turn, failed)) { *failed = 1; ok = false; break; }
+                    umma_stage(acc, a_low, b_low, idesc, kb > 0 ? 1u : 0u);
+                    umma_commit_at(empty0 + 8u * (unsigned)s);  // the stage is free once these products have read it
+                    a_low += step;
+                    b_low += step;
+                    if (++s == L::STAGES) { s = 0; turn ^= 1u; a_low = a_low0; b_low = b_low0; }
                 }
                 if (ok) umma_commit(&acc_full[buf]);
             }
@@ -451,47 +356,6 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     sum += bias_f ? bias_f[col] : (bias_h ? __bfloat162float(bias_h[col]) : 0.f);
     if (out_is_f32) reinterpret_cast<float*>(c)[(size_t)row * ldc + col] = sum;
     else reinterpret_cast<bf16*>(c)[(size_t)row * ldc + col] = __float2bfloat16_rn(sum);
-}
-
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_tiled() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* found = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &found, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiled>(found);
-    }
-    return fn;
-}
-
-// A [rows, k] bfloat16 matrix with row stride ld, fetched in boxes of box_rows x 64 elements with the 128-byte swizzle;
-// rows and columns beyond the matrix read as zero.
-int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int box_rows) {
-    EncodeTiled encode = encode_tiled();
-    if (!encode) return HB_BAD_ARGUMENT;
-    if (((uintptr_t)base & 15) || (ld % 8) || box_rows > 256) return HB_UNSUPPORTED_SIZE;
-    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : HB_BAD_ARGUMENT;
-}
-
-int sm_count() {
-    static int count = 0;
-    if (!count) {
-        int device = 0;
-        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
-            count = 148;
-    }
-    return count;
 }
 
 template <int BN, int EPI>
@@ -560,11 +424,10 @@ HB_EXPORT long long hb_gemm_bf16_workspace(int m, int n, int splits) { return sp
 //   workspace of hb_gemm_bf16_workspace(m, n, splits) elements; with leave_partials the sums stay there, [splits, m, n].
 HB_EXPORT int hb_gemm_bf16(const void* a, int lda, const void* w, int ldw, void* c, int ldc, const float* bias_f, const void* bias_h,
                            int m, int n, int k, int epilogue, int batch_tile, int splits, float* workspace, int leave_partials,
-                           int* status, cudaStream_t stream, int w_tiled) {
+                           int* status, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (k <= 0 || splits < 1) return HB_BAD_ARGUMENT;
-    if (w_tiled && (batch_tile == 0 || n % BM || k % BK)) return HB_UNSUPPORTED_SIZE;
-    GemmParams p{c, bias_f, (const bf16*)bias_h, workspace, m, n, k, ldc, 0, status, w_tiled};
+    GemmParams p{c, bias_f, (const bf16*)bias_h, workspace, m, n, k, ldc, 0, status};
     const int k_blocks = (k + BK - 1) / BK;
     CUtensorMap map_x, map_w;
     if (batch_tile == 0) {
@@ -591,7 +454,7 @@ HB_EXPORT int hb_gemm_bf16(const void* a, int lda, const void* w, int ldw, void*
     if (splits > k_blocks) splits = k_blocks;
     if (splits > 1 && !workspace) return HB_BAD_ARGUMENT;
     p.k_blocks_per_split = (k_blocks + splits - 1) / splits;
-    if (int code = w_tiled ? make_map(&map_w, w, (n / BM) * k_blocks * BM, BK, BK, BM) : make_map(&map_w, w, n, k, ldw, BM)) return code;
+    if (int code = make_map(&map_w, w, n, k, ldw, BM)) return code;
     if (int code = make_map(&map_x, a, m, k, lda, batch_tile)) return code;
     dim3 grid((n + BM - 1) / BM, 1, splits);
     const int epi = splits > 1 ? (int)EPI_PARTIAL : epilogue;

@@ -88,17 +88,21 @@ def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float, out_dt
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """[tokens, 2I] (gate columns first) -> silu(gate) * up, [tokens, I]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int | None = None) -> torch.Tensor:
+    """[tokens, 2I] -> silu(gate) * up, [tokens, I].  ``block``: gate and up columns alternate in runs of that many columns
+    (``block`` gate columns, then their up columns); None: all gate columns first."""
     require_cuda(gate_up)
     tokens, twice = gate_up.shape
     inter = twice // 2
+    block = inter if block is None else block
+    if block <= 0 or inter % block:
+        raise KernelError(f"swiglu: runs of {block} columns do not divide {inter}")
     if out is None:
         out = torch.empty((tokens, inter), dtype=gate_up.dtype, device=gate_up.device)
     lib = library("elementwise")
     for start in range(0, tokens, 65535):
         count = min(65535, tokens - start)
-        check(lib.hb_swiglu(ptr(gate_up[start:]), ptr(out[start:]), i32(is_bf16(gate_up)), i32(count), i32(inter), stream_ptr()), "swiglu")
+        check(lib.hb_swiglu(ptr(gate_up[start:]), ptr(out[start:]), i32(is_bf16(gate_up)), i32(count), i32(inter), i32(block), stream_ptr()), "swiglu")
     return out
 
 

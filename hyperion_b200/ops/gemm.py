@@ -18,6 +18,7 @@ from .native import KernelError, check, i32, library, ptr, require_cuda, sm_coun
 
 EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
 SWIGLU_BLOCK = 128  # the fused epilogue wants 128 gate rows followed by their 128 up rows, repeated
+PAIR_MIN_ROWS = 128  # more rows than this: the pair kernel's 256-row tiles (when this package's kernels take a prompt-sized product at all)
 
 
 def supported(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -78,7 +79,7 @@ class SplitSum:
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, epilogue: int = EPI_BF16,
-              out: Optional[torch.Tensor] = None, splits: Optional[int] = None, leave_partials: bool = False, w_tiled: bool = False):
+              out: Optional[torch.Tensor] = None, splits: Optional[int] = None, leave_partials: bool = False):
     """``leave_partials``: when K is split, return a :class:`SplitSum` instead of adding the pieces up."""
     require_cuda(x, w, bias)
     if not supported(x, w):
@@ -109,7 +110,32 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     lib = library("gemm_tcgen05")
     check(lib.hb_gemm_bf16(ptr(x), i32(x.stride(0)), ptr(w), i32(w.stride(0)), ptr(out), i32(out.stride(0)), ptr(bias_f), ptr(bias_h),
                            i32(m), i32(n), i32(k), i32(epilogue), i32(tile), i32(splits), ptr(workspace), i32(leave), ptr(status_word(x.device)),
-                           stream_ptr(), i32(w_tiled)), "gemm_bf16")
+                           stream_ptr()), "gemm_bf16")
     if leave:
         return SplitSum(workspace.view(splits, m, n), bias, out_dtype)
+    return out
+
+
+def gemm_pair_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, epilogue: int = EPI_BF16,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x w^T`` on pairs of SMs (``csrc/gemm_pair_tcgen05.cu``: 256 x BN tiles, ``tcgen05.mma.cta_group::2``), for prompt-sized
+    ``x``; the same operands and epilogues as :func:`gemm_bf16` in its tile shape."""
+    require_cuda(x, w, bias)
+    if not supported(x, w):
+        raise KernelError("gemm_pair_bf16: operands must be bfloat16, K-contiguous, with 16-byte aligned rows")
+    m, k = x.shape
+    n = w.shape[0]
+    out_cols = n // 2 if epilogue == EPI_SWIGLU else n
+    out_dtype = torch.float32 if epilogue == EPI_F32 else torch.bfloat16
+    if out is None:
+        out = torch.empty((m, out_cols), dtype=out_dtype, device=x.device)
+    if out.dtype != out_dtype or out.shape != (m, out_cols) or out.stride(1) != 1:
+        raise KernelError("gemm_pair_bf16: bad output tensor")
+    bias_f = bias if bias is not None and bias.dtype == torch.float32 else None
+    bias_h = bias if bias is not None and bias.dtype == torch.bfloat16 else None
+    if bias is not None and bias_f is None and bias_h is None:
+        raise KernelError("gemm_pair_bf16: the bias is float32 or bfloat16")
+    check(library("gemm_pair_tcgen05").hb_gemm_pair_bf16(ptr(x), i32(x.stride(0)), ptr(w), i32(w.stride(0)), ptr(out), i32(out.stride(0)), ptr(bias_f),
+                                                         ptr(bias_h), i32(m), i32(n), i32(k), i32(epilogue), ptr(status_word(x.device)), stream_ptr()),
+          "gemm_pair_bf16")
     return out

@@ -34,13 +34,12 @@ def gemm_policy() -> str:
 
 
 def _takes_own_kernel(x: torch.Tensor, weight: torch.Tensor, bias, out_dtype) -> bool:
-    """Which bfloat16 products go to the package's tcgen05 kernel.  ``auto``: with a reduction of at least 2,048, the
-    products of up to 16 rows whose weight matrix has at most 65,536 rows (every projection; the output head over a
-    large vocabulary is 0.3 % of a step faster in the library), and the products of up to 64 rows whose weight matrix
-    has at most 4,096 rows (output and down projections).  There the swapped kernel streams the weights as fast as or faster than the library and starts
-    fetching them while the kernel before it still runs (measured on a B200 at the 7B shapes: batch 8 decodes 3 %
-    faster with every product here, batch 64 is fastest with the library's wide products).  Prompt-sized products stay
-    with the library, whose 2-CTA kernels are ahead of this one-CTA kernel."""
+    """Which bfloat16 products go to the package's tcgen05 kernels.  ``auto``: every product of up to 64 rows with a
+    reduction of at least 2,048 (the swapped kernel streams the weights as fast as or faster than the library at every
+    decode batch, measured on a B200 at the 7B shapes: the output head over 152,064 tokens at 8 rows in 163 against 181 us,
+    gate+up at 64 rows in 47 against 50 us, the whole step 4 % faster at batch 32; and it starts fetching weights while
+    the kernel before it still runs).  Prompt-sized products stay with the library, whose kernels are up to 10 % ahead of
+    this package's pair kernel, except gate+up with SwiGLU, which the pair kernel fuses (see ``gated_linear``)."""
     policy = gemm_policy()
     if policy == "library" or out_dtype not in (torch.bfloat16, torch.float32) or not gemm.supported(x, weight):
         return False
@@ -49,8 +48,7 @@ def _takes_own_kernel(x: torch.Tensor, weight: torch.Tensor, bias, out_dtype) ->
     if policy == "own":
         return True
     m, k = x.shape
-    n = weight.shape[0]
-    return k >= 2048 and ((m <= 16 and n <= 65536) or (m <= 64 and n <= 4096))
+    return k >= 2048 and m <= 64
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -68,8 +66,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         raise KernelError(f"linear: weights are float32 or bfloat16, got {weight.dtype}")
     xin = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
     if _takes_own_kernel(xin, weight, bias, out_dtype):
-        return gemm.gemm_bf16(xin, weight, bias, gemm.EPI_F32 if out_dtype == torch.float32 else gemm.EPI_BF16,
-                              leave_partials=may_leave_partials and out_dtype == torch.bfloat16)
+        epilogue = gemm.EPI_F32 if out_dtype == torch.float32 else gemm.EPI_BF16
+        if xin.shape[0] > gemm.PAIR_MIN_ROWS:  # only under HYPERION_B200_GEMM=own: prompt-sized products on pairs of SMs
+            return gemm.gemm_pair_bf16(xin, weight, bias, epilogue)
+        return gemm.gemm_bf16(xin, weight, bias, epilogue, leave_partials=may_leave_partials and out_dtype == torch.bfloat16)
     if not xin.is_contiguous():
         xin = xin.contiguous()
     if out_dtype == torch.bfloat16:
@@ -79,3 +79,28 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if bias is not None:
         y += bias.float()
     return y if out_dtype == torch.float32 else y.to(out_dtype)
+
+
+def fuses_swiglu(m: int, k: int) -> bool:
+    """Whether gate+up of ``m`` rows goes to the pair kernel with SwiGLU in its epilogue: from 512 rows on, when the rows
+    fill their 256-row tiles to 85 % (measured at the 1.5B, 7B and 32B widths: 1.04 to 1.19 times the library's product
+    followed by the SwiGLU kernel from 1,024 rows on, even at 512, behind below)."""
+    policy = gemm_policy()
+    if policy == "library":
+        return False
+    tiles = -(-m // 256)
+    return m >= 512 and m >= 0.85 * tiles * 256
+
+
+def gated_linear(x: torch.Tensor, weight: torch.Tensor, block: Optional[int], out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for a fused gate/up matrix ``weight`` [2I, H].  ``block`` None: the gate rows come first, then
+    the up rows.  ``block`` = 128: rows alternate in runs of 128 gate rows and their 128 up rows
+    (``ops.gemm.interleave_gate_up``), which lets a prompt-sized product apply SwiGLU in the epilogue of the pair kernel, so
+    that the [tokens, 2I] projections never travel to memory and back."""
+    from .basic import swiglu
+
+    out_dtype = out_dtype or x.dtype
+    if (block == gemm.SWIGLU_BLOCK and weight.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+            and gemm.supported(x, weight) and fuses_swiglu(x.shape[0], x.shape[1])):
+        return gemm.gemm_pair_bf16(x, weight, None, gemm.EPI_SWIGLU)
+    return swiglu(linear(x, weight, None, out_dtype), block=block)

@@ -73,3 +73,29 @@ def test_a_row_does_not_depend_on_its_batch():
     for m in (1, 5, 16, 40):
         part = gemm.gemm_bf16(x[:m].to(DEV), w.to(DEV), splits=2)
         assert torch.equal(part, full[:m])
+
+
+@pytest.mark.parametrize("m, n, k", [(256, 256, 64), (200, 520, 328), (2048, 1024, 512), (65, 272, 1096), (700, 136, 72), (1000, 3584, 640)])
+def test_pairs_of_sms_bf16_and_float_outputs(m, n, k):
+    """The cta_group::2 kernel: 256-row tiles shared by two SMs, ragged in every extent, several tiles per pair."""
+    from hyperion_b200.ops import gemm, raise_on_status
+
+    x, w, b = rnd(m, k, seed=21), rnd(n, k, seed=22, scale=0.1), rnd(n, seed=23)
+    want = x.double() @ w.double().t()
+    check(gemm.gemm_pair_bf16(x.to(DEV), w.to(DEV)), want)
+    check(gemm.gemm_pair_bf16(x.to(DEV), w.to(DEV), b.to(DEV)), want + b.double())
+    check(gemm.gemm_pair_bf16(x.to(DEV), w.to(DEV), b.float().to(DEV), epilogue=gemm.EPI_F32), want + b.double(), bf16_out=False)
+    raise_on_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("m, inter, k", [(130, 256, 192), (2048, 1280, 256), (300, 128, 64)])
+def test_pairs_of_sms_fused_swiglu(m, inter, k):
+    from hyperion_b200.ops import gemm, raise_on_status
+
+    x, gate, up = rnd(m, k, seed=26), rnd(inter, k, seed=27, scale=0.2), rnd(inter, k, seed=28, scale=0.2)
+    w = gemm.interleave_gate_up(gate, up)
+    got = gemm.gemm_pair_bf16(x.to(DEV), w.to(DEV), epilogue=gemm.EPI_SWIGLU)
+    g = (x.double() @ gate.double().t()).to(torch.bfloat16).double()  # the projections are rounded before the activation
+    u = (x.double() @ up.double().t()).to(torch.bfloat16).double()
+    check(got, g / (1 + torch.exp(-g)) * u)
+    raise_on_status(torch.device(DEV))

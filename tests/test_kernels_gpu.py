@@ -68,13 +68,40 @@ def test_add_rmsnorm(hidden, eps, out_dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_swiglu(dtype):
-    gate_up = rnd(5, 2 * 330, seed=5, scale=2.0, dtype=dtype)
-    out = ops().swiglu(gate_up.to(DEV))
-    g, u = gate_up.double()[:, :330], gate_up.double()[:, 330:]
+@pytest.mark.parametrize("inter, block", [(330, None), (384, 128), (96, 24), (330, 5)])
+def test_swiglu(dtype, inter, block):
+    """All gate columns first, or gate and up columns alternating in runs of `block` (the layout a fused product wants)."""
+    gate_up = rnd(5, 2 * inter, seed=5, scale=2.0, dtype=dtype)
+    out = ops().swiglu(gate_up.to(DEV), block=block)
+    runs = gate_up.double().view(5, -1, 2, block or inter)
+    g, u = runs[:, :, 0].reshape(5, inter), runs[:, :, 1].reshape(5, inter)
     want = g / (1 + torch.exp(-g)) * u
     tolerance = 1e-6 if dtype == torch.float32 else 2 ** -8
     assert (out.cpu().double() - want).abs().max() <= tolerance * want.abs().max()
+
+
+def test_gate_up_with_swiglu_fused_or_not_gives_the_same_values():
+    """`gated_linear` over an interleaved gate/up matrix: 700 rows take the pair kernel with SwiGLU in its epilogue, 40 rows
+    the swapped product and the SwiGLU kernel; both against float64 with the projections rounded to bfloat16 first."""
+    import importlib
+
+    from hyperion_b200.ops import gemm
+
+    routing = importlib.import_module("hyperion_b200.ops.linear")  # the module: the package's attribute of that name is the function
+    inter, hidden = 384, 2048
+    gate, up = rnd(inter, hidden, seed=31, scale=0.05, dtype=torch.bfloat16), rnd(inter, hidden, seed=32, scale=0.05, dtype=torch.bfloat16)
+    weight = gemm.interleave_gate_up(gate.to(DEV), up.to(DEV))
+    assert routing.fuses_swiglu(700, hidden) and not routing.fuses_swiglu(40, hidden) and not routing.fuses_swiglu(520, hidden)
+    for rows in (700, 40):
+        x = rnd(rows, hidden, seed=33, dtype=torch.bfloat16)
+        got = ops().gated_linear(x.to(DEV), weight, gemm.SWIGLU_BLOCK)
+        g = (x.double() @ gate.double().t()).to(torch.bfloat16).double()
+        u = (x.double() @ up.double().t()).to(torch.bfloat16).double()
+        want = g / (1 + torch.exp(-g)) * u
+        assert (got.cpu().double() - want).abs().max() <= 2 ** -7 * want.abs().max(), rows
+    plain = torch.cat([gate, up]).to(DEV)
+    x = rnd(40, hidden, seed=34, dtype=torch.bfloat16).to(DEV)
+    assert torch.equal(ops().gated_linear(x, plain, None), ops().gated_linear(x, weight, gemm.SWIGLU_BLOCK))  # the layout changes nothing
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -518,7 +518,7 @@ def test_a_routed_feed_forward_and_another_position_encoding(tmp_path):
 # ------------------------------------------------------------------------------------------------
 # A toy mixer whose paged payload is one latent vector per token (not keys and values of heads): it states the shape,
 # the cache manager sizes pages from it, the step hands it its pages and block table.  Nothing in the package knows it.
-LATENT = {"architectures": ["TestLatentLM"], "hidden": 40, "vocab": 89, "inter": 56, "latent": 12, "eps": 1e-6, "max_positions": 256}
+LATENT = {"architectures": ["TestLatentLM"], "hidden": 136, "vocab": 89, "inter": 152, "latent": 24, "eps": 1e-6, "max_positions": 256}
 
 
 def register_latent():
@@ -574,19 +574,23 @@ def register_latent():
     register_architecture(Architecture("TestLatentLM", lambda document: dict(document), spec, lambda config: dict(config)))
 
 
-def latent_plain(c, w, ids):
+def latent_plain(c, w, ids, stored=lambda x: x):
+    """Whole sequence in float64.  ``stored``: applied where the engine stores an activation in its element type (the
+    norms' outputs, the mixer's and the feed-forward's results and what lies between their products): the identity for the
+    exact model, a rounding to bfloat16 to measure what that storage costs this model."""
     w = {k: v.double() for k, v in w.items()}
     t = len(ids)
     h = plain.embedding(w["embed.weight"], torch.tensor(ids))
     causal = torch.arange(t)[None, :] <= torch.arange(t)[:, None]
     for i in range(2):
-        x = plain.rmsnorm(h, w[f"l{i}.n1.weight"], c["eps"])
+        x = stored(plain.rmsnorm(h, w[f"l{i}.n1.weight"], c["eps"]))
         latent, q = x @ w[f"l{i}.mix.c.weight"].t(), x @ w[f"l{i}.mix.q.weight"].t()
         probs = torch.softmax((q @ latent.t()).masked_fill(~causal, float("-inf")), dim=-1)
-        h = h + (probs @ latent) @ w[f"l{i}.mix.o.weight"].t()
-        x = plain.rmsnorm(h, w[f"l{i}.n2.weight"], c["eps"])
-        h = h + plain.swiglu_mlp(x, w[f"l{i}.mlp.gate_proj.weight"], w[f"l{i}.mlp.up_proj.weight"], w[f"l{i}.mlp.down_proj.weight"])
-    return plain.linear(plain.rmsnorm(h, w["norm.weight"], c["eps"]), w["embed.weight"])
+        h = h + stored((probs @ latent) @ w[f"l{i}.mix.o.weight"].t())
+        x = stored(plain.rmsnorm(h, w[f"l{i}.n2.weight"], c["eps"]))
+        gate, up = stored(x @ w[f"l{i}.mlp.gate_proj.weight"].t()), stored(x @ w[f"l{i}.mlp.up_proj.weight"].t())
+        h = h + stored(stored(gate / (1.0 + torch.exp(-gate)) * up) @ w[f"l{i}.mlp.down_proj.weight"].t())
+    return plain.linear(stored(plain.rmsnorm(h, w["norm.weight"], c["eps"])), w["embed.weight"])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -597,7 +601,7 @@ def test_a_toy_mixer_that_keeps_one_latent_per_token_in_pages(tmp_path, dtype):
     from hyperion_b200.weights import read_all, write_model_folder
 
     register_latent()
-    folder = write_model_folder(tmp_path / "latent", "TestLatentLM", LATENT, seed=21, std=0.12)
+    folder = write_model_folder(tmp_path / "latent", "TestLatentLM", LATENT, seed=21, std=0.07)
     weights = read_all(folder)
     engine = Engine.from_folder(folder, dtype=dtype, page_size=8, max_tokens=96, max_requests=3)
     cache = engine.cache
@@ -606,7 +610,17 @@ def test_a_toy_mixer_that_keeps_one_latent_per_token_in_pages(tmp_path, dtype):
     g = torch.Generator().manual_seed(3)
     requests = {name: torch.randint(0, LATENT["vocab"], (n,), generator=g).tolist() for name, n in (("a", 50), ("b", 21), ("c", 40))}
     want = {name: latent_plain(LATENT, weights, ids).numpy() for name, ids in requests.items()}
-    tolerance = 1e-4 if dtype == "float32" else 3e-2
+    if dtype == "float32":
+        tolerance = 1e-4
+    else:
+        # This mixer's keys are its values, which makes it touchy: what rounding its activations to bfloat16 costs is measured
+        # on the plain model, and the engine may be off by that drift times a margin (the rule of the reference's oracle,
+        # helios/crates/helios-hal/src/oracle.rs:186-217: the reference run's own bfloat16 deviation times 1.5).
+        as_bfloat16 = lambda x: x.to(torch.bfloat16).double()
+        drift = max(float(np.abs(latent_plain(LATENT, weights, ids, as_bfloat16).numpy() - want[name]).max() / np.abs(want[name]).max())
+                    for name, ids in requests.items())
+        tolerance = 1.5 * drift
+        assert 0.005 < tolerance < 0.1, tolerance
     fed = {name: 0 for name in requests}
     order, sizes, k = ["a", "b"], [7, 2, 13, 1, 1, 20, 3], 0
     while order:
@@ -620,7 +634,8 @@ def test_a_toy_mixer_that_keeps_one_latent_per_token_in_pages(tmp_path, dtype):
         for entry in entries:
             n = len(entry.tokens)
             ref = want[entry.request][fed[entry.request]:fed[entry.request] + n]
-            assert np.abs(logits[row:row + n] - ref).max() <= tolerance * np.abs(ref).max(), (entry.request, fed[entry.request])
+            error = np.abs(logits[row:row + n] - ref).max() / np.abs(want[entry.request]).max()
+            assert error <= tolerance, (entry.request, fed[entry.request], float(error))
             row += n
             fed[entry.request] += n
             if fed[entry.request] == len(requests[entry.request]):
