@@ -77,32 +77,65 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc, unsigned accumulate) {
+// The lane that issues the products is one thread, and a lone thread runs a few cycles per instruction: descriptor
+// arithmetic between two products is time the tensor cores stand idle. So descriptors are kept as 32-bit low words that
+// are only added to (the high word is the same for K-major and MN-major tiles with the 128-byte swizzle and 8-row groups
+// 1,024 bytes apart), and the products of a tile are issued from one statement.
+constexpr unsigned DESC_HIGH = (unsigned)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ unsigned low_k_major(const void* tile) { return ((smem_u32(tile) & 0x3FFFFu) >> 4) | (1u << 16); }
+__device__ __forceinline__ unsigned low_mn_major(const void* tile, unsigned panel_bytes) { return ((smem_u32(tile) & 0x3FFFFu) >> 4) | ((panel_bytes >> 4) << 16); }
+
+// S = Q K^T over one 64-column panel of the head (4 products of 16 columns); `first` = 0 starts a new S.
+__device__ __forceinline__ void umma_s_panel(unsigned tmem_d, unsigned q_low, unsigned k_low, unsigned idesc, unsigned first) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t"
+        "add.u32 al, %1, 2;\n\t"
+        "add.u32 bl, %2, 2;\n\t"
+        "mov.b64 da, {al, %5};\n\t"
+        "mov.b64 db, {bl, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, q;\n\t"
+        "add.u32 al, %1, 4;\n\t"
+        "add.u32 bl, %2, 4;\n\t"
+        "mov.b64 da, {al, %5};\n\t"
+        "mov.b64 db, {bl, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, q;\n\t"
+        "add.u32 al, %1, 6;\n\t"
+        "add.u32 bl, %2, 6;\n\t"
+        "mov.b64 da, {al, %5};\n\t"
+        "mov.b64 db, {bl, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, q;\n\t}"
+        ::"r"(tmem_d), "r"(q_low), "r"(k_low), "r"(idesc), "r"(first), "r"(DESC_HIGH) : "memory");
 }
-// The same product with the A operand in tensor memory: lane = row, two consecutive bfloat16 of K per 32-bit column.
-__device__ __forceinline__ void umma_a_in_tmem(unsigned tmem_d, unsigned tmem_a, unsigned long long b, unsigned idesc, unsigned accumulate) {
+// O += P V over the 64 keys of a tile: 4 products of 16 keys, P from tensor memory (8 columns per 16 keys), V MN-major
+// (16 keys = two 8-key groups = 2,048 bytes = 128 units of the descriptor's address field).
+__device__ __forceinline__ void umma_pv_tile(unsigned tmem_o, unsigned tmem_p, unsigned v_low, unsigned idesc, unsigned first) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t.reg .b32 bl, pa;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t"
+        "add.u32 bl, %2, 128;\n\t"
+        "add.u32 pa, %1, 8;\n\t"
+        "mov.b64 db, {bl, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], db, %3, q;\n\t"
+        "add.u32 bl, %2, 256;\n\t"
+        "add.u32 pa, %1, 16;\n\t"
+        "mov.b64 db, {bl, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], db, %3, q;\n\t"
+        "add.u32 bl, %2, 384;\n\t"
+        "add.u32 pa, %1, 24;\n\t"
+        "mov.b64 db, {bl, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], db, %3, q;\n\t}"
+        ::"r"(tmem_o), "r"(tmem_p), "r"(v_low), "r"(idesc), "r"(first), "r"(DESC_HIGH) : "memory");
 }
-// K-major operand: rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ unsigned long long desc_k_major(const void* tile) {
-    return (unsigned long long)((smem_u32(tile) & 0x3FFFFu) >> 4) | (1ull << 16) | ((unsigned long long)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// MN-major operand (V as [key][64 columns] panels): panels `panel_bytes` apart along N, 8-key groups 1024 bytes apart along K.
-__device__ __forceinline__ unsigned long long desc_mn_major(const void* tile, unsigned panel_bytes) {
-    return (unsigned long long)((smem_u32(tile) & 0x3FFFFu) >> 4) | ((unsigned long long)(panel_bytes >> 4) << 16) |
-           ((unsigned long long)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+__device__ __forceinline__ void umma_commit_at(unsigned bar_addr) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
 }
 // float accumulator, bfloat16 operands, A K-major, M 128, N n; B MN-major when b_mn.
 __device__ __forceinline__ unsigned idesc_for(int n, bool b_mn) {
@@ -308,14 +341,14 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
             // ------------------------------------------------------------------ tensor-core issuer (one lane)
             if (lane == 0) {
                 bool ok = true;
+                const unsigned q_low = low_k_major(qs), k_low0 = low_k_major(k_ring), v_low0 = low_mn_major(v_ring, PANEL * 2);
+                const unsigned k_empty0 = smem_u32(&k_empty[0]), v_empty0 = smem_u32(&v_empty[0]), s_full0 = smem_u32(&s_full[0]), o_done_at = smem_u32(o_done);
                 auto issue_s = [&](int g) {
-                    const bf16* ks = reinterpret_cast<const bf16*>(k_ring + (size_t)(g % STAGES) * TILE_BYTES);
-#pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk)
-                        umma(tmem + (g & 1) * BN, desc_k_major(qs + (kk >> 2) * QPANEL) + (unsigned long long)((kk & 3) * 2),
-                             desc_k_major(ks + (kk >> 2) * PANEL) + (unsigned long long)((kk & 3) * 2), idesc_s, kk > 0 ? 1u : 0u);
-                    umma_commit(&k_empty[g % STAGES]);  // the K slot is free once this product has read it
-                    umma_commit(&s_full[g & 1]);
+                    const unsigned stage = (unsigned)(g % STAGES), k_low = k_low0 + stage * (TILE_BYTES >> 4);
+                    umma_s_panel(tmem + (g & 1) * BN, q_low, k_low, idesc_s, 0u);
+                    if (HALVES == 2) umma_s_panel(tmem + (g & 1) * BN, q_low + (QPANEL * 2 >> 4), k_low + (PANEL * 2 >> 4), idesc_s, 1u);
+                    umma_commit_at(k_empty0 + 8u * stage);  // the K slot is free once this product has read it
+                    umma_commit_at(s_full0 + 8u * (unsigned)(g & 1));
                 };
                 if (!mbar_wait(&k_full[g0 % STAGES], (g0 / STAGES) & 1, failed)) { *failed = 1; ok = false; }
                 if (ok) { tc_fence_after(); issue_s(g0); }
@@ -332,14 +365,11 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
                     if (!mbar_wait(p_full, g & 1, failed)) { *failed = 1; ok = false; break; }
                     if (!mbar_wait(&v_full[g % STAGES], (g / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
                     tc_fence_after();
-                    const bf16* vs = reinterpret_cast<const bf16*>(v_ring + (size_t)(g % STAGES) * TILE_BYTES);
                     // P(g) lies in tensor memory over the first half of S(g)'s columns: 16 keys = 8 columns per product
-#pragma unroll
-                    for (int kk = 0; kk < BN / 16; ++kk)
-                        umma_a_in_tmem(tmem + O_COL, tmem + (g & 1) * BN + kk * 8, desc_mn_major(vs, PANEL * 2) + (unsigned long long)(kk * (2048 >> 4)),
-                                       idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-                    umma_commit(&v_empty[g % STAGES]);
-                    umma_commit(o_done);
+                    const unsigned stage = (unsigned)(g % STAGES);
+                    umma_pv_tile(tmem + O_COL, tmem + (g & 1) * BN, v_low0 + stage * (TILE_BYTES >> 4), idesc_o, j > 0 ? 1u : 0u);
+                    umma_commit_at(v_empty0 + 8u * stage);
+                    umma_commit_at(o_done_at);
                 }
             }
         } else {
