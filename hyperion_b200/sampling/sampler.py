@@ -1,12 +1,16 @@
 """The sampler: a device kernel that picks one token per row of logits, and a slow host reference of
 the same rule for tests.
 
-The rule, in the reference's order (helios/crates/helios-hal/src/sampler_reference.rs:4-26):
+The rule follows the reference's steps (helios/crates/helios-hal/src/sampler_reference.rs:4-26):
 penalty on generated tokens, division by the temperature, the top-k set (value descending, ties
 to the lower index), the nucleus over that set (smallest prefix whose mass reaches top_p of the
 set's mass), then one uniform draw ``u`` from Philox4x32-10 with key = the request's seed and
-counter = the number of tokens it sampled before; the token is the first, walking the kept tokens
-by ascending index, at which the running mass exceeds ``u`` times the kept mass.
+counter = the number of tokens it sampled before.  One step differs: the token is the first,
+walking the kept tokens by **ascending index**, at which the running mass exceeds ``u`` times the
+kept mass; the reference walks them in its sorted order (value descending) with float32 prefix sums
+in segments of 1,024 (sampler_reference.rs steps 5-7).  The kept set, every token's probability and
+therefore the distribution are the same; a given seed and step may pick another token than the
+reference would.  Walking by index needs no sort of the kept set on the device.
 """
 from __future__ import annotations
 

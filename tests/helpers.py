@@ -33,6 +33,17 @@ TINY_C = Qwen2Config(num_hidden_layers=2, hidden_size=256, intermediate_size=264
                      tie_word_embeddings=False)
 TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
 WEIGHT_STD = 0.06  # larger than an initialiser's 0.02 so that attention is peaked and logits are O(1)
+# The two tiny configurations as the benchmark file states them, sizes and N(0, 0.02) weights and all.  A and B above are
+# harder versions of them (a vocabulary and an intermediate size that are no power of two, longer positions, weights
+# three times as large so that logits are O(1) and attention is peaked); these run their stated workloads once.
+STATED_A = Qwen2Config(num_hidden_layers=2, hidden_size=64, intermediate_size=176, num_attention_heads=4, num_key_value_heads=2,
+                       head_dim=16, vocab_size=256, max_position_embeddings=128, rope_theta=10000.0, rms_norm_eps=1e-6,
+                       tie_word_embeddings=True)
+STATED_B = Qwen2Config(num_hidden_layers=3, hidden_size=192, intermediate_size=384, num_attention_heads=6, num_key_value_heads=1,
+                       head_dim=32, vocab_size=512, max_position_embeddings=256, rope_theta=1e6, rms_norm_eps=1e-5,
+                       tie_word_embeddings=False)
+STATED = {"A": (STATED_A, 0), "B": (STATED_B, 1)}
+STATED_STD = 0.02
 
 # Declared before the first run. float32: the engine's fixed-order float arithmetic against the
 # plain float64 implementation. bfloat16: a few roundings to 8 bits of mantissa (2^-9 relative
@@ -43,6 +54,11 @@ TOLERANCE = {"float32": 2e-5, "bfloat16": 2.5e-2}
 def make_folder(tmp: Path, name: str, std: float = WEIGHT_STD) -> Path:
     config, seed = TINY[name]
     return write_model_folder(Path(tmp) / f"tiny_{name}", "Qwen2ForCausalLM", config, seed, std)
+
+
+def make_stated_folder(tmp: Path, name: str) -> Path:
+    config, seed = STATED[name]
+    return write_model_folder(Path(tmp) / f"stated_{name}", "Qwen2ForCausalLM", config, seed, STATED_STD)
 
 
 def plain_logits(folder: Path, ids, device: str = "cpu") -> np.ndarray:

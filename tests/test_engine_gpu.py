@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import TINY, TOLERANCE, make_folder, plain_logits, random_ids
+from helpers import STATED, TINY, TOLERANCE, make_folder, make_stated_folder, plain_logits, random_ids
 from plain import qwen2_plain
 
 pytestmark = pytest.mark.gpu
@@ -130,6 +130,45 @@ def test_temperature_sampling_follows_the_host_rule_under_chunked_mixed_steps(fo
     # the same seeds give the same tokens whatever else is in the batch
     alone = engine.generate([prompts[2]], params[2])
     assert alone[0] == got[2]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_two_tiny_configurations_as_stated_run_their_stated_workloads(tmp_path, dtype):
+    """The sizes, N(0, 0.02) weights and workloads the benchmark file gives its two tiny configurations: A (seed 0) three
+    prompts of 5, 17 and 31 tokens and 8 greedy tokens each; B (seed 1) four prompts of 1, 9, 40 and 63 tokens in portions
+    of 16 mixed with decoding, 12 tokens at temperature 0.8.  With weights this small the logits are nearly flat, so a
+    greedy choice is held to the plain logits by distance (the plain argmax, or within the tolerance of it), and a sampled
+    one to the host rule."""
+    from hyperion_b200.sampling import SamplingParams, reference_sample
+
+    tolerance = TOLERANCE[dtype]
+    config, _ = STATED["A"]
+    folder = make_stated_folder(tmp_path, "A")
+    prompts = [random_ids(200 + i, n, config.vocab_size) for i, n in enumerate([5, 17, 31])]
+    engine = engine_for(folder, dtype, max_tokens=256)
+    got = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for prompt, tokens in zip(prompts, got):
+        assert len(tokens) == 8
+        logits = plain_logits(folder, prompt + tokens)
+        for i, token in enumerate(tokens):
+            row = logits[len(prompt) + i - 1]
+            assert row.max() - row[token] <= 2 * tolerance * np.abs(row).max()
+    config, _ = STATED["B"]
+    folder = make_stated_folder(tmp_path, "B")
+    prompts = [random_ids(300 + i, n, config.vocab_size) for i, n in enumerate([1, 9, 40, 63])]
+    params = [SamplingParams(temperature=0.8, seed=1000 + i, max_tokens=12, ignore_eos=True) for i in range(4)]
+    engine = engine_for(folder, dtype, max_tokens=512)
+    got = engine.generate(prompts, params, max_batch_tokens=16, prefill_chunk_busy=16)
+    assert [len(g) for g in got] == [12] * 4
+    slack = 1e-5 if dtype == "float32" else 0.05  # how far the draw may lie beyond the interval the plain logits give the token
+    for prompt, tokens, p in zip(prompts, got, params):
+        logits = plain_logits(folder, prompt + tokens)
+        for i, token in enumerate(tokens):
+            want, info = reference_sample(logits[len(prompt) + i - 1], p.validated(), i, tokens[:i])
+            if want != token:
+                kept = info["kept"].tolist()
+                j = kept.index(token)
+                assert (info["cdf"][j - 1] if j else 0.0) - slack <= info["u"] <= info["cdf"][j] + slack
 
 
 def test_top_k_top_p_penalty_through_generate(folders):
