@@ -1,20 +1,24 @@
-// Prompt attention on the 5th-generation tensor cores: causal grouped-query attention of a tile of 128
+// Prompt attention on the 5th-generation tensor cores: causal grouped-query attention of a tile of 256
 // "virtual rows" (tokens x heads of one key/value group) over the paged bfloat16 cache, with S = Q K^T and
-// O += P V issued as tcgen05.mma and S and O living in tensor memory.  Head sizes 64 and 128 (HB_HEAD_DIM),
+// O += P V issued as tcgen05.mma and S, P and O living in tensor memory.  Head sizes 64 and 128 (HB_HEAD_DIM),
 // pages of 8 to 64 tokens.
 //
-// Roles in a block of 192 threads:
-//   warp 0      producer: one cp.async.bulk.tensor per page and 64-column panel into a ring of key/value stages
-//               (the same layout and barriers as attention_tma.cu);
-//   warp 1      owns tensor memory and issues the products: S_j = Q K_j^T (M 128, N 64, K = head size) into one of
-//               two S buffers, and O += P_j V_j (M 128, N = head size, K 64) with V as an MN-major operand.  S_{j+1}
-//               is issued before P_j is waited for, so the tensor cores work while the softmax warps do;
-//   warps 2-5   softmax: thread r owns row r (tensor-memory lane r).  It reads S_j with tcgen05.ld, masks and scales
-//               into the exp2 domain, keeps a running maximum and sum in float, writes P_j as bfloat16 into shared
-//               memory in the swizzled K-major layout the product wants (after the previous product has finished
-//               with that buffer), and rescales O in tensor memory only when
-//               the maximum has grown by more than 2^8 (until then the stale maximum is kept, which changes no
-//               result: the final division uses the same maximum for numerator and denominator).
+// One block per SM holds all of the SM's tensor memory and works on two halves of 128 rows (H and L) that walk the
+// same key tiles of 128 keys.  While the softmax threads of one half work on their S, the tensor core runs the other
+// half's products, so neither stands still for long:
+//   warp 0      producer: one cp.async.bulk.tensor per page and 64-column panel into rings of key and of value tiles;
+//   warp 1      issues the products, per key tile and half: O_x += P_x V (M 128, N = head size, K 128, P read from
+//               tensor memory, V an MN-major operand) as soon as the half's softmax threads have handed P over, then
+//               at once S_x = Q_x K_next^T (M 128, N 128, K = head size) into the columns P_x was read from (products
+//               of one thread run in the order they were issued);
+//   warps 2-5   softmax of half H, warps 6-9 of half L: thread r owns row r (tensor-memory lane r).  It reads its S row
+//               with tcgen05.ld, masks, keeps a running maximum and sum in float, writes P as bfloat16 over the first
+//               half of S's columns, and rescales O only when the maximum has grown by more than 2^8 (until then the
+//               stale maximum is kept, which changes no result: the final division uses the same maximum for
+//               numerator and denominator).
+// A product of 64 keys cannot feed the tensor core: it is bound by reading Q out of shared memory (measured: 54 clocks
+// for M 128, N 64, K 16 against 64 for N 128, which does twice the arithmetic), and the hand-overs between the roles
+// cost the same per tile whatever its width; hence tiles of 128 keys.
 // Every mbarrier wait is bounded; a wait that runs out sets HB_STATUS_WAIT_EXPIRED, all roles leave their loops, the block
 // takes no further item, tensor memory is freed and the block returns.
 //
@@ -32,18 +36,17 @@ namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int D = HB_HEAD_DIM;
 static_assert(D == 64 || D == 128, "the tcgen05 attention takes head sizes 64 and 128");
-constexpr int BM = 128;                       // virtual rows per block = tensor-memory lanes
-constexpr int BN = 64;                        // keys per tile
-constexpr int HALVES = D / 64;
-constexpr int PANEL = BN * 64;                // elements of a 64-key x 64-column panel (8 KB)
-constexpr int QPANEL = BM * 64;               // elements of a 128-row x 64-column panel of Q (16 KB)
-constexpr int TILE_ELEMS = HALVES * PANEL;
-constexpr int TILE_BYTES = TILE_ELEMS * 2;      // one K or one V tile
-constexpr int STAGES = 2;                     // K tiles and V tiles have rings of their own: a K slot is free as soon as S is done,
-                                              // so K is fetched two tiles ahead; with one P buffer two blocks fit an SM (2 x 112 KB)
-constexpr int THREADS = 192;
-constexpr int TMEM_COLS = 256;                // S0 [0,64) S1 [64,128) O [128,128+D)
-constexpr int O_COL = 128;
+constexpr int BM = 128;                       // rows of one half = tensor-memory lanes
+constexpr int ROWS = 2 * BM;                  // virtual rows of a tile
+constexpr int BN = 128;                       // keys per tile
+constexpr int PANELS = D / 64;
+constexpr int KV_PANEL = BN * 64;             // elements of a 128-key x 64-column panel (16 KB)
+constexpr int Q_PANEL = ROWS * 64;            // elements of a 256-row x 64-column panel of Q (32 KB)
+constexpr int TILE_BYTES = PANELS * KV_PANEL * 2;  // one K or one V tile
+constexpr int STAGES = 2;                     // K tiles and V tiles have rings of their own: a K slot is free as soon as both S are done
+constexpr int THREADS = 320;
+constexpr int TMEM_COLS = 512;                // S_H [0,128) S_L [128,256) O_H [256,256+D) O_L [384,384+D); P_x over S_x's first 64 columns
+constexpr int O_COL = 256;
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 constexpr float RESCALE_THRESHOLD = 8.0f;     // in the exp2 domain
 
@@ -75,12 +78,16 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // The lane that issues the products is one thread, and a lone thread runs a few cycles per instruction: descriptor
 // arithmetic between two products is time the tensor cores stand idle. So descriptors are kept as 32-bit low words that
 // are only added to (the high word is the same for K-major and MN-major tiles with the 128-byte swizzle and 8-row groups
-// 1,024 bytes apart), and the products of a tile are issued from one statement.
+// 1,024 bytes apart), and four products are issued from one statement.
 constexpr unsigned DESC_HIGH = (unsigned)(1024 >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ unsigned low_k_major(const void* tile) { return ((smem_u32(tile) & 0x3FFFFu) >> 4) | (1u << 16); }
 __device__ __forceinline__ unsigned low_mn_major(const void* tile, unsigned panel_bytes) { return ((smem_u32(tile) & 0x3FFFFu) >> 4) | ((panel_bytes >> 4) << 16); }
@@ -111,9 +118,9 @@ __device__ __forceinline__ void umma_s_panel(unsigned tmem_d, unsigned q_low, un
         "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, q;\n\t}"
         ::"r"(tmem_d), "r"(q_low), "r"(k_low), "r"(idesc), "r"(first), "r"(DESC_HIGH) : "memory");
 }
-// O += P V over the 64 keys of a tile: 4 products of 16 keys, P from tensor memory (8 columns per 16 keys), V MN-major
+// O += P V over 64 keys: 4 products of 16 keys, P from tensor memory (8 columns per 16 keys), V MN-major
 // (16 keys = two 8-key groups = 2,048 bytes = 128 units of the descriptor's address field).
-__device__ __forceinline__ void umma_pv_tile(unsigned tmem_o, unsigned tmem_p, unsigned v_low, unsigned idesc, unsigned first) {
+__device__ __forceinline__ void umma_pv_64(unsigned tmem_o, unsigned tmem_p, unsigned v_low, unsigned idesc, unsigned first) {
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t.reg .b32 bl, pa;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
@@ -152,7 +159,7 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 // 64 consecutive float columns of this thread's lane in one instruction.
-__device__ __forceinline__ void tmem_ld64(unsigned taddr, float (&v)[64]) {
+__device__ __forceinline__ void tmem_ld64(unsigned taddr, float* v) {
     unsigned r[64];
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
@@ -176,6 +183,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ unsigned pack_bf16x2(float lo, float hi) {
+    unsigned w;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
+    return w;
+}
 __device__ __forceinline__ void tmem_st16(unsigned taddr, const float (&v)[16]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
                  ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
@@ -184,7 +196,6 @@ __device__ __forceinline__ void tmem_st16(unsigned taddr, const float (&v)[16]) 
                    "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
                  : "memory");
 }
-
 __device__ __forceinline__ void tmem_st16_words(unsigned taddr, const unsigned* v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
                  ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
@@ -200,20 +211,23 @@ struct AttnArgs {
     int heads, kv_heads, page_size, pages, window;
     float scale_log2;
     int* status;
+    int wide_stores;  // rows of the output start on 32-byte boundaries
 };
 
 // tiles[3*i] = first token (flat index), tiles[3*i+1] = token count, tiles[3*i+2] = batch row; virtual row v of a tile is
-// token v / gc, head v % gc of the block's key/value group (gc = min(group, 128) heads per block).
+// token v / gc, head v % gc of the block's key/value group (gc = min(group, 256) heads per block); rows 0-127 are half
+// H, rows 128-255 half L. A tile of at most 128 rows runs half H alone.
 //
 // The blocks are persistent: a work item is (tile, key/value head and head chunk), item i being tile n_tiles - 1 - i / ys
 // (within a prompt the later tiles walk more keys, so the long items come first), and every block takes the next item
 // from a counter in global memory when it has finished one. A prompt's first tile walks one tile of keys and its last
-// tile all of them; with one block per item the longest item alone set the kernel's time (32 key tiles in a row for a
-// 2,048-token prompt), now the items spread evenly over the blocks. `work` = {next item, blocks that have finished}:
-// the block that finishes last sets both back to zero for the next launch in the stream.
-__global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a,
-                                                               const int* __restrict__ tiles, int n_work_tiles, int ys, int gc, int head_chunks,
-                                                               int* __restrict__ work) {
+// tile all of them; with one block per item the longest item alone would set the kernel's time, now the items spread
+// evenly over the blocks. `work` = {next item, blocks that have finished}: the block that finishes last sets both back
+// to zero for the next launch in the stream.
+__global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map,
+                                                                  const AttnArgs a,
+                                                                  const int* __restrict__ tiles, int n_work_tiles, int ys, int gc, int head_chunks,
+                                                                  int* __restrict__ work) {
     // The swizzled tiles need a 1024-byte aligned base; where dynamic shared memory starts is not promised, so the
     // launch asks for 1 KB more and the base is rounded up.
     extern __shared__ unsigned char smem_raw[];
@@ -221,40 +235,64 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
     let_next_kernel_start();
     unsigned char* k_ring = base;                                                   // STAGES K tiles
     unsigned char* v_ring = base + (size_t)STAGES * TILE_BYTES;                     // STAGES V tiles
-    bf16* qs = reinterpret_cast<bf16*>(base + (size_t)2 * STAGES * TILE_BYTES);     // HALVES panels of 128 rows x 64
-    unsigned long long* k_full = reinterpret_cast<unsigned long long*>(qs + HALVES * QPANEL);
+    bf16* qs = reinterpret_cast<bf16*>(base + (size_t)2 * STAGES * TILE_BYTES);     // PANELS panels of 256 rows x 64
+    unsigned long long* k_full = reinterpret_cast<unsigned long long*>(qs + PANELS * Q_PANEL);
     unsigned long long* k_empty = k_full + STAGES;
     unsigned long long* v_full = k_empty + STAGES;
     unsigned long long* v_empty = v_full + STAGES;
-    unsigned long long* s_full = v_empty + STAGES;    // [2]
-    unsigned long long* p_full = s_full + 2;          // [1]
-    unsigned long long* o_done = p_full + 1;          // [1]
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(o_done + 1);
+    unsigned long long* s_full = v_empty + STAGES;    // [2]: per half
+    unsigned long long* p_full = s_full + 2;          // [2]
+    unsigned long long* o_done = p_full + 2;          // [2]
+    unsigned long long* q_full = o_done + 2;          // [1]: the item's queries have landed
+    unsigned long long* q_empty = q_full + 1;         // [1]: the item's last S has been computed
+    unsigned long long* round_done = q_empty + 1;     // [1]: the eight softmax warps have finished the item
+    unsigned long long* q_seen = round_done + 1;      // [1]: the eight softmax warps have seen the item's queries land
+    const int total_items = n_work_tiles * ys;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(q_seen + 1);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    volatile int* item_slot = failed + 1;             // [2]: the item of this round and of the next
+    // [4][5]: the items in flight, each with what every thread wants to know of it (item, first token, token count, batch
+    // row, first position), fetched by the producer while the item before is still being worked on
+    volatile int* item_slot = failed + 1;
+    auto take_item = [&](int slot) {  // one thread
+        const int item = *failed ? total_items : atomicAdd(&work[0], 1);
+        volatile int* info = item_slot + 5 * slot;
+        info[0] = item;
+        if (item < total_items) {
+            const int tile = n_work_tiles - 1 - item / ys;
+            const int tok0 = tiles[3 * tile];
+            info[1] = tok0;
+            info[2] = tiles[3 * tile + 1];
+            info[3] = tiles[3 * tile + 2];
+            info[4] = a.positions[tok0];
+        }
+    };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int total_items = n_work_tiles * ys;
     const int group = a.heads / a.kv_heads;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-        for (int b = 0; b < 2; ++b) mbar_init(&s_full[b], 1);
-        mbar_init(p_full, 4);
-        mbar_init(o_done, 1);
+        for (int x = 0; x < 2; ++x) { mbar_init(&s_full[x], 1); mbar_init(&p_full[x], 4); mbar_init(&o_done[x], 1); }
+        mbar_init(q_full, 1);
+        mbar_init(q_empty, 1);
+        mbar_init(round_done, 8);
+        mbar_init(q_seen, 8);
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // Pages that a tile does not fetch (beyond the last position, before a window's start) leave under masked keys what
+    // the stage held before: earlier keys and values, which are finite. The rings start as zeros so that this holds for
+    // the first tiles too. The rows of Q that no copy writes (beyond tokens x heads of a tile) are never stored; they start
+    // as zeros all the same.
+    for (int e = tid; e < (2 * STAGES * TILE_BYTES + PANELS * Q_PANEL * 2) / 16; e += THREADS) reinterpret_cast<uint4*>(base)[e] = make_uint4(0, 0, 0, 0);
+    wait_for_previous_kernels();  // the queries and the newest keys and values come from the kernel before; so does the counter's reset
+    // All of the SM's tensor memory, and only now: a block of a kernel further back in the stream that has yet to start
+    // on this SM can no longer want any.
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // Pages that a tile does not fetch (beyond the last position, before a window's start) leave under masked keys what
-    // the stage held before: earlier keys and values, which are finite. The rings start as zeros so that this holds for
-    // the first tiles too.
-    for (int e = tid; e < 2 * STAGES * TILE_BYTES / 16; e += THREADS) reinterpret_cast<uint4*>(base)[e] = make_uint4(0, 0, 0, 0);
-    wait_for_previous_kernels();  // the queries and the newest keys and values come from the kernel before; so does the counter's reset
-    if (tid == 0) item_slot[0] = atomicAdd(&work[0], 1);
+    if (tid == 0) take_item(0);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
     __syncthreads();
@@ -262,53 +300,80 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
     const unsigned tmem = *tmem_slot;
     const int shift = 31 - __clz(a.page_size);
     const unsigned idesc_s = idesc_for(BN, false), idesc_o = idesc_for(D, true);
-    if (warp == 0 && lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
+    if (warp == 0 && lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
+    }
+    const int tokens_per_tile = ROWS / gc;
 
-    // g0: key tiles of the items before this one. Rings and barriers run on across items: stage g % STAGES, phase by g.
-    int g0 = 0;
-    for (int round = 0;; ++round) {
-        const int item = item_slot[round & 1];
-        if (item >= total_items || *failed) break;  // the same for every thread: both were written before the barrier behind us
-        const int tile = n_work_tiles - 1 - item / ys, y = item % ys;
-        const int tok0 = tiles[3 * tile], ntok = tiles[3 * tile + 1], brow = tiles[3 * tile + 2];
-        const int kvh = y / head_chunks, chunk = y - kvh * head_chunks;
-        const int first_head = kvh * group + chunk * gc;
-        const int heads_here = min(gc, group - chunk * gc);
-        const int* table = a.block_table + (size_t)brow * a.table_width;
-        const int pos_first = a.positions[tok0], pos_last = pos_first + ntok - 1;
-        const int need_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
-        const int start = (need_lo / BN) * BN;
-        const int n_tiles = (pos_last - start) / BN + 1;
+    // The roles run through the items each at its own pace, held together by the barriers of the data alone: the producer
+    // fetches the next item's keys while the last tiles of this one are worked on, its queries as soon as this item's last
+    // S has been issued, and the first S of the next item follows the last product of this one without a pause.
+    // g0: key tiles of the items before this one; the rings of K and V run on across items (stage g % STAGES, phase by g).
+    // h0[x]: key tiles half x has seen; its three barriers change phase once per tile of an item the half takes part in.
+    struct Item { int tok0, ntok, kvh, first_head, heads_here, pos_first, pos_last, need_lo, start, n_tiles, halves; const int* table; };
+    auto read_item = [&](int round, Item& it) -> bool {  // false: no item left
+        volatile int* info = item_slot + 5 * (round & 3);
+        const int item = info[0];
+        if (item >= total_items) return false;
+        const int y = item % ys;
+        it.tok0 = info[1];
+        it.ntok = info[2];
+        it.table = a.block_table + (size_t)info[3] * a.table_width;
+        it.kvh = y / head_chunks;
+        const int chunk = y - it.kvh * head_chunks;
+        it.first_head = it.kvh * group + chunk * gc;
+        it.heads_here = min(gc, group - chunk * gc);
+        it.pos_first = info[4];
+        it.pos_last = it.pos_first + it.ntok - 1;
+        it.need_lo = a.window > 0 ? max(0, it.pos_first - a.window + 1) : 0;
+        it.start = (it.need_lo / BN) * BN;
+        it.n_tiles = (it.pos_last - it.start) / BN + 1;
+        it.halves = it.ntok * gc > BM ? 2 : 1;
+        return true;
+    };
 
-        // queries into the swizzled K-major panels: element (row v, column c) -> panel c / 64, row v, chunk ((c % 64) / 8) ^ (v % 8)
-        // (every product of the item before has finished: its rows were read out of tensor memory before the barrier behind us)
-        for (int e = tid; e < BM * (D / 8); e += THREADS) {
-            const int v = e / (D / 8), cc = e - v * (D / 8);
-            const int tok = v / gc, hh = v - tok * gc;
-            uint4 value = make_uint4(0, 0, 0, 0);
-            if (tok < ntok && hh < heads_here)
-                value = *reinterpret_cast<const uint4*>(a.q + (size_t)(tok0 + tok) * a.q_stride + (size_t)(first_head + hh) * D + cc * 8);
-            *reinterpret_cast<uint4*>(qs + (cc >> 3) * QPANEL + v * 64 + (((cc & 7) ^ (v & 7)) << 3)) = value;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        tc_fence_before();
-        __syncthreads();
-        tc_fence_after();
-
-        if (warp == 0) {
-            // ------------------------------------------------------------------ producer (whole warp)
-            const int pages_per_tile = BN >> shift;
-            const int ops = pages_per_tile * HALVES;
-            const unsigned page_bytes = (unsigned)a.page_size * D * 2u;  // of one page of K, or of V
-            bool alive = true;
-            for (int it = 0; it < n_tiles && alive; ++it) {
-                const int g = g0 + it, s = g % STAGES, turn = g / STAGES;
-                const int tile_base = start + it * BN;
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer (whole warp)
+        const int pages_per_tile = BN >> shift;
+        const int ops = pages_per_tile * PANELS;
+        const unsigned page_bytes = (unsigned)a.page_size * D * 2u;  // of one page of K, or of V
+        bool alive = true;
+        int g0 = 0;
+        for (int round = 0; alive; ++round) {
+            Item it;
+            __syncwarp();  // lane 0 wrote the item's slot
+            if (!read_item(round, it)) {
+                // the others learn from the slot that nothing is left; this phase of q_full, like every other, may only
+                // complete once every waiter has seen the one before
+                if (lane == 0) {
+                    if (mbar_wait(q_empty, (round & 1) ^ 1, failed) && mbar_wait(q_seen, (round & 1) ^ 1, failed)) mbar_arrive(q_full);
+                    else *failed = 1;
+                }
+                break;
+            }
+            // The item's queries: a box of (64 columns, gc heads, tokens of a tile) per panel lands as rows token x head of
+            // 128 bytes, swizzled like every K-major operand. Tokens beyond the tile's own (another request's, or none) and
+            // heads beyond the group's come along or are filled with zeros; their rows are never stored. The buffer is free
+            // once the last S of the item before has been computed. And every thread that waits for q_full has to have seen
+            // the phase before go by: an item of one key tile has its only S issued before the softmax threads need look
+            // at their barrier, and a phase that completes twice behind a waiter's back looks to it like one that has not.
+            if (lane == 0) {
+                if (!mbar_wait(q_empty, (round & 1) ^ 1, failed) || !mbar_wait(q_seen, (round & 1) ^ 1, failed)) { *failed = 1; alive = false; }
+                if (alive) {
+                    mbar_expect_tx(q_full, (unsigned)(PANELS * 128 * gc * tokens_per_tile));
+                    for (int h = 0; h < PANELS; ++h) tma_load_3d(qs + h * Q_PANEL, &q_map, q_full, h * 64, it.first_head, it.tok0);
+                }
+            }
+            alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
+            for (int t = 0; t < it.n_tiles && alive; ++t) {
+                const int g = g0 + t, s = g % STAGES, turn = g / STAGES;
+                const int tile_base = it.start + t * BN;
                 int my_page = -1;
                 const int k0 = tile_base + lane * a.page_size;
-                if (lane < pages_per_tile && k0 <= pos_last && k0 + a.page_size - 1 >= need_lo) {
+                if (lane < pages_per_tile && k0 <= it.pos_last && k0 + a.page_size - 1 >= it.need_lo) {
                     const int block = k0 >> shift;
-                    const int id = block < a.table_width ? __ldg(table + block) : -1;
+                    const int id = block < a.table_width ? __ldg(it.table + block) : -1;
                     if (id >= 0 && id < a.pages) my_page = id;
                     else atomicOr(a.status, HB_STATUS_BAD_PAGE);
                 }
@@ -326,164 +391,205 @@ __global__ void __launch_bounds__(THREADS) attention_tc_kernel(const __grid_cons
                     bf16* stage = reinterpret_cast<bf16*>((which ? v_ring : k_ring) + (size_t)s * TILE_BYTES);
                     for (int op0 = 0; op0 < ops; op0 += 32) {
                         const int op = op0 + lane;
-                        const int p = min(op, ops - 1) / HALVES, h = op % HALVES;
+                        const int p = min(op, ops - 1) / PANELS, h = op % PANELS;
                         const int page = __shfl_sync(0xffffffffu, my_page, p);
                         if (op < ops && page >= 0)
-                            tma_load_2d(stage + h * PANEL + p * a.page_size * 64, &kv_map, full, h * 64,
-                                        ((page * 2 + which) * a.kv_heads + kvh) * a.page_size);
+                            tma_load_2d(stage + h * KV_PANEL + p * a.page_size * 64, &kv_map, full, h * 64,
+                                        ((page * 2 + which) * a.kv_heads + it.kvh) * a.page_size);
                     }
                 }
             }
-            // the next item, taken while the others still work on this one (they read this round's slot long ago: nobody
-            // passes the barrier at the end of the round before every thread is there)
-            if (lane == 0) item_slot[(round + 1) & 1] = *failed ? total_items : atomicAdd(&work[0], 1);
-        } else if (warp == 1) {
-            // ------------------------------------------------------------------ tensor-core issuer (one lane)
-            if (lane == 0) {
-                bool ok = true;
-                const unsigned q_low = low_k_major(qs), k_low0 = low_k_major(k_ring), v_low0 = low_mn_major(v_ring, PANEL * 2);
-                const unsigned k_empty0 = smem_u32(&k_empty[0]), v_empty0 = smem_u32(&v_empty[0]), s_full0 = smem_u32(&s_full[0]), o_done_at = smem_u32(o_done);
-                auto issue_s = [&](int g) {
-                    const unsigned stage = (unsigned)(g % STAGES), k_low = k_low0 + stage * (TILE_BYTES >> 4);
-                    umma_s_panel(tmem + (g & 1) * BN, q_low, k_low, idesc_s, 0u);
-                    if (HALVES == 2) umma_s_panel(tmem + (g & 1) * BN, q_low + (QPANEL * 2 >> 4), k_low + (PANEL * 2 >> 4), idesc_s, 1u);
-                    umma_commit_at(k_empty0 + 8u * stage);  // the K slot is free once this product has read it
-                    umma_commit_at(s_full0 + 8u * (unsigned)(g & 1));
-                };
-                if (!mbar_wait(&k_full[g0 % STAGES], (g0 / STAGES) & 1, failed)) { *failed = 1; ok = false; }
-                if (ok) { tc_fence_after(); issue_s(g0); }
+            g0 += it.n_tiles;
+            // the next item and what the others want to know of it; its slot was last read four items ago
+            if (lane == 0 && alive) take_item((round + 1) & 3);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ tensor-core issuer (one lane)
+        if (lane == 0) {
+            bool ok = true;
+            const unsigned q_low0 = low_k_major(qs), k_low0 = low_k_major(k_ring), v_low0 = low_mn_major(v_ring, KV_PANEL * 2);
+            const unsigned k_empty0 = smem_u32(&k_empty[0]), v_empty0 = smem_u32(&v_empty[0]), s_full0 = smem_u32(&s_full[0]), o_done0 = smem_u32(&o_done[0]);
+            const unsigned q_empty_at = smem_u32(q_empty);
+            auto issue_s = [&](int x, int g) {  // S_x = Q_x K(g)^T
+                const unsigned k_low = k_low0 + (unsigned)(g % STAGES) * (TILE_BYTES >> 4), q_low = q_low0 + (unsigned)x * (BM * 128 >> 4);
+                umma_s_panel(tmem + x * BN, q_low, k_low, idesc_s, 0u);
+                if (PANELS == 2) umma_s_panel(tmem + x * BN, q_low + (Q_PANEL * 2 >> 4), k_low + (KV_PANEL * 2 >> 4), idesc_s, 1u);
+                umma_commit_at(s_full0 + 8u * (unsigned)x);
+            };
+            auto issue_pv = [&](int x, int g, unsigned accumulate) {  // O_x (+)= P_x V(g); P_x lies over the first 64 columns of S_x
+                const unsigned v_low = v_low0 + (unsigned)(g % STAGES) * (TILE_BYTES >> 4);
+                umma_pv_64(tmem + O_COL + x * BM, tmem + x * BN, v_low, idesc_o, accumulate);
+                umma_pv_64(tmem + O_COL + x * BM, tmem + x * BN + 32, v_low + 512, idesc_o, 1u);
+                umma_commit_at(o_done0 + 8u * (unsigned)x);
+            };
+            int g0 = 0, h0[2] = {0, 0};
+            for (int round = 0; ok; ++round) {
+                Item it;
+                if (!mbar_wait(q_full, round & 1, failed)) { *failed = 1; break; }
+                if (!read_item(round, it)) break;
+                const int halves = it.halves, n_tiles = it.n_tiles;
+                if (!mbar_wait(&k_full[g0 % STAGES], (g0 / STAGES) & 1, failed)) { *failed = 1; break; }
+                tc_fence_after();
+                // S_x of the first tile lands in the columns the last product of the item before read its P from: products
+                // of one thread run in the order of their issue
+                for (int x = 0; x < halves; ++x) issue_s(x, g0);
+                umma_commit_at(k_empty0 + 8u * (unsigned)(g0 % STAGES));  // the K slot is free once both products have read it
+                if (n_tiles == 1) umma_commit_at(q_empty_at);            // and so are the queries after the item's last S
                 for (int j = 0; j < n_tiles && ok; ++j) {
                     const int g = g0 + j;
-                    if (j + 1 < n_tiles) {
-                        if (!mbar_wait(&k_full[(g + 1) % STAGES], ((g + 1) / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
-                        // S(g + 1) lands in the columns that P(g - 1) was read from: the product that read it must be over
-                        // (for the item's first tile it is: the item before ended with every product done)
-                        if (j > 0 && !mbar_wait(o_done, (g - 1) & 1, failed)) { *failed = 1; ok = false; break; }
+                    const bool more = j + 1 < n_tiles;
+                    for (int x = 0; x < halves && ok; ++x) {
+                        if (!mbar_wait(&p_full[x], (h0[x] + j) & 1, failed)) { *failed = 1; ok = false; break; }
+                        if (x == 0 && !mbar_wait(&v_full[g % STAGES], (g / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
                         tc_fence_after();
-                        issue_s(g + 1);
+                        issue_pv(x, g, j > 0 ? 1u : 0u);
+                        if (x == halves - 1) umma_commit_at(v_empty0 + 8u * (unsigned)(g % STAGES));
+                        if (more) {
+                            if (x == 0) {
+                                if (!mbar_wait(&k_full[(g + 1) % STAGES], ((g + 1) / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
+                                tc_fence_after();
+                            }
+                            // S_x(g + 1) lands in the columns the product just issued reads P_x(g) from: products of one
+                            // thread run in the order of their issue, so the columns are read before they are written
+                            issue_s(x, g + 1);
+                            if (x == halves - 1) {
+                                umma_commit_at(k_empty0 + 8u * (unsigned)((g + 1) % STAGES));
+                                if (j + 2 == n_tiles) umma_commit_at(q_empty_at);
+                            }
+                        }
                     }
-                    if (!mbar_wait(p_full, g & 1, failed)) { *failed = 1; ok = false; break; }
-                    if (!mbar_wait(&v_full[g % STAGES], (g / STAGES) & 1, failed)) { *failed = 1; ok = false; break; }
-                    tc_fence_after();
-                    // P(g) lies in tensor memory over the first half of S(g)'s columns: 16 keys = 8 columns per product
-                    const unsigned stage = (unsigned)(g % STAGES);
-                    umma_pv_tile(tmem + O_COL, tmem + (g & 1) * BN, v_low0 + stage * (TILE_BYTES >> 4), idesc_o, j > 0 ? 1u : 0u);
-                    umma_commit_at(v_empty0 + 8u * stage);
-                    umma_commit_at(o_done_at);
                 }
+                g0 += n_tiles;
+                h0[0] += n_tiles;
+                if (halves == 2) h0[1] += n_tiles;
             }
-        } else {
-            // ------------------------------------------------------------------ softmax: thread = row = tensor-memory lane
-            const int quarter = warp & 3;
-            const int r = quarter * 32 + lane;
-            const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
-            const int tok = r / gc, hh = r - tok * gc;
-            const bool row_valid = tok < ntok && hh < heads_here;
-            const int hi = row_valid ? pos_first + tok : -1;
-            const int lo = (row_valid && a.window > 0) ? max(0, hi - a.window + 1) : 0;
-            float m = -INFINITY, l = 0.f;
-            bool ok = true;
-            for (int j = 0; j < n_tiles; ++j) {
-                const int g = g0 + j, b = g & 1;
-                if (!mbar_wait(&s_full[b], (g >> 1) & 1, failed)) { *failed = 1; ok = false; break; }
-                tc_fence_after();
-                float s[BN];
-                tmem_ld64(lane_addr + b * BN, s);
-                const int tile_base = start + j * BN;
-                float tmax = -INFINITY;
-                if (tile_base + BN - 1 <= hi && tile_base >= lo) {  // every key of the tile is visible to this row
-#pragma unroll
-                    for (int i = 0; i < BN; ++i) {
-                        s[i] *= a.scale_log2;
-                        tmax = fmaxf(tmax, s[i]);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < BN; ++i) {
-                        const int pos = tile_base + i;
-                        s[i] = (pos <= hi && pos >= lo) ? s[i] * a.scale_log2 : -INFINITY;
-                        tmax = fmaxf(tmax, s[i]);
-                    }
-                }
-                const float m_new = fmaxf(m, tmax);
-                float alpha = 1.f;
-                if (m == -INFINITY) {
-                    m = m_new;  // nothing visible so far: the row of O holds zeros (or is overwritten by the first product), no rescale
-                } else if (m_new - m > RESCALE_THRESHOLD) {
-                    alpha = exp2f(m - m_new);
-                    m = m_new;
-                }
-                const float m_use = (m == -INFINITY) ? 0.f : m;
-                float sum = 0.f;
-                uint4 packed[BN / 8];
-#pragma unroll
-                for (int c = 0; c < BN / 8; ++c) {
-                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed[c]);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float p0 = fast_exp2(s[c * 8 + 2 * e] - m_use), p1 = fast_exp2(s[c * 8 + 2 * e + 1] - m_use);
-                        sum += p0 + p1;
-                        h2[e] = __floats2bfloat162_rn(p0, p1);
-                    }
-                }
-                l = l * alpha + sum;
-                // P(g) goes into this thread's lane over the columns S(g) came from (the thread holds its S row in registers;
-                // the tensor core writes those columns again only with S(g + 2), issued after the product that reads P(g))
-                const unsigned* words = reinterpret_cast<const unsigned*>(packed);
-                tmem_st16_words(lane_addr + b * BN, words);
-                tmem_st16_words(lane_addr + b * BN + 16, words + 16);
-                // Every thread sees every phase of o_done go by, tile by tile: a wait by parity tells "phase g - 1 is over" only
-                // to a thread that knows phase g - 2 is (a thread two phases behind would read the parity of a later phase as
-                // "not yet" and wait for ever). Here phase g - 2 was waited for one tile ago (or, at an item's second tile, at
-                // the end of the item before) and the product of tile g cannot start before this thread hands P(g) over, so
-                // the barrier is in phase g - 1 or g. The product of tile g - 1 was issued a whole tile ago; the wait is
-                // almost always over at the first look.
-                if (j > 0 && !mbar_wait(o_done, (g - 1) & 1, failed)) { *failed = 1; ok = false; break; }
-                if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                    // O may be rescaled only between two products: the one before is done
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax: thread = row = tensor-memory lane of its half
+        const int x = (warp - 2) >> 2;
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int v = x * BM + r;
+        const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
+        const unsigned s_addr = lane_addr + x * BN, o_addr = lane_addr + O_COL + x * BM;
+        const float scale = a.scale_log2;
+        int hx = 0;  // key tiles this half has seen
+        bool ok = true;
+        for (int round = 0; ok; ++round) {
+            Item it;
+            if (!mbar_wait(q_full, round & 1, failed)) { *failed = 1; break; }  // every thread sees every phase of it go by
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_seen);
+            if (!read_item(round, it)) break;
+            if (x < it.halves) {
+                const int n_tiles = it.n_tiles;
+                const int tok = v / gc, hh = v - tok * gc;
+                const bool row_valid = tok < it.ntok && hh < it.heads_here;
+                // A row beyond the tile's end (or beyond the heads of the chunk) is computed like the tile's last token and never
+                // stored: it takes the same way through the code as its neighbours, so no warp has to walk two ways.
+                const int hi = row_valid ? it.pos_first + tok : it.pos_last;
+                const int lo = a.window > 0 ? max(0, hi - a.window + 1) : 0;
+                float m = -INFINITY, l = 0.f;
+                for (int j = 0; j < n_tiles; ++j) {
+                    const int h = hx + j;
+                    if (!mbar_wait(&s_full[x], h & 1, failed)) { *failed = 1; ok = false; break; }
                     tc_fence_after();
+                    float s[BN];
+                    tmem_ld64(s_addr, s);
+                    tmem_ld64(s_addr + 64, s + 64);
+                    const int tile_base = it.start + j * BN;
+                    // one way for the whole warp: the masked walk only where some row of the warp needs it
+                    const int last_visible = hi - tile_base, first_visible = lo - tile_base;  // among the tile's keys 0 .. BN - 1
+                    if (!__all_sync(0xffffffffu, last_visible >= BN - 1 && first_visible <= 0)) {
+#pragma unroll
+                        for (int i = 0; i < BN; ++i) s[i] = (i <= last_visible && i >= first_visible) ? s[i] : -INFINITY;
+                    }
+                    float part[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                    for (int i = 0; i < BN; ++i) part[i & 3] = fmaxf(part[i & 3], s[i]);
+                    const float tmax = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])) * scale;  // the scale is positive: the largest score stays the largest
+                    const float m_new = fmaxf(m, tmax);
+                    float alpha = 1.f;
+                    if (m == -INFINITY) {
+                        m = m_new;  // nothing visible so far: the row of O holds zeros (or is overwritten by the first product), no rescale
+                    } else if (m_new - m > RESCALE_THRESHOLD) {
+                        alpha = exp2f(m - m_new);
+                        m = m_new;
+                    }
+                    const float minus_m = (m == -INFINITY) ? 0.f : -m;
+                    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+                    unsigned words[BN / 2];
+#pragma unroll
+                    for (int i = 0; i < BN / 2; ++i) {
+                        const float p0 = fast_exp2(fmaf(s[2 * i], scale, minus_m)), p1 = fast_exp2(fmaf(s[2 * i + 1], scale, minus_m));
+                        sum[i & 3] += p0 + p1;
+                        words[i] = pack_bf16x2(p0, p1);
+                    }
+                    l = l * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
+                    // P goes into this thread's lane over the columns its S came from (the thread holds its S row in registers;
+                    // the tensor core writes those columns again only with the next S, issued after the product that reads P)
+#pragma unroll
+                    for (int c = 0; c < BN / 2; c += 16) tmem_st16_words(s_addr + c, words + c);
+                    // Every thread sees every phase of o_done go by, tile by tile: a wait by parity tells "phase h - 1 is over" only
+                    // to a thread that knows phase h - 2 is (a thread two phases behind would read the parity of a later phase as
+                    // "not yet" and wait for ever). Here phase h - 2 was waited for one tile ago (or, at an item's second tile, at
+                    // the end of the item before) and the product of tile h cannot start before this thread hands P over, so
+                    // the barrier is in phase h - 1 or h. The product of tile h - 1 was issued a whole tile ago; the wait is
+                    // almost always over at the first look.
+                    if (j > 0 && !mbar_wait(&o_done[x], (h - 1) & 1, failed)) { *failed = 1; ok = false; break; }
+                    if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                        // O may be rescaled only between two products: the one before is done
+                        tc_fence_after();
+#pragma unroll
+                        for (int c = 0; c < D; c += 16) {
+                            float o[16];
+                            tmem_ld16(o_addr + c, o);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) o[i] *= alpha;
+                            tmem_st16(o_addr + c, o);
+                        }
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&p_full[x]);
+                }
+                // every phase but the item's last was seen in the loop
+                if (ok) ok = mbar_wait(&o_done[x], (hx + n_tiles - 1) & 1, failed);
+                if (!ok) *failed = 1;
+                tc_fence_after();
+                if (ok) {
+                    const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
                     for (int c = 0; c < D; c += 16) {
                         float o[16];
-                        tmem_ld16(lane_addr + O_COL + c, o);
+                        tmem_ld16(o_addr + c, o);
+                        if (row_valid) {
+                            uint4 w[2];
+                            unsigned* packed = reinterpret_cast<unsigned*>(w);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i] *= alpha;
-                        tmem_st16(lane_addr + O_COL + c, o);
+                            for (int i = 0; i < 8; ++i) packed[i] = pack_bf16x2(o[2 * i] * inv, o[2 * i + 1] * inv);
+                            uint4* dst = reinterpret_cast<uint4*>(a.out + (size_t)(it.tok0 + tok) * a.out_stride + (size_t)(it.first_head + hh) * D + c);
+                            if (a.wide_stores) {  // one 32-byte store per 16 columns: half as many requests to the memory pipe
+                                asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]),
+                                             "r"(packed[3]), "r"(packed[4]), "r"(packed[5]), "r"(packed[6]), "r"(packed[7]) : "memory");
+                            } else {
+                                dst[0] = w[0];
+                                dst[1] = w[1];
+                            }
+                        }
                     }
+                    // the rows are out of tensor memory before this thread hands over the next item's first P, and only then is O written anew
+                    tc_fence_before();
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(p_full);
+                hx += n_tiles;
             }
-            // every phase but the item's last was seen in the loop
-            if (ok) ok = mbar_wait(o_done, (g0 + n_tiles - 1) & 1, failed);
-            if (!ok) *failed = 1;
-            tc_fence_after();
-            if (ok) {
-                const float inv = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll
-                for (int c = 0; c < D; c += 16) {
-                    float o[16];
-                    tmem_ld16(lane_addr + O_COL + c, o);
-                    if (row_valid) {
-                        uint4 w[2];
-                        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(w);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) h2[i] = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv);
-                        uint4* dst = reinterpret_cast<uint4*>(a.out + (size_t)(tok0 + tok) * a.out_stride + (size_t)(first_head + hh) * D + c);
-                        dst[0] = w[0];
-                        dst[1] = w[1];
-                    }
-                }
-            }
+            // The softmax warps end an item together, so that none of them (those of a half that had nothing to do least of
+            // all) falls an item behind the others: the slot of an item is written anew three items later.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(round_done);
+            if (ok && !mbar_wait(round_done, round & 1, failed)) { *failed = 1; ok = false; }
         }
-        g0 += n_tiles;
-        // the end of the round: every product of this item is over (the softmax threads saw the last one finish and have
-        // read their rows), the next item's number is in its slot
-        tc_fence_before();
-        __syncthreads();
-        tc_fence_after();
     }
     if (tid == 0) {
         if (*failed) atomicOr(a.status, HB_STATUS_WAIT_EXPIRED | HB_STATUS_IN_ATTENTION_TCGEN05);
@@ -516,26 +622,26 @@ EncodeTiled encode_tiled() {
     return fn;
 }
 
-constexpr size_t SMEM_USED = 1024 + (size_t)2 * STAGES * TILE_BYTES + (size_t)HALVES * QPANEL * sizeof(bf16) + (4 * STAGES + 4) * 8 + 32;
-// A block holds half of the SM's tensor memory, so two blocks are all an SM can serve. The launch asks for at least
-// 80 KB of shared memory so that no third block becomes resident only to wait for tensor memory: such a block of a
-// kernel launched early (as a programmatic dependent) would hold what a block of the kernel before it still needs.
-constexpr size_t SMEM_BYTES = SMEM_USED > 80 * 1024 ? SMEM_USED : 80 * 1024;
+// More than half of an SM's shared memory, so that one block is all an SM takes: the block holds all of its tensor memory.
+constexpr size_t SMEM_USED = 1024 + (size_t)2 * STAGES * TILE_BYTES + (size_t)PANELS * Q_PANEL * sizeof(bf16) + (4 * STAGES + 10) * 8 + 96;
+constexpr size_t SMEM_BYTES = SMEM_USED > 120 * 1024 ? SMEM_USED : 120 * 1024;
 }  // namespace
 
 // Rows of a tile (tokens x heads of a group) this kernel wants: the host planner cuts rows into tiles of
-// 128 / min(group, 128) tokens.
-HB_EXPORT int hb_attention_tc_tile_rows() { return BM; }
+// 256 / min(group, 256) tokens.
+HB_EXPORT int hb_attention_tc_tile_rows() { return ROWS; }
 
 HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
-                                    int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int heads,
-                                    int kv_heads, int head_dim, int page_size, int pages, float scale, int window, int* status,
+                                    int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int n_tokens,
+                                    int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, int window, int* status,
                                     int* work, cudaStream_t stream) {
     (void)token_row;
     if (!work) return HB_BAD_ARGUMENT;
     if (n_tiles <= 0) return 0;
+    if (n_tokens <= 0) return HB_BAD_ARGUMENT;
     if (head_dim != D) return HB_UNSUPPORTED_SIZE;
     if (kv_heads <= 0 || heads % kv_heads || q_stride % 8 || out_stride % 8) return HB_BAD_ARGUMENT;
+    if (!(scale > 0.f)) return HB_BAD_ARGUMENT;  // the row maximum is taken before the scores are scaled
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return HB_UNSUPPORTED_SIZE;
     if (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15) return HB_BAD_ARGUMENT;
     EncodeTiled encode = encode_tiled();
@@ -548,9 +654,19 @@ HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int 
     if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return HB_BAD_ARGUMENT;
+    // the queries as (column, head, token): a tile's box is 64 columns of gc heads of its tokens
+    const int group = heads / kv_heads, gc = group < ROWS ? group : ROWS, head_chunks = (group + gc - 1) / gc;
+    CUtensorMap q_map;
+    const cuuint64_t q_dims[3] = {(cuuint64_t)D, (cuuint64_t)heads, (cuuint64_t)n_tokens};
+    const cuuint64_t q_strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)q_stride * 2};
+    const cuuint32_t q_box[3] = {64, (cuuint32_t)gc, (cuuint32_t)(ROWS / gc)};
+    const cuuint32_t q_elem[3] = {1, 1, 1};
+    if (encode(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), q_dims, q_strides, q_box, q_elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return HB_BAD_ARGUMENT;
     AttnArgs a{(const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_width, positions,
-               heads, kv_heads, page_size, pages, window, scale * 1.4426950408889634f, status};
-    const int group = heads / kv_heads, gc = group < BM ? group : BM, head_chunks = (group + gc - 1) / gc;
+               heads, kv_heads, page_size, pages, window, scale * 1.4426950408889634f, status,
+               (((uintptr_t)out & 31) == 0 && out_stride % 16 == 0) ? 1 : 0};
     if ((long long)kv_heads * head_chunks > 65535) return HB_UNSUPPORTED_SIZE;
     static bool configured = false;
     if (!configured) {
@@ -558,13 +674,13 @@ HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    // two blocks fit an SM (tensor memory, shared memory): that many persistent blocks, or one per item if there are fewer
+    // one persistent block per SM (it holds the SM's tensor memory), or one per item if there are fewer
     int device = 0, sms = 0;
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
         return HB_BAD_ARGUMENT;
     const long long items = (long long)n_tiles * kv_heads * head_chunks;
     if (items > 0x7fffffffLL) return HB_UNSUPPORTED_SIZE;
-    const int blocks = (int)(items < 2LL * sms ? items : 2LL * sms);
-    return launch_after_previous(attention_tc_kernel, dim3(blocks), THREADS, SMEM_BYTES, stream, map, a, tiles, n_tiles, kv_heads * head_chunks, gc,
+    const int blocks = (int)(items < (long long)sms ? items : (long long)sms);
+    return launch_after_previous(attention_tc_kernel, dim3(blocks), THREADS, SMEM_BYTES, stream, map, q_map, a, tiles, n_tiles, kv_heads * head_chunks, gc,
                                  head_chunks, work);
 }

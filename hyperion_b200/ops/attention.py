@@ -18,6 +18,7 @@ from .native import KernelError, check, f32, i32, library, ptr, require_cuda, sm
 
 TOKEN_SHAPE_MAX = 4  # at most csrc/attention_tma.cu's FRESH_TOKENS: its producer fetches older keys before the kernel ahead has finished
 TILE_ROWS = 64
+TC_TILE_ROWS = 256  # csrc/attention_tcgen05.cu: two halves of 128 rows per block
 KEY_TILE = 64
 BLOCKS_PER_SM = 2  # two blocks of the token shape fit one SM
 
@@ -38,13 +39,13 @@ def _entry(head_dim: int, page_size: int, shape: str):
 
 
 def uses_tcgen05(head_dim: int, page_size: int) -> bool:
-    """Head sizes 64 and 128 with pages of 8 to 64 tokens: prompt portions take the tcgen05 kernel (128-row tiles)."""
+    """Head sizes 64 and 128 with pages of 8 to 64 tokens: prompt portions take the tcgen05 kernel (256-row tiles)."""
     return head_dim in (64, 128) and 8 <= page_size <= 64
 
 
 def tile_rows(head_dim: int, page_size) -> int:
     """Virtual rows (tokens x heads of a group) per tile of the kernel that will run."""
-    return 128 if page_size is not None and uses_tcgen05(head_dim, page_size) else TILE_ROWS
+    return TC_TILE_ROWS if page_size is not None and uses_tcgen05(head_dim, page_size) else TILE_ROWS
 
 
 def tile_tokens(heads: int, kv_heads: int, rows: int = TILE_ROWS) -> int:
@@ -94,14 +95,14 @@ def _common(q, out, cache, block_table, token_row, positions):
 
 
 def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n_tiles, scale, window, out, tile_size: int = TILE_ROWS):
-    """``tile_size``: the virtual rows per tile the tiles were planned for (64, or 128 for the tcgen05 kernel)."""
+    """``tile_size``: the virtual rows per tile the tiles were planned for (64, or 256 for the tcgen05 kernel)."""
     _common(q, out, cache, block_table, token_row, positions)
     pages, _, kv_heads, page_size, head_dim = cache.shape
-    if uses_tcgen05(head_dim, page_size) and tile_size == 128:
+    if uses_tcgen05(head_dim, page_size) and tile_size == TC_TILE_ROWS:
         check(library("attention_tcgen05", HB_HEAD_DIM=head_dim).hb_attention_tc_tiles(
             ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table), i32(block_table.shape[1]), ptr(token_row),
-            ptr(positions), ptr(tiles), i32(n_tiles), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale),
-            i32(window or 0), ptr(status_word(q.device)), ptr(work_counters(q.device)), stream_ptr()), "attention_tiles")
+            ptr(positions), ptr(tiles), i32(n_tiles), i32(q.shape[0]), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages),
+            f32(scale), i32(window or 0), ptr(status_word(q.device)), ptr(work_counters(q.device)), stream_ptr()), "attention_tiles")
         return
     entry = _entry(head_dim, page_size, "tiles")
     check(entry(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),

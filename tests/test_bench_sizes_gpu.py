@@ -69,7 +69,7 @@ def test_prompt_attention_of_2048_tokens_at_the_benchmark_sizes(first):
     cache, table, keys, values = big_paged_case([first + count], seed=31 + first)
     q = rnd(count, (HEADS + 2 * KV_HEADS) * HEAD_DIM, seed=32, dtype=torch.bfloat16).to(DEV)
     size = fast.tile_rows(HEAD_DIM, PAGE)
-    assert size == 128 and fast.uses_tcgen05(HEAD_DIM, PAGE)
+    assert size == fast.TC_TILE_ROWS and fast.uses_tcgen05(HEAD_DIM, PAGE)
     tiles, items = fast.plan([Row(0, 0, count, first, 0)], fast.tile_tokens(HEADS, KV_HEADS, size))
     assert len(items) == 0
     token_row = torch.zeros(count, dtype=torch.int32, device=DEV)

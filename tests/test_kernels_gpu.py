@@ -269,11 +269,11 @@ def run_fast_attention(q, heads, cache, table, rows, scale, window):
                              len(tiles) // 3, scale, window, out)
     outs = {}
     page_size, head_dim = cache.shape[3], cache.shape[4]
-    if tiles and fast.uses_tcgen05(head_dim, page_size):  # the same rows again through the tcgen05 kernel (128-row tiles)
-        tiles128 = fast.plan(step_rows, fast.tile_tokens(heads, kv_heads, 128))[0].tolist()
+    if tiles and fast.uses_tcgen05(head_dim, page_size):  # the same rows again through the tcgen05 kernel (256-row tiles)
+        wide = fast.plan(step_rows, fast.tile_tokens(heads, kv_heads, fast.TC_TILE_ROWS))[0].tolist()
         o = out.clone()
-        fast.attention_tiles(qd, heads, cd, batch_table, token_row, positions, torch.tensor(tiles128, dtype=torch.int32, device=DEV),
-                             len(tiles128) // 3, scale, window, o, tile_size=128)
+        fast.attention_tiles(qd, heads, cd, batch_table, token_row, positions, torch.tensor(wide, dtype=torch.int32, device=DEV),
+                             len(wide) // 3, scale, window, o, tile_size=fast.TC_TILE_ROWS)
         if items:
             fast.attention_tokens(qd, heads, cd, batch_table, token_row, positions, torch.tensor(items, dtype=torch.int32, device=DEV),
                                   len(items), 2, scale, window, o)
