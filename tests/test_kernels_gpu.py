@@ -315,6 +315,32 @@ def test_attention_bf16_tiles_and_tokens(heads, kv_heads, head_dim, page_size, w
         assert (got - want).abs().max() <= 2 ** -7 * want.abs().max(), f"splits {splits}"
 
 
+def test_prompt_attention_with_more_short_items_than_blocks():
+    """Hundreds of short prompt portions in one launch: every persistent block of the tcgen05 kernel takes several
+    items one after the other, most of them a single tile of keys (the next item's queries are then wanted before the
+    softmax threads have looked at this item's), some of two or three, some that run one half of the block alone."""
+    from hyperion_b200.ops import raise_on_status
+
+    heads, kv_heads, head_dim, page_size = 8, 2, 128, 16
+    g = torch.Generator().manual_seed(77)
+    counts = torch.randint(5, 70, (360,), generator=g).tolist()
+    firsts = [int(f) for f in torch.randint(0, 300, (360,), generator=g)]
+    for i in range(0, 360, 9):
+        firsts[i] = 0  # whole short prompts among the portions
+    contexts = [f + c for f, c in zip(firsts, counts)]
+    cache, table, keys, values = paged_case(kv_heads, head_dim, page_size, contexts, torch.bfloat16, seed=8)
+    rows = [(r, firsts[r], counts[r]) for r in range(360)]
+    tokens = sum(counts)
+    q = rnd(tokens, (heads + 2 * kv_heads) * head_dim, seed=15, dtype=torch.bfloat16)
+    scale = head_dim ** -0.5
+    outs = run_fast_attention(q, heads, cache, table, rows, scale, 0)
+    raise_on_status(torch.device(DEV))
+    want = reference_attention(q[:, : heads * head_dim].double().view(tokens, heads, head_dim), keys, values, rows, scale, None)
+    got = outs["tcgen05"].cpu().double().view(tokens, heads, head_dim)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() <= 2 ** -7 * want.abs().max()
+
+
 def test_attention_bf16_finds_one_far_key_among_hundreds():
     """Random scores would average a lost key away: make one distant key dominate every query."""
     heads, kv_heads, head_dim, page_size = 8, 2, 64, 16
