@@ -6,7 +6,9 @@
 // One block per SM holds all of the SM's tensor memory and works on two halves of 128 rows (H and L) that walk the
 // same key tiles of 128 keys.  While the softmax threads of one half work on their S, the tensor core runs the other
 // half's products, so neither stands still for long:
-//   warp 0      producer: one cp.async.bulk.tensor per page and 64-column panel into rings of key and of value tiles;
+//   warp 0      producer: one cp.async.bulk.tensor per page and 64-column panel into rings of key and of value tiles, and
+//               the item's queries as one 3-D box per panel (columns x heads of the group x tokens of the tile), which
+//               lands the rows token x head in the swizzled K-major layout the products read;
 //   warp 1      issues the products, per key tile and half: O_x += P_x V (M 128, N = head size, K 128, P read from
 //               tensor memory, V an MN-major operand) as soon as the half's softmax threads have handed P over, then
 //               at once S_x = Q_x K_next^T (M 128, N 128, K = head size) into the columns P_x was read from (products
