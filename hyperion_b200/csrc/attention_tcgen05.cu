@@ -224,8 +224,8 @@ struct AttnArgs {
 // (within a prompt the later tiles walk more keys, so the long items come first), and every block takes the next item
 // from a counter in global memory when it has finished one. A prompt's first tile walks one tile of keys and its last
 // tile all of them; with one block per item the longest item alone would set the kernel's time, now the items spread
-// evenly over the blocks. `work` = {next item, blocks that have finished}: the block that finishes last sets both back
-// to zero for the next launch in the stream.
+// evenly over the blocks. `work` = {items handed out beyond every block's first, blocks that have finished}: the block
+// that finishes last sets both back to zero for the next launch in the stream.
 __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map,
                                                                   const AttnArgs a,
                                                                   const int* __restrict__ tiles, int n_work_tiles, int ys, int gc, int head_chunks,
@@ -255,8 +255,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_c
     // [4][5]: the items in flight, each with what every thread wants to know of it (item, first token, token count, batch
     // row, first position), fetched by the producer while the item before is still being worked on
     volatile int* item_slot = failed + 1;
-    auto take_item = [&](int slot) {  // one thread
-        const int item = *failed ? total_items : atomicAdd(&work[0], 1);
+    auto note_item = [&](int slot, int item) {  // one thread
         volatile int* info = item_slot + 5 * slot;
         info[0] = item;
         if (item < total_items) {
@@ -268,6 +267,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_c
             info[4] = a.positions[tok0];
         }
     };
+    // A block's first item is the one of its own number (the grid has no more blocks than there are items); the counter
+    // hands out the items after those.
+    auto take_item = [&](int slot) { note_item(slot, *failed ? total_items : (int)gridDim.x + atomicAdd(&work[0], 1)); };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int group = a.heads / a.kv_heads;
@@ -287,6 +289,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_c
     // the first tiles too. The rows of Q that no copy writes (beyond tokens x heads of a tile) are never stored; they start
     // as zeros all the same.
     for (int e = tid; e < (2 * STAGES * TILE_BYTES + PANELS * Q_PANEL * 2) / 16; e += THREADS) reinterpret_cast<uint4*>(base)[e] = make_uint4(0, 0, 0, 0);
+    // what the first item is needs nothing of the kernel before: the tiles and positions were copied in at the step's start
+    if (tid == 0) note_item(0, (int)blockIdx.x);
     wait_for_previous_kernels();  // the queries and the newest keys and values come from the kernel before; so does the counter's reset
     // All of the SM's tensor memory, and only now: a block of a kernel further back in the stream that has yet to start
     // on this SM can no longer want any.
@@ -294,7 +298,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_c
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (tid == 0) take_item(0);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
     __syncthreads();
