@@ -1,9 +1,10 @@
 """Tensor-core attention over the paged bfloat16 cache: planning on the host and the two launches.
 
 A step's rows are divided by length: rows of more than ``TOKEN_SHAPE_MAX`` tokens are cut into tiles
-of ``tile_tokens`` tokens (times the heads of one key/value group = up to 64 rows of a block); the
-tokens of shorter rows (decoded tokens, very short portions) each get blocks of their own, with the
-keys split over several blocks when the batch alone would not fill the GPU.
+of ``tile_tokens`` tokens (times the heads of one key/value group = the virtual rows of a block: up to
+256 for the tcgen05 kernel, 64 for the others); the tokens of shorter rows (decoded tokens, very short
+portions) each get blocks of their own, with the keys split over several blocks when the batch alone
+would not fill the GPU.
 """
 from __future__ import annotations
 
