@@ -56,11 +56,12 @@ def reference(q, keys, values, rows):
     return torch.cat(outs)
 
 
-@pytest.mark.parametrize("first", [0, 2048, 1029])
+@pytest.mark.parametrize("first", [0, 2048, 1029, 14336])
 def test_prompt_attention_of_2048_tokens_at_the_benchmark_sizes(first):
-    """One portion of 2,048 tokens from position 0, one from position 2,048 (context 4,096) and one from an odd position
-    (its context ends inside a page and inside a tile of keys) through the tile kernel the engine picks for heads of
-    128 and pages of 16."""
+    """One portion of 2,048 tokens from position 0, one from position 2,048 (context 4,096), one from an odd position
+    (its context ends inside a page and inside a tile of keys) and one that ends at a context of 16,384 (every block
+    walks some hundred tiles of keys, item after item) through the tile kernel the engine picks for heads of 128 and
+    pages of 16."""
     from hyperion_b200.engine.batch import Row
     from hyperion_b200.ops import attention as fast
     from hyperion_b200.ops import raise_on_status
