@@ -1,5 +1,5 @@
 """The kernels and the engine at the sizes the benchmark runs, each against the plain implementation in float64:
-attention alone at contexts of 2,048 to 4,096 with the 7B configuration's 28/4 heads of 128 and pages of 16, and a
+attention alone at contexts of 2,048 to 4,096 (and of tens of thousands, with one key that dominates) with the 7B configuration's 28/4 heads of 128 and pages of 16, and a
 two-layer model of the 7B configuration's widths under mixed steps, decode batches of 8 and 64, and replayed graphs."""
 from __future__ import annotations
 
@@ -115,6 +115,70 @@ def test_decode_attention_at_contexts_of_2048_to_4096(batch):
         assert torch.isfinite(got).all(), f"{splits} splits: not finite"
         error = (got - want).abs().amax(dim=(1, 2)) / want.abs().max()
         assert error.max() <= ATTENTION_TOLERANCE, f"{splits} splits, row {int(error.argmax())} (context {contexts[int(error.argmax())]}): {float(error.max()):.3e}"
+
+
+def test_decode_attention_finds_one_key_in_contexts_of_tens_of_thousands():
+    """Random keys average a lost tile away when there are tens of thousands of them: here one key per request dominates
+    every query (at the start, in the middle, at the last position but one, at the edge of a split), so the output is
+    that key's value, or the kernel has skipped it."""
+    from hyperion_b200.ops import attention as fast
+    from hyperion_b200.ops import raise_on_status
+
+    contexts = [16384, 32768, 20000, 9001]
+    batch = len(contexts)
+    cache, table, keys, values = big_paged_case(contexts, seed=60)
+    direction = rnd(HEAD_DIM, seed=61).to(torch.bfloat16)
+    spots = [5, 32768 // 2 + 63, 20000 - 2, 9001 - 64 * 47]
+    for r, spot in enumerate(spots):
+        keys[r][spot] = direction * 4
+        cache[table[r, spot // PAGE], 0, :, spot % PAGE] = (direction * 4).to(DEV)
+    q = (direction.float() * 4).repeat(batch, HEADS + 2 * KV_HEADS).to(torch.bfloat16).to(DEV)
+    token_row = torch.arange(batch, dtype=torch.int32, device=DEV)
+    positions = torch.tensor([c - 1 for c in contexts], dtype=torch.int32, device=DEV)
+    items = torch.arange(batch, dtype=torch.int32, device=DEV)
+    rows = [(r, c - 1, 1) for r, c in enumerate(contexts)]
+    want = reference(q[:, : HEADS * HEAD_DIM].double().view(batch, HEADS, HEAD_DIM), keys, values, rows)
+    for splits in sorted({1, 7, fast.choose_splits(batch, HEADS, KV_HEADS, max(contexts)), 64}):
+        out = torch.full((batch, HEADS * HEAD_DIM), float("nan"), dtype=torch.bfloat16, device=DEV)
+        fast.attention_tokens(q, HEADS, cache, table, token_row, positions, items, batch, splits, HEAD_DIM ** -0.5, 0, out)
+        raise_on_status(torch.device(DEV))
+        got = out.double().view(batch, HEADS, HEAD_DIM)
+        assert torch.isfinite(got).all(), f"{splits} splits: not finite"
+        assert (got - want).abs().max() <= ATTENTION_TOLERANCE * want.abs().max(), f"{splits} splits"
+        for r, spot in enumerate(spots):
+            distance = (got[r, 0] - values[r][spot, 0].double().to(DEV)).abs().max()
+            assert distance < 0.05, f"{splits} splits: request {r} did not find its key at {spot} ({float(distance):.3f})"
+
+
+@pytest.mark.parametrize("spot", [3, 10000 + 127, 128 * 77, 19999])
+def test_prompt_attention_finds_one_key_in_a_context_of_twenty_thousand(spot):
+    """A prompt portion of 300 tokens behind 20,000 cached ones, one of which (near the start, at the last and at the
+    first key of a 128-key tile, right before the portion) dominates every query."""
+    from hyperion_b200.engine.batch import Row
+    from hyperion_b200.ops import attention as fast
+    from hyperion_b200.ops import raise_on_status
+
+    first, count = 20000, 300
+    cache, table, keys, values = big_paged_case([first + count], seed=70)
+    direction = rnd(HEAD_DIM, seed=71).to(torch.bfloat16)
+    keys[0][spot] = direction * 4
+    cache[table[0, spot // PAGE], 0, :, spot % PAGE] = (direction * 4).to(DEV)
+    q = (direction.float() * 4).repeat(count, HEADS + 2 * KV_HEADS).to(torch.bfloat16).to(DEV)
+    size = fast.tile_rows(HEAD_DIM, PAGE)
+    tiles, items = fast.plan([Row(0, 0, count, first, 0)], fast.tile_tokens(HEADS, KV_HEADS, size))
+    assert len(items) == 0
+    token_row = torch.zeros(count, dtype=torch.int32, device=DEV)
+    positions = torch.arange(first, first + count, dtype=torch.int32, device=DEV)
+    out = torch.full((count, HEADS * HEAD_DIM), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fast.attention_tiles(q, HEADS, cache, table, token_row, positions, torch.tensor(tiles, dtype=torch.int32, device=DEV), len(tiles) // 3,
+                         HEAD_DIM ** -0.5, 0, out, tile_size=size)
+    raise_on_status(torch.device(DEV))
+    want = reference(q[:, : HEADS * HEAD_DIM].double().view(count, HEADS, HEAD_DIM), keys, values, [(0, first, count)])
+    got = out.double().view(count, HEADS, HEAD_DIM)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() <= ATTENTION_TOLERANCE * want.abs().max()
+    distance = (got[:, 0] - values[0][spot, 0].double().to(DEV)).abs().max()
+    assert distance < 0.05, f"the key at {spot} was not found ({float(distance):.3f})"
 
 
 # ------------------------------------------------------------------------------------------------ a model of real widths
