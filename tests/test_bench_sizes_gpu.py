@@ -1,6 +1,7 @@
 """The kernels and the engine at the sizes the benchmark runs, each against the plain implementation in float64:
-attention alone at contexts of 2,048 to 4,096 (and of tens of thousands, with one key that dominates) with the 7B configuration's 28/4 heads of 128 and pages of 16, and a
-two-layer model of the 7B configuration's widths under mixed steps, decode batches of 8 and 64, and replayed graphs."""
+attention alone at contexts of 2,048 to 4,096 (and of tens of thousands, with one key that dominates) with the 7B
+configuration's 28/4 heads of 128 and pages of 16, and a two-layer model of the 7B configuration's widths under mixed
+steps, decode batches of 8 and 64, and replayed graphs."""
 from __future__ import annotations
 
 import numpy as np
