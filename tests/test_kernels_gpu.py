@@ -296,7 +296,7 @@ def run_fast_attention(q, heads, cache, table, rows, scale, window):
 @pytest.mark.parametrize("heads, kv_heads, head_dim, page_size, window", [(14, 2, 64, 16, 0), (6, 1, 32, 8, 0), (8, 8, 80, 16, 0),
                                                                           (20, 1, 16, 4, 0), (4, 2, 128, 32, 100), (3, 1, 48, 16, 70),
                                                                           (28, 4, 128, 16, 0), (4, 1, 64, 64, 0), (4, 2, 192, 8, 50),
-                                                                          (36, 2, 64, 16, 0)])
+                                                                          (36, 2, 64, 16, 0), (130, 1, 64, 16, 0), (264, 1, 64, 16, 0)])
 def test_attention_bf16_tiles_and_tokens(heads, kv_heads, head_dim, page_size, window):
     from hyperion_b200.ops import raise_on_status
 
