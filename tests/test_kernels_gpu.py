@@ -341,6 +341,55 @@ def test_prompt_attention_with_more_short_items_than_blocks():
     assert (got - want).abs().max() <= 2 ** -7 * want.abs().max()
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_prompt_attention_of_random_shapes(seed):
+    """Ten random steps per seed (head size 64 or 128, 1 to 8 key/value heads with 1 to 18 query heads each, pages of 8 to
+    64, with and without a window, 1 to 30 portions of 5 to 900 tokens at positions up to 3,000) through the tcgen05
+    kernel, each against the plain attention in float64."""
+    import random
+
+    from hyperion_b200.engine.batch import Row
+    from hyperion_b200.ops import attention as fast
+    from hyperion_b200.ops import raise_on_status
+
+    rng = random.Random(seed)
+    for case in range(10):
+        head_dim, kv_heads, group = rng.choice([64, 128]), rng.choice([1, 2, 4, 8]), rng.choice([1, 2, 3, 4, 7, 8, 16, 18])
+        heads, page_size = kv_heads * group, rng.choice([8, 16, 32, 64])
+        window = rng.choice([0, 0, rng.randrange(1, 600)])
+        n_rows = rng.randrange(1, 30)
+        counts = [rng.choice([rng.randrange(5, 40), rng.randrange(5, 300), rng.randrange(5, 900)]) for _ in range(n_rows)]
+        firsts = [rng.choice([0, rng.randrange(0, 200), rng.randrange(0, 3000)]) for _ in range(n_rows)]
+        cache, table, keys, values = paged_case(kv_heads, head_dim, page_size, [f + c for f, c in zip(firsts, counts)], torch.bfloat16,
+                                                seed=100 * seed + case)
+        tokens = sum(counts)
+        q = rnd(tokens, (heads + 2 * kv_heads) * head_dim, seed=1000 + 100 * seed + case, dtype=torch.bfloat16).to(DEV)
+        rows, at = [], 0
+        for i, (first, count) in enumerate(zip(firsts, counts)):
+            rows.append(Row(i, at, count, first, i))
+            at += count
+        size = fast.TC_TILE_ROWS
+        tiles = fast.plan(rows, fast.tile_tokens(heads, kv_heads, size))[0]
+        token_row = torch.tensor([i for i, c in enumerate(counts) for _ in range(c)], dtype=torch.int32, device=DEV)
+        positions = torch.tensor([p for f, c in zip(firsts, counts) for p in range(f, f + c)], dtype=torch.int32, device=DEV)
+        out = torch.full((tokens, heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+        fast.attention_tiles(q, heads, cache.to(DEV), table.to(DEV), token_row, positions, torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                             len(tiles) // 3, head_dim ** -0.5, window, out, tile_size=size)
+        raise_on_status(torch.device(DEV))
+        got = out.double().view(tokens, heads, head_dim)
+        what = dict(case=case, head_dim=head_dim, kv_heads=kv_heads, group=group, page_size=page_size, window=window, rows=n_rows)
+        assert torch.isfinite(got).all(), what
+        at = 0
+        for i, (first, count) in enumerate(zip(firsts, counts)):  # the plain attention in float64, on the device: the sizes are not small
+            k, v = keys[i].to(DEV).double(), values[i].to(DEV).double()
+            want = plain.attention(q[at : at + count, : heads * head_dim].double().view(count, heads, head_dim), k, v,
+                                   torch.arange(first, first + count, device=DEV), torch.arange(k.shape[0], device=DEV), head_dim ** -0.5,
+                                   window or None)
+            error = (got[at : at + count] - want).abs().max() / want.abs().max()
+            assert error <= 2 ** -7, (what, i, first, count, float(error))
+            at += count
+
+
 def test_attention_bf16_finds_one_far_key_among_hundreds():
     """Random scores would average a lost key away: make one distant key dominate every query."""
     heads, kv_heads, head_dim, page_size = 8, 2, 64, 16
