@@ -410,20 +410,44 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
     }
 }
 
+// Every piece is asked for before the first is used: a thread that fetches a piece, folds it in and only then fetches the
+// next waits for memory once per piece, and at a handful of rows the kernel is nothing but such waits. The order of the
+// sums stays the order of the splits.
+constexpr int MERGE_AHEAD = 16;
 __global__ void attention_merge_kernel(const int* __restrict__ items, const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                        bf16* __restrict__ out, int out_stride, int heads, int splits) {
     const int item = blockIdx.x, head = blockIdx.y, t = items[item];
     let_next_kernel_start();
     wait_for_previous_kernels();
     const size_t slot0 = ((size_t)item * heads + head) * splits;
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, ws_ml[(slot0 + s) * 2]);
+    const float2* ml = reinterpret_cast<const float2*>(ws_ml) + slot0;  // (maximum, sum) of each piece
+    float2 piece[MERGE_AHEAD];
+#pragma unroll
+    for (int s = 0; s < MERGE_AHEAD; ++s)
+        if (s < splits) piece[s] = ml[s];
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float value[MERGE_AHEAD];
+#pragma unroll
+        for (int s = 0; s < MERGE_AHEAD; ++s)
+            if (s < splits) value[s] = ws_o[(slot0 + s) * D + c];
+        float m = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < MERGE_AHEAD; ++s)
+            if (s < splits) m = fmaxf(m, piece[s].x);
+        for (int s = MERGE_AHEAD; s < splits; ++s) m = fmaxf(m, ml[s].x);
         float l = 0.f, o = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = ws_ml[(slot0 + s) * 2];
-            const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
-            l += f * ws_ml[(slot0 + s) * 2 + 1];
+#pragma unroll
+        for (int s = 0; s < MERGE_AHEAD; ++s) {
+            if (s < splits) {
+                const float f = (piece[s].x == -INFINITY) ? 0.f : exp2f(piece[s].x - m);
+                l += f * piece[s].y;
+                o += f * value[s];
+            }
+        }
+        for (int s = MERGE_AHEAD; s < splits; ++s) {
+            const float2 p = ml[s];
+            const float f = (p.x == -INFINITY) ? 0.f : exp2f(p.x - m);
+            l += f * p.y;
             o += f * ws_o[(slot0 + s) * D + c];
         }
         out[(size_t)t * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);

@@ -152,9 +152,12 @@ __global__ void add_rmsnorm_cached_kernel(float* __restrict__ h, const TD* __res
 }
 
 // The serving path's shape of it (bfloat16 delta and output, rows of a multiple of 8 values): 8 values per thread and
-// group with 16- and 32-byte accesses, each row read once. G groups per thread cover rows of up to 8 * G * 1024 values.
+// group with 16- and 32-byte accesses, each row read once. G groups per thread cover rows of up to 8 * G * 512 values.
 // With `partials` ([splits, tokens, hidden] floats: the split-K sums of the product that made the delta) the delta is
 // their sum in split order plus the bias, rounded to bfloat16 as the product's own reduction would store it.
+// split-K pieces a thread asks for at once (products of a decode step are split 5 to 10 times); fewer where a thread holds
+// several groups of a wide row
+__host__ __device__ constexpr int pieces_ahead(int groups_per_thread) { return groups_per_thread == 1 ? 12 : (groups_per_thread == 2 ? 8 : 4); }
 struct SplitDelta {
     const float* partials;
     size_t split_stride;  // tokens * hidden
@@ -164,7 +167,7 @@ struct SplitDelta {
 };
 
 template <int G>
-__global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ delta, const SplitDelta split,
+__global__ void __launch_bounds__(512) add_rmsnorm_bf16x8_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ delta, const SplitDelta split,
                                           const float* __restrict__ weight, __nv_bfloat16* __restrict__ out, const int* __restrict__ rows,
                                           int hidden, float eps, int write_h) {
     __shared__ float scratch[32];
@@ -193,11 +196,29 @@ __global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ h, const __nv_bflo
             if (split.partials) {
                 float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                 const float* first = split.partials + (size_t)s * hidden + i;
-#pragma unroll 4
-                for (int k = 0; k < split.splits; ++k) {
-                    const float4 p0 = *reinterpret_cast<const float4*>(first + k * split.split_stride);
-                    const float4 p1 = *reinterpret_cast<const float4*>(first + k * split.split_stride + 4);
-                    d[0] += p0.x; d[1] += p0.y; d[2] += p0.z; d[3] += p0.w; d[4] += p1.x; d[5] += p1.y; d[6] += p1.z; d[7] += p1.w;
+                // Every piece is asked for before the first is added: a thread that loads four pieces, adds them and only
+                // then loads the next four waits for memory once per group, and a step of a handful of rows is nothing but
+                // such waits. The order of the additions stays the order of the splits.
+                constexpr int PIECES_AHEAD = pieces_ahead(G);
+                float4 p0[PIECES_AHEAD], p1[PIECES_AHEAD];
+#pragma unroll
+                for (int k = 0; k < PIECES_AHEAD; ++k) {
+                    if (k < split.splits) {
+                        p0[k] = *reinterpret_cast<const float4*>(first + k * split.split_stride);
+                        p1[k] = *reinterpret_cast<const float4*>(first + k * split.split_stride + 4);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < PIECES_AHEAD; ++k) {
+                    if (k < split.splits) {
+                        d[0] += p0[k].x; d[1] += p0[k].y; d[2] += p0[k].z; d[3] += p0[k].w;
+                        d[4] += p1[k].x; d[5] += p1[k].y; d[6] += p1[k].z; d[7] += p1[k].w;
+                    }
+                }
+                for (int k = PIECES_AHEAD; k < split.splits; ++k) {
+                    const float4 q0 = *reinterpret_cast<const float4*>(first + k * split.split_stride);
+                    const float4 q1 = *reinterpret_cast<const float4*>(first + k * split.split_stride + 4);
+                    d[0] += q0.x; d[1] += q0.y; d[2] += q0.z; d[3] += q0.w; d[4] += q1.x; d[5] += q1.y; d[6] += q1.z; d[7] += q1.w;
                 }
                 __nv_bfloat162* packed = reinterpret_cast<__nv_bfloat162*>(&d4);
 #pragma unroll
@@ -244,11 +265,13 @@ static bool bf16x8_norm_takes(const void* h, const void* delta, const void* weig
 static int launch_bf16x8_norm(float* h, const __nv_bfloat16* delta, const SplitDelta& split, const float* weight, __nv_bfloat16* out, const int* rows,
                               int n_rows, int hidden, float eps, int write_h, cudaStream_t stream) {
     const int groups = hidden / 8;
-    const int per_thread = groups > 1024 ? 2 : 1;
+    const int per_thread = groups > 1024 ? 4 : (groups > 512 ? 2 : 1);  // blocks of at most 512 threads: the kernel holds a row's pieces in registers
     const int width = ((groups + per_thread - 1) / per_thread + 31) / 32 * 32;
     if (per_thread == 1)
         return launch_after_previous(add_rmsnorm_bf16x8_kernel<1>, n_rows, width, 0, stream, h, delta, split, weight, out, rows, hidden, eps, write_h);
-    return launch_after_previous(add_rmsnorm_bf16x8_kernel<2>, n_rows, width, 0, stream, h, delta, split, weight, out, rows, hidden, eps, write_h);
+    if (per_thread == 2)
+        return launch_after_previous(add_rmsnorm_bf16x8_kernel<2>, n_rows, width, 0, stream, h, delta, split, weight, out, rows, hidden, eps, write_h);
+    return launch_after_previous(add_rmsnorm_bf16x8_kernel<4>, n_rows, width, 0, stream, h, delta, split, weight, out, rows, hidden, eps, write_h);
 }
 
 // The same with the delta still in pieces: partials [splits, tokens, hidden] floats (+ a bias) are added up in split order

@@ -358,6 +358,61 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     else reinterpret_cast<bf16*>(c)[(size_t)row * ldc + col] = __float2bfloat16_rn(sum);
 }
 
+// The same, four columns per thread (n and ldc multiples of 4, aligned bases), and every piece asked for before the first
+// is added: a thread that adds piece after piece waits for memory once per piece, and the kernels of a decode step are
+// nothing but such waits. The order of the additions stays the order of the splits.
+constexpr int REDUCE_AHEAD = 16;
+__global__ void splitk_reduce4_kernel(const float* __restrict__ partial, int splits, int m, int n, void* c, int ldc, int out_is_f32,
+                                      const float* bias_f, const bf16* bias_h) {
+    const size_t quad = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    let_next_kernel_start();
+    const size_t i = quad * 4, total = (size_t)m * n;
+    const int row = (int)(i / n), col = (int)(i - (size_t)row * n);
+    float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < total) {  // the bias is nobody's output: fetched while the kernel before still runs
+        if (bias_f) b = *reinterpret_cast<const float4*>(bias_f + col);
+        else if (bias_h) b = make_float4(__bfloat162float(bias_h[col]), __bfloat162float(bias_h[col + 1]), __bfloat162float(bias_h[col + 2]),
+                                         __bfloat162float(bias_h[col + 3]));
+    }
+    wait_for_previous_kernels();
+    if (i >= total) return;
+    float4 p[REDUCE_AHEAD];
+#pragma unroll
+    for (int s = 0; s < REDUCE_AHEAD; ++s)
+        if (s < splits) p[s] = *reinterpret_cast<const float4*>(partial + (size_t)s * total + i);
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < REDUCE_AHEAD; ++s)
+        if (s < splits) { sum.x += p[s].x; sum.y += p[s].y; sum.z += p[s].z; sum.w += p[s].w; }
+    for (int s = REDUCE_AHEAD; s < splits; ++s) {
+        const float4 q = *reinterpret_cast<const float4*>(partial + (size_t)s * total + i);
+        sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
+    }
+    sum.x += b.x; sum.y += b.y; sum.z += b.z; sum.w += b.w;
+    if (out_is_f32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(c) + (size_t)row * ldc + col) = sum;
+    } else {
+        uint2 packed;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+        h2[0] = __floats2bfloat162_rn(sum.x, sum.y);
+        h2[1] = __floats2bfloat162_rn(sum.z, sum.w);
+        *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(c) + (size_t)row * ldc + col) = packed;
+    }
+}
+
+static int launch_splitk_reduce(const float* workspace, int splits, int m, int n, void* c, int ldc, int out_is_f32, const float* bias_f,
+                                const bf16* bias_h, cudaStream_t stream) {
+    const size_t total = (size_t)m * n;
+    const size_t out_bytes = out_is_f32 ? 4 : 2;
+    const bool by_four = n % 4 == 0 && ldc % 4 == 0 && ((uintptr_t)workspace & 15) == 0 && ((uintptr_t)c & (4 * out_bytes - 1)) == 0 &&
+                         (!bias_f || ((uintptr_t)bias_f & 15) == 0);
+    if (by_four)
+        return launch_after_previous(splitk_reduce4_kernel, (unsigned)((total / 4 + 127) / 128), 128, 0, stream, workspace, splits, m, n, c, ldc,
+                                     out_is_f32, bias_f, bias_h);
+    return launch_after_previous(splitk_reduce_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, workspace, splits, m, n, c, ldc, out_is_f32,
+                                 bias_f, bias_h);
+}
+
 template <int BN, int EPI>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using L = Layout<BN>;
@@ -462,9 +517,7 @@ HB_EXPORT int hb_gemm_bf16(const void* a, int lda, const void* w, int ldw, void*
              : batch_tile == 32 ? launch_swap<32>(epi, map_w, map_x, p, grid, stream)
                                 : launch_swap<64>(epi, map_w, map_x, p, grid, stream);
     if (code || splits == 1 || leave_partials) return code;  // the caller adds the partial sums up itself (hb_splitk_reduce, or a kernel that reads them)
-    const size_t total = (size_t)m * n;
-    return launch_after_previous(splitk_reduce_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, (const float*)workspace, splits, m, n, c, ldc,
-                                 (int)(epilogue == EPI_F32), bias_f, (const bf16*)bias_h);
+    return launch_splitk_reduce((const float*)workspace, splits, m, n, c, ldc, (int)(epilogue == EPI_F32), bias_f, (const bf16*)bias_h, stream);
 }
 
 // Adds up split-K partials [splits, m, n] in split order, adds the bias and stores bfloat16 or float: the second half of
@@ -473,7 +526,5 @@ HB_EXPORT int hb_splitk_reduce(const float* workspace, int splits, int m, int n,
                                const void* bias_h, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (splits < 1 || !workspace) return HB_BAD_ARGUMENT;
-    const size_t total = (size_t)m * n;
-    return launch_after_previous(splitk_reduce_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, workspace, splits, m, n, c, ldc, out_is_f32, bias_f,
-                                 (const bf16*)bias_h);
+    return launch_splitk_reduce(workspace, splits, m, n, c, ldc, out_is_f32, bias_f, (const bf16*)bias_h, stream);
 }
