@@ -20,6 +20,8 @@ from .basic import sgemm_f32
 from .native import KernelError, require_cuda
 
 
+SMALL_PRODUCT_BYTES = 64 << 20  # weights of at most this many bytes go to the library at more than 32 rows
+
 _policy: list = [None]
 
 
@@ -38,7 +40,9 @@ def _takes_own_kernel(x: torch.Tensor, weight: torch.Tensor, bias, out_dtype) ->
     reduction of at least 2,048 (the swapped kernel streams the weights as fast as or faster than the library at every
     decode batch, measured on a B200 at the 7B shapes: the output head over 152,064 tokens at 8 rows in 163 against 181 us,
     gate+up at 64 rows in 47 against 50 us, the whole step 4 % faster at batch 32; and it starts fetching weights while
-    the kernel before it still runs).  Prompt-sized products stay with the library, whose kernels are up to 10 % ahead of
+    the kernel before it still runs), except products of a few tens of megabytes at more than 32 rows (qkv and o at the 7B
+    shape: 12.6 and 11.2 us against the library's 9.1 and 8.3 at 64 rows; the step 4.54 against 4.61 ms at batch 64, 4.29
+    against 4.33 at batch 48, even at batch 32, behind below).  Prompt-sized products stay with the library, whose kernels are up to 10 % ahead of
     this package's pair kernel, except gate+up with SwiGLU, which the pair kernel fuses (see ``gated_linear``)."""
     policy = gemm_policy()
     if policy == "library" or out_dtype not in (torch.bfloat16, torch.float32) or not gemm.supported(x, weight):
@@ -48,6 +52,8 @@ def _takes_own_kernel(x: torch.Tensor, weight: torch.Tensor, bias, out_dtype) ->
     if policy == "own":
         return True
     m, k = x.shape
+    if m > 32 and weight.shape[0] * k * 2 <= SMALL_PRODUCT_BYTES:
+        return False
     return k >= 2048 and m <= 64
 
 
